@@ -1,0 +1,117 @@
+/*
+ * oxq -- B200 (sm_100a) kernels for oxydLLM's quantized-weight matrix product.
+ *
+ * C ABI of liboxq.so. Every entry point takes raw DEVICE pointers to the
+ * reference's packed layouts (unchanged), explicit sizes, dtype enums and a
+ * cudaStream_t passed as void*. The library never allocates or frees caller
+ * memory, never synchronises the device and never aborts: it returns an
+ * oxq_status and records a message retrievable with oxq_last_error().
+ * All work is enqueued on the given stream. Results are deterministic: no
+ * floating-point atomics, fixed-order reductions (the reference's
+ * bit-reproducibility contract, metal_ops.rs:4562-4625).
+ *
+ * Each declaration cites the reference interface it stands in for
+ * (file:line inside the oxydllm source tree).
+ */
+#ifndef OXQ_H
+#define OXQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    OXQ_OK = 0,
+    OXQ_ERR_BAD_SHAPE = -1,   /* a shape/divisibility rule of the reference is violated */
+    OXQ_ERR_BAD_ALIGN = -2,   /* a pointer is not aligned as the kernel requires */
+    OXQ_ERR_UNSUPPORTED = -3, /* dtype / bits / format combination not implemented */
+    OXQ_ERR_NULL = -4,        /* a required pointer is NULL */
+    OXQ_ERR_WORKSPACE = -5,   /* workspace missing or too small */
+    OXQ_ERR_CUDA = -6,        /* a CUDA runtime/driver call failed */
+    OXQ_ERR_DEVICE_FLAG = -7  /* a kernel reported a bounded wait that ran out */
+} oxq_status;
+
+/* Element types of activations, scales, biases and outputs. */
+typedef enum { OXQ_F32 = 0, OXQ_F16 = 1, OXQ_BF16 = 2 } oxq_dtype;
+
+/* GGML block types, numbered as in GGUF files (candle GgmlDType; linear.rs:199-211). */
+typedef enum { OXQ_GGML_Q4_0 = 2, OXQ_GGML_Q8_0 = 8, OXQ_GGML_Q4_K = 12, OXQ_GGML_Q6_K = 14 } oxq_ggml_type;
+
+const char *oxq_status_string(int status);
+/* Message of the last failing call on this thread ("" if none). */
+const char *oxq_last_error(void);
+int oxq_version(void);
+
+/* ------------------------------------------------------------------ AWQ
+ * qweight u32 [k, n/8] (slot s of a word = out column 8j + {0,2,4,6,1,3,5,7}[s]),
+ * qzeros u32 [k/g, n/8], scales [k/g, n] of `scales_dtype` (awq.rs:23-24,45-70).
+ */
+
+/* dequantize_awq / fill_awq_weight (awq.rs:325-440,612-633):
+ * w_out[o][i] = convert((nibble - zero) as f32 * f32(scale)), dense [n, k], bit-exact. */
+int oxq_awq_dequant(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                    void *w_out, int out_dtype, int k, int n, int group_size, void *stream);
+
+/* PackedQuantLinear::forward decode branch -> w4a16_matmul (linear.rs:450-480,
+ * metal_ops.rs:1821-1867): y[m, n] = x[m, k] . deq(W) (+ bias[n]), 1 <= m <= 32,
+ * x bf16, f32 accumulation, y in `y_dtype`. No workspace: the split along k is
+ * reduced inside a thread-block cluster. */
+int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
+                 int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+                 int group_size, void *stream);
+
+/* ------------------------------------------------------------------ GPTQ
+ * qweight u32 [k/pf, n] sequential LSB-first along k, qzeros u32 [k/g, n/pf]
+ * storing zero-1 (NULL or sym != 0: zero = 2^(bits-1) - 1), pf = 32/bits. */
+
+/* dequantize_gptq / fill_gptq_weight (awq.rs:442-590), dense [n, k], bit-exact. */
+int oxq_gptq_dequant(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                     void *w_out, int out_dtype, int k, int n, int group_size, int bits, int sym, void *stream);
+
+/* ------------------------------------------------------------------ GGUF
+ * weight = raw GGML blocks, rows [n] contiguous, blocks along k
+ * (metal_ops.rs:5228-5241, linear.rs:220-236). */
+
+/* QTensor::dequantize as restated by the reference's per-element strips
+ * (quant_kernels.metal:2342-2384,2438-2482,2518-2554), dense [n, k], bit-exact. */
+int oxq_gguf_dequant(int ggml_type, const void *blocks, void *w_out, int out_dtype, int n, int k, void *stream);
+
+/* QLinear::forward (linear.rs:324-393) / gguf_quant_matmul (metal_ops.rs:5819):
+ * y[m, n] = x[m, k] . deq(W)^T (+ bias), 1 <= m <= 32, x bf16. */
+int oxq_gguf_gemv(int ggml_type, const void *x, int x_dtype, const void *blocks, const void *bias, int bias_dtype,
+                  void *y, int y_dtype, int m, int k, int n, void *stream);
+
+/* ------------------------------------------------------------------- FP8
+ * weight = E4M3fn bytes [n, k]; scale_inv f32 grid [s_out, s_in] tiling the
+ * weight evenly (128x128 blocks: s_out = n/128, s_in = k/128; per-row: s_in = 1;
+ * scalar: 1x1; none: NULL) (linear.rs:96-141, weights.rs:207-234). */
+
+/* f8_block_dequant_bf16 / Fp8Linear's dequant (metal_ops.rs:5788, linear.rs:96-141):
+ * w_out = convert(f32(e4m3) * scale), bit-exact. */
+int oxq_fp8_dequant(const uint8_t *weight, const float *scale_inv, int s_out, int s_in, void *w_out, int out_dtype,
+                    int n, int k, void *stream);
+
+/* Fp8Linear::forward (linear.rs:96-145) / f8_gemv (metal_ops.rs:5788-5796), 1 <= m <= 32. */
+int oxq_fp8_gemv(const void *x, int x_dtype, const uint8_t *weight, const float *scale_inv, int s_out, int s_in,
+                 const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, void *stream);
+
+/* ----------------------------------------------------------------- MXFP4
+ * blocks u8 [n, k/32, 16] two E2M1 codes per byte low nibble first, scales u8
+ * [n, k/32] E8M0 (mxfp4.rs:3-6). */
+
+/* dequantize_mxfp4_f32 (mxfp4.rs:35-64), dense [n, k], bit-exact. */
+int oxq_mxfp4_dequant(const uint8_t *blocks, const uint8_t *scales, void *w_out, int out_dtype, int n, int k,
+                      void *stream);
+
+/* Mxfp4Linear::forward (mxfp4.rs:119-154) / mxfp4_matmul gemv branch
+ * (metal_ops.rs:6197-6222), 1 <= m <= 32. */
+int oxq_mxfp4_gemv(const void *x, int x_dtype, const uint8_t *blocks, const uint8_t *scales, const void *bias,
+                   int bias_dtype, void *y, int y_dtype, int m, int k, int n, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OXQ_H */

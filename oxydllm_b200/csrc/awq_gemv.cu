@@ -1,0 +1,369 @@
+// AWQ W4A16 batched decode GEMV, 1 <= m <= 32.
+//
+// The kernel is bound by the stream of packed weights from HBM (0.5 B/weight
+// plus scales/zeros), so everything is arranged around that stream:
+//
+//  * every lane copies exactly the packed words it will consume with cp.async
+//    into a lane-private slot of a shared-memory ring (STAGES deep), so the
+//    number of bytes in flight does not depend on registers and no barrier is
+//    needed between producer and consumer;
+//  * a warp-level step covers 16 input rows x (8 * V) packed words; lanes with
+//    the same lane%4 read one row, 8 lanes x 4V bytes contiguous, 4 rows per
+//    instruction;
+//  * the 4-bit values are turned into bf16 pairs along k with one prmt + one
+//    lop3 per weight (magic-number conversion: 0x4300 | q == 128 + q exactly),
+//    and contracted on the tensor cores (mma.sync m16n8k16, weights as the
+//    16-row operand, up to 8 tokens as the 8-column operand) with f32
+//    accumulation. One extra MMA with an all-ones operand yields sum_k x per
+//    token, so scale and zero point are applied once per quantization group in
+//    f32:  y += s * (sum (128+q) x - (128+z) sum x);
+//  * the split along k (needed to fill 148 SMs with a skinny problem) is
+//    reduced in fixed rank order through distributed shared memory inside a
+//    thread-block cluster: no workspace, no second launch, no atomics.
+#include <cooperative_groups.h>
+
+#include <cstdio>
+#include <cstdlib>
+
+#include "oxq_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace oxq {
+
+constexpr int GEMV_STAGES = 8;
+
+struct AwqGemvParams {
+    const __nv_bfloat16 *x;
+    const uint32_t *qweight;
+    const uint32_t *qzeros;
+    const void *scales;
+    const void *bias;
+    void *y;
+    int scales_dtype, bias_dtype, y_dtype;
+    int m, k, n, group_size;
+    int packed_out;
+    int steps_per_cta; // 16-row steps handled by one CTA of the cluster
+};
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <int BYTES> __device__ __forceinline__ void cp_async(uint32_t smem_addr, const void *gptr, bool valid)
+{
+    const uint32_t src_size = valid ? BYTES : 0; // 0 -> the slot is zero-filled, the source is not read
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;\n" ::"r"(smem_addr), "l"(gptr), "n"(BYTES),
+                 "r"(src_size)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// Nibble `slot` (0..7) of w0 and of w1 as the bf16 pair (128 + q0, 128 + q1).
+// Slots 2b and 2b+1 live in byte b: gather byte b of both words with one prmt.
+template <int B> __device__ __forceinline__ uint32_t gather_byte(uint32_t w0, uint32_t w1)
+{
+    return __byte_perm(w0, w1, B | (B << 4) | ((4 + B) << 8) | ((4 + B) << 12));
+}
+__device__ __forceinline__ uint32_t lo_nibbles_bf16(uint32_t p) { return (p & 0x000F000Fu) | 0x43004300u; }
+__device__ __forceinline__ uint32_t hi_nibbles_bf16(uint32_t p) { return ((p >> 4) & 0x000F000Fu) | 0x43004300u; }
+
+// MT: 8-token tiles (m <= 8*MT). V: packed words per lane per input row.
+template <int MT, int V, int NW>
+__global__ void __launch_bounds__(NW * 32, 1) awq_gemv_kernel(const AwqGemvParams p)
+{
+    constexpr int NT = NW * 32;
+    constexpr int NACC = V * 4 * MT * 4;
+    constexpr int W_BYTES = 4 * V;                            // per lane per row
+    constexpr int STAGE_BYTES = 32 * (4 * W_BYTES + 8 * MT);  // per warp
+    extern __shared__ __align__(16) unsigned char smem[];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int rank = blockIdx.y, nranks = gridDim.y;
+
+    const int jbase = (blockIdx.x * NW + warp) * 8 * V + g * V; // first packed word of this lane
+    const bool j_ok = jbase < p.packed_out;                     // packed_out % V == 0: all or nothing
+    const int total_steps = p.k >> 4;
+    const int step_beg = rank * p.steps_per_cta;
+    const int step_end = min(total_steps, step_beg + p.steps_per_cta);
+    const int steps = max(0, step_end - step_beg);
+
+    unsigned char *ring = smem + (size_t)warp * GEMV_STAGES * STAGE_BYTES;
+    const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(ring);
+    // slot layout per stage: [row i][lane] W_BYTES, then [mt][lane] 8 bytes of x
+    const uint32_t w_off = lane * W_BYTES, x_off = 4 * 32 * W_BYTES + lane * 8;
+
+    auto issue = [&](int s) {
+        const uint32_t base = ring_addr + (uint32_t)(s % GEMV_STAGES) * STAGE_BYTES;
+        const int kb = (step_beg + s) * 16 + 4 * c;
+        const uint32_t *wsrc = p.qweight + (size_t)kb * p.packed_out + (j_ok ? jbase : 0);
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            cp_async<W_BYTES>(base + i * 32 * W_BYTES + w_off, wsrc + (size_t)i * p.packed_out, j_ok);
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            const int row = 8 * mt + g;
+            const bool ok = row < p.m;
+            cp_async<8>(base + x_off + mt * 32 * 8, p.x + (size_t)(ok ? row : 0) * p.k + kb, ok);
+        }
+    };
+
+    float acc[V][4][MT][4], tot[V][4][MT][4], sx[MT][4];
+#pragma unroll
+    for (int v = 0; v < V; v++)
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[v][t][mt][e] = tot[v][t][mt][e] = 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) sx[mt][e] = 0.0f;
+
+#pragma unroll
+    for (int s = 0; s < GEMV_STAGES - 1; s++) {
+        if (s < steps) issue(s);
+        cp_async_commit();
+    }
+
+    const uint32_t ones[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};
+
+    for (int s = 0; s < steps; s++) {
+        cp_async_wait<GEMV_STAGES - 2>();
+        if (s + GEMV_STAGES - 1 < steps) issue(s + GEMV_STAGES - 1);
+        cp_async_commit();
+
+        const unsigned char *st = ring + (size_t)(s % GEMV_STAGES) * STAGE_BYTES;
+        uint32_t w[4][V], xb[MT][2];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (V == 1) w[i][0] = *reinterpret_cast<const uint32_t *>(st + i * 32 * W_BYTES + w_off);
+            else if (V == 2) {
+                const uint2 t2 = *reinterpret_cast<const uint2 *>(st + i * 32 * W_BYTES + w_off);
+                w[i][0] = t2.x; w[i][V - 1] = t2.y;
+            } else {
+                const uint4 t4 = *reinterpret_cast<const uint4 *>(st + i * 32 * W_BYTES + w_off);
+                w[i][0] = t4.x; w[i][1 % V] = t4.y; w[i][2 % V] = t4.z; w[i][3 % V] = t4.w;
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            const uint2 t2 = *reinterpret_cast<const uint2 *>(st + x_off + mt * 32 * 8);
+            xb[mt][0] = t2.x; xb[mt][1] = t2.y;
+        }
+
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) mma_bf16_16816(sx[mt], ones, xb[mt]);
+
+#pragma unroll
+        for (int v = 0; v < V; v++) {
+            // rows (4c, 4c+1) -> first k pair, rows (4c+2, 4c+3) -> second k pair
+            const uint32_t pa[4] = {gather_byte<0>(w[0][v], w[1][v]), gather_byte<1>(w[0][v], w[1][v]),
+                                    gather_byte<2>(w[0][v], w[1][v]), gather_byte<3>(w[0][v], w[1][v])};
+            const uint32_t pb[4] = {gather_byte<0>(w[2][v], w[3][v]), gather_byte<1>(w[2][v], w[3][v]),
+                                    gather_byte<2>(w[2][v], w[3][v]), gather_byte<3>(w[2][v], w[3][v])};
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                // tile t: MMA row g = column 2t of the word (slot t), row g+8 = column 2t+1 (slot t+4)
+                uint32_t a[4];
+                if (t & 1) {
+                    a[0] = hi_nibbles_bf16(pa[t >> 1]); a[1] = hi_nibbles_bf16(pa[2 + (t >> 1)]);
+                    a[2] = hi_nibbles_bf16(pb[t >> 1]); a[3] = hi_nibbles_bf16(pb[2 + (t >> 1)]);
+                } else {
+                    a[0] = lo_nibbles_bf16(pa[t >> 1]); a[1] = lo_nibbles_bf16(pa[2 + (t >> 1)]);
+                    a[2] = lo_nibbles_bf16(pb[t >> 1]); a[3] = lo_nibbles_bf16(pb[2 + (t >> 1)]);
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) mma_bf16_16816(acc[v][t][mt], a, xb[mt]);
+            }
+        }
+
+        // End of a quantization group (or of this CTA's k range): fold scale and zero point in f32.
+        const int k_next = (step_beg + s + 1) * 16;
+        if ((k_next % p.group_size) == 0 || s == steps - 1) {
+            const int grp = (k_next - 1) / p.group_size;
+#pragma unroll
+            for (int v = 0; v < V; v++) {
+                const uint32_t zw = j_ok ? p.qzeros[(size_t)grp * p.packed_out + jbase + v] : 0u;
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    const size_t n0 = (size_t)(jbase + v) * 8 + 2 * t;
+                    const float s0 = j_ok ? load_as_f32(p.scales, p.scales_dtype, (size_t)grp * p.n + n0) : 0.0f;
+                    const float s1 = j_ok ? load_as_f32(p.scales, p.scales_dtype, (size_t)grp * p.n + n0 + 1) : 0.0f;
+                    const float z0 = 128.0f + (float)((zw >> (4 * t)) & 0xFu);
+                    const float z1 = 128.0f + (float)((zw >> (4 * t + 16)) & 0xFu);
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) {
+                        float(&a4)[4] = acc[v][t][mt];
+                        float(&t4)[4] = tot[v][t][mt];
+                        t4[0] = fmaf(s0, fmaf(-z0, sx[mt][0], a4[0]), t4[0]);
+                        t4[1] = fmaf(s0, fmaf(-z0, sx[mt][1], a4[1]), t4[1]);
+                        t4[2] = fmaf(s1, fmaf(-z1, sx[mt][0], a4[2]), t4[2]);
+                        t4[3] = fmaf(s1, fmaf(-z1, sx[mt][1], a4[3]), t4[3]);
+                        a4[0] = a4[1] = a4[2] = a4[3] = 0.0f;
+                    }
+                }
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) sx[mt][0] = sx[mt][1] = sx[mt][2] = sx[mt][3] = 0.0f;
+        }
+    }
+    cp_async_wait<0>();
+
+    // tot[v][t][mt][e]: token 8mt + 2c + (e&1), out column 8(jbase+v) + 2t + (e>>1)
+    auto emit = [&](int v, int t, int mt, int e, float val) {
+        const int row = 8 * mt + 2 * c + (e & 1);
+        const size_t col = (size_t)(jbase + v) * 8 + 2 * t + (e >> 1);
+        if (j_ok && row < p.m) {
+            if (p.bias) val += load_as_f32(p.bias, p.bias_dtype, col);
+            store_as(p.y, p.y_dtype, (size_t)row * p.n + col, val);
+        }
+    };
+
+    if (nranks == 1) {
+#pragma unroll
+        for (int v = 0; v < V; v++)
+#pragma unroll
+            for (int t = 0; t < 4; t++)
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) emit(v, t, mt, e, tot[v][t][mt][e]);
+        return;
+    }
+
+    // Cluster reduction over the k split: every CTA publishes its partials in its
+    // own shared memory, then CTA r sums accumulator slots a == r (mod nranks)
+    // over the ranks in ascending order.
+    cg::cluster_group cluster = cg::this_cluster();
+    float *red = reinterpret_cast<float *>(smem);
+    __syncthreads(); // every warp is done with its ring before it is reused
+#pragma unroll
+    for (int v = 0; v < V; v++)
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) red[(((v * 4 + t) * MT + mt) * 4 + e) * NT + tid] = tot[v][t][mt][e];
+    cluster.sync();
+#pragma unroll
+    for (int v = 0; v < V; v++)
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int a = ((v * 4 + t) * MT + mt) * 4 + e;
+                    if (a % nranks == rank) {
+                        float sum = 0.0f;
+                        for (int q = 0; q < nranks; q++) sum += cluster.map_shared_rank(red, q)[a * NT + tid];
+                        emit(v, t, mt, e, sum);
+                    }
+                }
+    cluster.sync(); // nobody leaves while a peer may still read its shared memory
+    (void)NACC;
+}
+
+template <int MT, int V, int NW>
+static int launch_awq_gemv(const AwqGemvParams &p, int ksplit, cudaStream_t stream)
+{
+    constexpr int NACC = V * 4 * MT * 4;
+    constexpr int STAGE_BYTES = 32 * (16 * V + 8 * MT);
+    const size_t ring = (size_t)NW * GEMV_STAGES * STAGE_BYTES;
+    const size_t red = (size_t)NACC * NW * 32 * sizeof(float);
+    const size_t smem = ring > red ? ring : red;
+    auto kern = awq_gemv_kernel<MT, V, NW>;
+    // Per-device, once: the attribute call is not a stream operation and must stay out of graph captures.
+    static bool configured[64] = {};
+    int device = 0;
+    OXQ_CUDA(cudaGetDevice(&device));
+    if (device < 64 && !configured[device]) {
+        OXQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[device] = true;
+    } else if (device >= 64) {
+        OXQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ceil_div(p.packed_out, 8 * V * NW), ksplit, 1);
+    cfg.blockDim = dim3(NW * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = ksplit;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    OXQ_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+    return OXQ_OK;
+}
+
+} // namespace oxq
+
+using namespace oxq;
+
+OXQ_EXPORT int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros,
+                            const void *scales, int scales_dtype, const void *bias, int bias_dtype, void *y,
+                            int y_dtype, int m, int k, int n, int group_size, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(x && qweight && qzeros && scales && y, OXQ_ERR_NULL, "oxq_awq_gemv: null pointer");
+    OXQ_REQUIRE(x_dtype == OXQ_BF16, OXQ_ERR_UNSUPPORTED, "oxq_awq_gemv: activations must be bf16");
+    OXQ_REQUIRE(valid_dtype(scales_dtype) && valid_dtype(y_dtype) && (!bias || valid_dtype(bias_dtype)),
+                OXQ_ERR_UNSUPPORTED, "oxq_awq_gemv: unsupported dtype");
+    OXQ_REQUIRE(m >= 1 && m <= 32, OXQ_ERR_BAD_SHAPE, "oxq_awq_gemv: m=%d outside 1..32 (use the GEMM entry)", m);
+    OXQ_REQUIRE(k > 0 && n > 0 && group_size > 0, OXQ_ERR_BAD_SHAPE, "oxq_awq_gemv: non-positive size");
+    OXQ_REQUIRE(n % 8 == 0, OXQ_ERR_BAD_SHAPE, "AWQ out_features (%d) not divisible by pack factor 8", n);
+    OXQ_REQUIRE(k % group_size == 0, OXQ_ERR_BAD_SHAPE, "quant in_features (%d) not divisible by group size (%d)", k,
+                group_size);
+    OXQ_REQUIRE((group_size & (group_size - 1)) == 0, OXQ_ERR_BAD_SHAPE, "group_size %d is not a power of two",
+                group_size);
+    OXQ_REQUIRE(group_size % 16 == 0 && k % 16 == 0, OXQ_ERR_UNSUPPORTED,
+                "oxq_awq_gemv: group_size (%d) and in_features (%d) must be multiples of 16", group_size, k);
+    OXQ_REQUIRE(aligned(x, 16) && aligned(qweight, 16) && aligned(qzeros, 4) && aligned(scales, 4) && aligned(y, 4),
+                OXQ_ERR_BAD_ALIGN, "oxq_awq_gemv: x/qweight must be 16-byte aligned");
+
+    AwqGemvParams p;
+    p.x = (const __nv_bfloat16 *)x;
+    p.qweight = qweight; p.qzeros = qzeros; p.scales = scales; p.bias = bias; p.y = y;
+    p.scales_dtype = scales_dtype; p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
+    p.m = m; p.k = k; p.n = n; p.group_size = group_size;
+    p.packed_out = n / 8;
+
+    const int mt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
+    int v = mt == 4 ? 1 : 2;
+    if (p.packed_out % v != 0) v = 1;
+    constexpr int NW = 4;
+    const int total_steps = k / 16;
+    // Enough CTAs for about two per SM; the k split is the cluster size (portable maximum 8).
+    const int n_tiles = ceil_div(p.packed_out, 8 * v * NW);
+    int ksplit = 1;
+    while (ksplit < 8 && n_tiles * ksplit < 2 * 148 && total_steps / (ksplit * 2) >= 4) ksplit *= 2;
+    if (const char *env = getenv("OXQ_AWQ_GEMV_TUNE")) { // bench-harness knob: "V,KSPLIT"
+        int ev = 0, ek = 0;
+        if (sscanf(env, "%d,%d", &ev, &ek) == 2) {
+            if ((ev == 1 || ev == 2 || ev == 4) && p.packed_out % ev == 0 && 16 * ev * mt <= 64) v = ev;
+            if (ek == 1 || ek == 2 || ek == 4 || ek == 8) ksplit = ek;
+        }
+    }
+    p.steps_per_cta = ceil_div(total_steps, ksplit);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (mt == 1 && v == 1) return launch_awq_gemv<1, 1, NW>(p, ksplit, st);
+    if (mt == 1 && v == 2) return launch_awq_gemv<1, 2, NW>(p, ksplit, st);
+    if (mt == 1 && v == 4) return launch_awq_gemv<1, 4, NW>(p, ksplit, st);
+    if (mt == 2 && v == 1) return launch_awq_gemv<2, 1, NW>(p, ksplit, st);
+    if (mt == 2 && v == 2) return launch_awq_gemv<2, 2, NW>(p, ksplit, st);
+    return launch_awq_gemv<4, 1, NW>(p, ksplit, st);
+}

@@ -1,0 +1,254 @@
+// Dequantization kernels: packed weights -> dense [n, k] in f32/f16/bf16,
+// bit-exact with the reference's CPU dequantizers. They are memory-bound
+// elementwise passes (the load-time path of the reference on non-Metal
+// devices, and the checking tool for every fused kernel).
+#include "formats.cuh"
+
+namespace oxq {
+
+// ---- AWQ -------------------------------------------------------------------
+// A CTA converts a tile of TK input rows x 64 out columns (8 packed words per
+// row) and transposes it through shared memory so that the dense [n, k] output
+// is written in runs along k.
+constexpr int AWQ_TK = 32;
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+awq_dequant_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict__ qzeros,
+                   const void *__restrict__ scales, int scales_dtype, OutT *__restrict__ w_out, int k, int n,
+                   int group_size)
+{
+    __shared__ float tile[64][AWQ_TK + 1];
+    const int packed_out = n >> 3;
+    const int k0 = blockIdx.y * AWQ_TK;
+    const int jw0 = blockIdx.x * 8;
+    const int t = threadIdx.x;
+
+    {
+        const int r = t >> 3, jw = jw0 + (t & 7);
+        const int kk = k0 + r;
+        if (kk < k && jw < packed_out) {
+            const int g = kk / group_size;
+            const uint32_t w = qweight[(size_t)kk * packed_out + jw];
+            const uint32_t z = qzeros[(size_t)g * packed_out + jw];
+#pragma unroll
+            for (int col = 0; col < 8; col++) {
+                const int sh = 4 * awq_slot_of_col(col);
+                const int q = (int)((w >> sh) & 0xFu) - (int)((z >> sh) & 0xFu);
+                const float s = load_as_f32(scales, scales_dtype, (size_t)g * n + (size_t)jw * 8 + col);
+                tile[(t & 7) * 8 + col][r] = __fmul_rn((float)q, s);
+            }
+        }
+    }
+    __syncthreads();
+    // 64 columns x 32 k: each group of 32 threads writes one column's run.
+    for (int c = t >> 5; c < 64; c += 8) {
+        const int o = jw0 * 8 + c, kk = k0 + (t & 31);
+        if (o < n && kk < k) w_out[(size_t)o * k + kk] = narrow<OutT>(tile[c][t & 31]);
+    }
+}
+
+// ---- GPTQ ------------------------------------------------------------------
+// One thread per output element, consecutive threads along k of one out row;
+// a word of qweight serves pf consecutive k so the reads stay cached.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+gptq_dequant_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict__ qzeros,
+                    const void *__restrict__ scales, int scales_dtype, OutT *__restrict__ w_out, int k, int n,
+                    int group_size, int bits, int sym)
+{
+    const int pf = 32 / bits;
+    const uint32_t mask = (1u << bits) - 1u;
+    const size_t total = (size_t)n * k;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int o = (int)(idx / k), i = (int)(idx % k);
+        const int g = i / group_size;
+        const uint32_t q = (qweight[(size_t)(i / pf) * n + o] >> ((i % pf) * bits)) & mask;
+        uint32_t zero;
+        if (sym) zero = (1u << (bits - 1)) - 1u;
+        else zero = (qzeros[(size_t)g * (n / pf) + o / pf] >> ((o % pf) * bits)) & mask;
+        const float s = load_as_f32(scales, scales_dtype, (size_t)g * n + o);
+        w_out[idx] = narrow<OutT>(__fmul_rn((float)((int)q - ((int)zero + 1)), s));
+    }
+}
+
+// ---- GGUF ------------------------------------------------------------------
+template <int TYPE, typename OutT>
+__global__ void __launch_bounds__(256)
+gguf_dequant_kernel(const uint8_t *__restrict__ blocks, OutT *__restrict__ w_out, size_t total)
+{
+    int bel, bby;
+    gguf_block_layout(TYPE, bel, bby);
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t b = idx / bel;
+        const int j = (int)(idx % bel);
+        w_out[idx] = narrow<OutT>(gguf_decode_elem<TYPE>(blocks + b * bby, j));
+    }
+}
+
+// ---- FP8 -------------------------------------------------------------------
+// Four bytes per thread; scale grid [s_out, s_in] tiles the [n, k] weight in
+// (n/s_out) x (k/s_in) blocks. scale_inv == nullptr means no scaling.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+fp8_dequant_kernel(const uint8_t *__restrict__ weight, const float *__restrict__ scale_inv, int s_in, int block_out,
+                   int block_in, OutT *__restrict__ w_out, int n, int k)
+{
+    const size_t total4 = (size_t)n * k / 4;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t e = idx * 4;
+        const int r = (int)(e / k), c = (int)(e % k);
+        const uint32_t w = reinterpret_cast<const uint32_t *>(weight)[idx];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            float v = e4m3_to_f32((w >> (8 * u)) & 0xFFu);
+            if (scale_inv) v = __fmul_rn(scale_inv[(size_t)(r / block_out) * s_in + (c + u) / block_in], v);
+            w_out[e + u] = narrow<OutT>(v);
+        }
+    }
+}
+
+// ---- MXFP4 -----------------------------------------------------------------
+// One thread per packed byte (two consecutive k of one row).
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+mxfp4_dequant_kernel(const uint8_t *__restrict__ blocks, const uint8_t *__restrict__ scales,
+                     OutT *__restrict__ w_out, size_t total_bytes)
+{
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_bytes;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t b = blocks[idx];
+        const float s = e8m0_to_f32(scales[idx >> 4]);
+        w_out[2 * idx] = narrow<OutT>(__fmul_rn(e2m1_to_f32(b & 0xFu), s));
+        w_out[2 * idx + 1] = narrow<OutT>(__fmul_rn(e2m1_to_f32(b >> 4), s));
+    }
+}
+
+static int grid_for(size_t work_items, int block = 256)
+{
+    size_t blocks = (work_items + block - 1) / block;
+    const size_t cap = 148 * 32; // a few waves of resident CTAs on 148 SMs, then grid-stride
+    return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+} // namespace oxq
+
+using namespace oxq;
+
+#define DISPATCH_OUT(dtype, ...)                                              \
+    do {                                                                      \
+        if ((dtype) == OXQ_F32) { using OutT = float; __VA_ARGS__; }          \
+        else if ((dtype) == OXQ_F16) { using OutT = __half; __VA_ARGS__; }    \
+        else { using OutT = __nv_bfloat16; __VA_ARGS__; }                     \
+    } while (0)
+
+OXQ_EXPORT int oxq_awq_dequant(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                               void *w_out, int out_dtype, int k, int n, int group_size, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(qweight && qzeros && scales && w_out, OXQ_ERR_NULL, "oxq_awq_dequant: null pointer");
+    OXQ_REQUIRE(valid_dtype(scales_dtype) && valid_dtype(out_dtype), OXQ_ERR_UNSUPPORTED,
+                "oxq_awq_dequant: unsupported dtype");
+    OXQ_REQUIRE(k > 0 && n > 0 && group_size > 0, OXQ_ERR_BAD_SHAPE, "oxq_awq_dequant: non-positive size");
+    OXQ_REQUIRE(n % 8 == 0, OXQ_ERR_BAD_SHAPE, "AWQ out_features (%d) not divisible by pack factor 8", n);
+    OXQ_REQUIRE(k % group_size == 0, OXQ_ERR_BAD_SHAPE,
+                "quant in_features (%d) not divisible by group size (%d)", k, group_size);
+    dim3 grid(ceil_div(n / 8, 8), ceil_div(k, AWQ_TK));
+    DISPATCH_OUT(out_dtype, awq_dequant_kernel<OutT><<<grid, 256, 0, (cudaStream_t)stream>>>(
+                                qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size));
+    OXQ_LAUNCH_CHECK("awq_dequant_kernel");
+    return OXQ_OK;
+}
+
+OXQ_EXPORT int oxq_gptq_dequant(const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
+                                int scales_dtype, void *w_out, int out_dtype, int k, int n, int group_size, int bits,
+                                int sym, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(qweight && scales && w_out, OXQ_ERR_NULL, "oxq_gptq_dequant: null pointer");
+    OXQ_REQUIRE(valid_dtype(scales_dtype) && valid_dtype(out_dtype), OXQ_ERR_UNSUPPORTED,
+                "oxq_gptq_dequant: unsupported dtype");
+    OXQ_REQUIRE(bits == 4 || bits == 8, OXQ_ERR_UNSUPPORTED, "dequantize_gptq: only 4/8-bit supported, got %d", bits);
+    OXQ_REQUIRE(k > 0 && n > 0 && group_size > 0, OXQ_ERR_BAD_SHAPE, "oxq_gptq_dequant: non-positive size");
+    const int pf = 32 / bits;
+    OXQ_REQUIRE(n % pf == 0, OXQ_ERR_BAD_SHAPE, "GPTQ out_features %d not divisible by pack_factor %d", n, pf);
+    OXQ_REQUIRE(k % pf == 0 && k % group_size == 0, OXQ_ERR_BAD_SHAPE,
+                "GPTQ in_features %d not divisible by pack_factor %d / group size %d", k, pf, group_size);
+    const int use_sym = (sym != 0 || qzeros == nullptr) ? 1 : 0;
+    DISPATCH_OUT(out_dtype, gptq_dequant_kernel<OutT><<<grid_for((size_t)n * k), 256, 0, (cudaStream_t)stream>>>(
+                                qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size, bits, use_sym));
+    OXQ_LAUNCH_CHECK("gptq_dequant_kernel");
+    return OXQ_OK;
+}
+
+OXQ_EXPORT int oxq_gguf_dequant(int ggml_type, const void *blocks, void *w_out, int out_dtype, int n, int k,
+                                void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(blocks && w_out, OXQ_ERR_NULL, "oxq_gguf_dequant: null pointer");
+    OXQ_REQUIRE(valid_dtype(out_dtype), OXQ_ERR_UNSUPPORTED, "oxq_gguf_dequant: unsupported out dtype");
+    int bel, bby;
+    OXQ_REQUIRE(gguf_block_layout(ggml_type, bel, bby), OXQ_ERR_UNSUPPORTED, "unsupported GGML type %d", ggml_type);
+    OXQ_REQUIRE(n > 0 && k > 0 && k % bel == 0, OXQ_ERR_BAD_SHAPE,
+                "GGUF in_features %d is not a multiple of the block size %d", k, bel);
+    OXQ_REQUIRE(aligned(blocks, 2), OXQ_ERR_BAD_ALIGN, "GGUF blocks must be 2-byte aligned");
+    const size_t total = (size_t)n * k;
+    const uint8_t *b = (const uint8_t *)blocks;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int grid = grid_for(total);
+    switch (ggml_type) {
+    case OXQ_GGML_Q4_0:
+        DISPATCH_OUT(out_dtype, gguf_dequant_kernel<OXQ_GGML_Q4_0, OutT><<<grid, 256, 0, st>>>(b, (OutT *)w_out, total));
+        break;
+    case OXQ_GGML_Q8_0:
+        DISPATCH_OUT(out_dtype, gguf_dequant_kernel<OXQ_GGML_Q8_0, OutT><<<grid, 256, 0, st>>>(b, (OutT *)w_out, total));
+        break;
+    case OXQ_GGML_Q4_K:
+        DISPATCH_OUT(out_dtype, gguf_dequant_kernel<OXQ_GGML_Q4_K, OutT><<<grid, 256, 0, st>>>(b, (OutT *)w_out, total));
+        break;
+    default:
+        DISPATCH_OUT(out_dtype, gguf_dequant_kernel<OXQ_GGML_Q6_K, OutT><<<grid, 256, 0, st>>>(b, (OutT *)w_out, total));
+        break;
+    }
+    OXQ_LAUNCH_CHECK("gguf_dequant_kernel");
+    return OXQ_OK;
+}
+
+OXQ_EXPORT int oxq_fp8_dequant(const uint8_t *weight, const float *scale_inv, int s_out, int s_in, void *w_out,
+                               int out_dtype, int n, int k, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(weight && w_out, OXQ_ERR_NULL, "oxq_fp8_dequant: null pointer");
+    OXQ_REQUIRE(valid_dtype(out_dtype), OXQ_ERR_UNSUPPORTED, "oxq_fp8_dequant: unsupported out dtype");
+    OXQ_REQUIRE(n > 0 && k > 0 && k % 4 == 0, OXQ_ERR_BAD_SHAPE, "FP8 weight [%d, %d]: in_features must be a multiple of 4",
+                n, k);
+    OXQ_REQUIRE(aligned(weight, 4), OXQ_ERR_BAD_ALIGN, "FP8 weight must be 4-byte aligned");
+    int bo = n, bi = k;
+    if (scale_inv) {
+        OXQ_REQUIRE(s_out > 0 && s_in > 0 && n % s_out == 0 && k % s_in == 0, OXQ_ERR_BAD_SHAPE,
+                    "block-wise FP8 weight_scale_inv [%d, %d] does not tile weight [%d, %d] evenly", s_out, s_in, n, k);
+        bo = n / s_out;
+        bi = k / s_in;
+    }
+    DISPATCH_OUT(out_dtype, fp8_dequant_kernel<OutT><<<grid_for((size_t)n * k / 4), 256, 0, (cudaStream_t)stream>>>(
+                                weight, scale_inv, s_in, bo, bi, (OutT *)w_out, n, k));
+    OXQ_LAUNCH_CHECK("fp8_dequant_kernel");
+    return OXQ_OK;
+}
+
+OXQ_EXPORT int oxq_mxfp4_dequant(const uint8_t *blocks, const uint8_t *scales, void *w_out, int out_dtype, int n,
+                                 int k, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(blocks && scales && w_out, OXQ_ERR_NULL, "oxq_mxfp4_dequant: null pointer");
+    OXQ_REQUIRE(valid_dtype(out_dtype), OXQ_ERR_UNSUPPORTED, "oxq_mxfp4_dequant: unsupported out dtype");
+    OXQ_REQUIRE(n > 0 && k > 0 && k % 32 == 0, OXQ_ERR_BAD_SHAPE, "MXFP4: cols %d must be a multiple of 32", k);
+    const size_t total_bytes = (size_t)n * k / 2;
+    DISPATCH_OUT(out_dtype, mxfp4_dequant_kernel<OutT><<<grid_for(total_bytes), 256, 0, (cudaStream_t)stream>>>(
+                                blocks, scales, (OutT *)w_out, total_bytes));
+    OXQ_LAUNCH_CHECK("mxfp4_dequant_kernel");
+    return OXQ_OK;
+}

@@ -1,0 +1,85 @@
+// Per-element decode of every packed weight format, bit-exact with the
+// reference's CPU dequantizers. Products and differences use the explicit
+// round-to-nearest intrinsics so that nvcc cannot contract them into fused
+// multiply-adds, which would change the last bit.
+#pragma once
+
+#include "oxq_common.cuh"
+
+namespace oxq {
+
+__host__ __device__ inline bool gguf_block_layout(int ggml_type, int &block_elems, int &block_bytes)
+{
+    switch (ggml_type) {
+    case OXQ_GGML_Q4_0: block_elems = 32; block_bytes = 18; return true;
+    case OXQ_GGML_Q8_0: block_elems = 32; block_bytes = 34; return true;
+    case OXQ_GGML_Q4_K: block_elems = 256; block_bytes = 144; return true;
+    case OXQ_GGML_Q6_K: block_elems = 256; block_bytes = 210; return true;
+    default: return false;
+    }
+}
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t ld_u16(const uint8_t *p)
+{
+    return *reinterpret_cast<const uint16_t *>(p); // all f16 fields sit at even offsets of even-sized blocks
+}
+
+// Q4_K: 6-bit scale and min of sub-block j (0..7) from the 12 packed bytes.
+__device__ __forceinline__ void q4k_scale_min(int j, const uint8_t *q, uint32_t &sc, uint32_t &mn)
+{
+    if (j < 4) {
+        sc = q[j] & 63u;
+        mn = q[j + 4] & 63u;
+    } else {
+        sc = (q[j + 4] & 0x0Fu) | ((uint32_t)(q[j - 4] >> 6) << 4);
+        mn = ((uint32_t)q[j + 4] >> 4) | ((uint32_t)(q[j] >> 6) << 4);
+    }
+}
+
+// Element j of one GGML block.
+//   Q4_0 {f16 d; u8 qs[16]}: (nibble - 8) * d, j < 16 low nibbles, j >= 16 high.
+//   Q8_0 {f16 d; i8 qs[32]}: qs[j] * d.
+//   Q4_K {f16 d, dmin; u8 scales[12]; u8 qs[128]}: (d*sc)*nibble - (dmin*mn).
+//   Q6_K {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d}: (d*scale) * (6-bit - 32).
+template <int TYPE> __device__ __forceinline__ float gguf_decode_elem(const uint8_t *blk, int j)
+{
+    if (TYPE == OXQ_GGML_Q4_0) {
+        float d = half_bits_to_f32((uint16_t)ld_u16(blk));
+        uint32_t b = blk[2 + (j & 15)];
+        int q = (int)(j < 16 ? (b & 0x0Fu) : (b >> 4)) - 8;
+        return __fmul_rn((float)q, d);
+    } else if (TYPE == OXQ_GGML_Q8_0) {
+        float d = half_bits_to_f32((uint16_t)ld_u16(blk));
+        int q = (int)(int8_t)blk[2 + j];
+        return __fmul_rn((float)q, d);
+    } else if (TYPE == OXQ_GGML_Q4_K) {
+        float d = half_bits_to_f32((uint16_t)ld_u16(blk));
+        float dmin = half_bits_to_f32((uint16_t)ld_u16(blk + 2));
+        int sub = j >> 5, el = j & 31;
+        uint32_t sc, mn;
+        q4k_scale_min(sub, blk + 4, sc, mn);
+        float sc_v = __fmul_rn(d, (float)sc), m_v = __fmul_rn(dmin, (float)mn);
+        uint32_t b = blk[16 + (sub >> 1) * 32 + el];
+        uint32_t nib = (sub & 1) ? (b >> 4) : (b & 0x0Fu);
+        return __fsub_rn(__fmul_rn(sc_v, (float)nib), m_v);
+    } else {
+        int half_i = j >> 7, pos = j & 127, quad = pos >> 5, l = pos & 31;
+        const uint8_t *ql = blk + 64 * half_i, *qh = blk + 128 + 32 * half_i;
+        uint32_t nib = (ql[(quad & 1) ? l + 32 : l] >> (quad < 2 ? 0 : 4)) & 0x0Fu;
+        uint32_t hb = (qh[l] >> (2 * quad)) & 3u;
+        int q = (int)(nib | (hb << 4)) - 32;
+        float d = half_bits_to_f32((uint16_t)ld_u16(blk + 208));
+        int sc = (int)(int8_t)blk[192 + 8 * half_i + 2 * quad + (l >> 4)];
+        return __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
+    }
+}
+
+// AWQ: slot (0..7) inside a packed word that holds out column `col` of the word.
+// Columns {0,2,4,6} sit in slots {0,1,2,3}, columns {1,3,5,7} in slots {4,5,6,7}.
+__device__ __forceinline__ int awq_slot_of_col(int col) { return (col >> 1) + ((col & 1) << 2); }
+
+#endif // __CUDACC__
+
+} // namespace oxq
