@@ -274,6 +274,303 @@ __global__ void __launch_bounds__(NW * 32, 1) awq_gemv_kernel(const AwqGemvParam
     (void)NACC;
 }
 
+
+// ---------------------------------------------------------------------------
+// Main variant: slices aligned to quantization groups, weights streamed straight
+// into registers.
+//
+// A CTA is KW warps on the SAME 8*V packed words (64*V out columns), each warp
+// on its own contiguous k slice; a cluster of R such CTAs covers all of k.
+// A slice is either a whole number of groups or a divisor of one group, so the
+// scale/zero fold happens at most once per group into running f32 totals.
+// Weights go from HBM to registers with streaming vector loads issued D steps
+// ahead (plain loads sustain the stream; lane-private cp.async measured about
+// half the rate). The CTA's slice of x is staged once in shared memory.
+// The integer pipe is the scarce resource here (one op per weight at half
+// issue rate), so the nibble-to-bf16 step is written as explicit three-input
+// lop3 instructions. Partials meet in (distributed) shared memory and every
+// valid output is summed by one thread of the cluster in ascending k order.
+constexpr int GK_KW = 4;
+
+template <int V> __device__ __forceinline__ void ld_stream(uint32_t (&dst)[V], const uint32_t *p)
+{
+    if (V == 1) dst[0] = __ldcs(p);
+    else if (V == 2) { const uint2 t = __ldcs(reinterpret_cast<const uint2 *>(p)); dst[0] = t.x; dst[V - 1] = t.y; }
+    else { const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(p)); dst[0] = t.x; dst[1 % V] = t.y; dst[2 % V] = t.z; dst[3 % V] = t.w; }
+}
+
+// (p & mask) | magic in one instruction (lut 0xEA = (a & b) | c). Mask 0x000F000F and magic
+// 0x43004300 are passed in registers: a LOP3 encodes a single immediate, so with two literals the
+// compiler re-materialises one of them with an extra move in front of every use.
+__device__ __forceinline__ uint32_t nib_lo(uint32_t p, uint32_t mask, uint32_t magic)
+{
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(p), "r"(mask), "r"(magic));
+    return r;
+}
+__device__ __forceinline__ uint32_t nib_hi(uint32_t p, uint32_t mask, uint32_t magic)
+{
+    return nib_lo(p >> 4, mask, magic);
+}
+
+template <int MT, int V, int D, int MINB>
+__global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const AwqGemvParams p)
+{
+    constexpr int KW = GK_KW;
+    constexpr int NACC = V * 4 * MT * 4;
+    extern __shared__ __align__(16) unsigned char smem[];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int rank = blockIdx.y, nranks = gridDim.y;
+    const int jtile = blockIdx.x * 8 * V;
+    const int jbase = jtile + g * V;
+    const bool j_ok = jbase < p.packed_out;
+    const int steps = p.steps_per_cta; // 16-row steps per warp slice, identical for all slices
+    const int gsteps = p.group_size >> 4;
+    uint32_t kmask, kmagic; // opaque to constant propagation so that they stay in registers
+    asm volatile("mov.b32 %0, 0x000F000F;\n\tmov.b32 %1, 0x43004300;" : "=r"(kmask), "=r"(kmagic));
+    const int kr = KW * steps * 16;    // k range of this CTA
+    const int k_cta = rank * kr;
+    const int step_beg = (rank * KW + warp) * steps;
+
+    // First weights on their way before anything else. Lanes past the last word re-read word 0
+    // (their results are never stored).
+    const size_t row_stride = (size_t)p.packed_out;
+    const uint32_t *wsrc = p.qweight + (size_t)(step_beg * 16 + 4 * c) * row_stride + (j_ok ? jbase : 0);
+    uint32_t buf[D][4][V];
+#pragma unroll
+    for (int d = 0; d < D; d++)
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (d < steps) ld_stream<V>(buf[d][i], wsrc + (size_t)(16 * d + i) * row_stride);
+
+    // x[0 .. 8*MT) x [k_cta, k_cta + kr) -> shared memory, rows padded by 32 bytes so that the
+    // 8-byte fragment reads of a half warp (4 rows x 32 bytes) fall into distinct banks.
+    const int xrow = kr + 16; // elements
+    __nv_bfloat16 *xs = reinterpret_cast<__nv_bfloat16 *>(smem);
+    {
+        const int chunks_per_row = kr >> 3; // 16-byte chunks
+        for (int idx = tid; idx < 8 * MT * chunks_per_row; idx += KW * 32) {
+            const int row = idx / chunks_per_row, ch = idx % chunks_per_row;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (row < p.m) val = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)row * p.k + k_cta) + ch);
+            *reinterpret_cast<uint4 *>(xs + (size_t)row * xrow + ch * 8) = val;
+        }
+    }
+
+    // Zero points and scales of the slice's first group (16-bit scales ride in registers).
+    const bool sc16 = p.scales_dtype != OXQ_F32;
+    const bool is_f16 = p.scales_dtype == OXQ_F16;
+    uint32_t zw[V], sraw[V][4];
+    auto fetch_group = [&](int grp) {
+#pragma unroll
+        for (int v = 0; v < V; v++) {
+            zw[v] = j_ok ? __ldg(p.qzeros + (size_t)grp * p.packed_out + jbase + v) : 0u;
+            uint4 r = make_uint4(0u, 0u, 0u, 0u);
+            if (j_ok && sc16)
+                r = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.scales) +
+                                                          (size_t)grp * p.n + (size_t)(jbase + v) * 8));
+            sraw[v][0] = r.x; sraw[v][1] = r.y; sraw[v][2] = r.z; sraw[v][3] = r.w;
+        }
+    };
+    int grp = (step_beg * 16) / p.group_size;
+    fetch_group(grp);
+    __syncthreads();
+
+    float acc[V][4][MT][4], tot[V][4][MT][4], sx[MT][4];
+#pragma unroll
+    for (int v = 0; v < V; v++)
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[v][t][mt][e] = tot[v][t][mt][e] = 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) sx[mt][e] = 0.0f;
+
+    // tot += s * acc - (s * (128 + z)) * sum_x for the group that just ended; acc, sum_x restart.
+    auto fold = [&]() {
+#pragma unroll
+        for (int v = 0; v < V; v++)
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                float s0, s1;
+                if (sc16) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&sraw[v][t]));
+                    const float b0 = __uint_as_float(sraw[v][t] << 16), b1 = __uint_as_float(sraw[v][t] & 0xFFFF0000u);
+                    s0 = is_f16 ? f.x : b0;
+                    s1 = is_f16 ? f.y : b1;
+                } else {
+                    const size_t n0 = (size_t)(jbase + v) * 8 + 2 * t;
+                    s0 = j_ok ? reinterpret_cast<const float *>(p.scales)[(size_t)grp * p.n + n0] : 0.0f;
+                    s1 = j_ok ? reinterpret_cast<const float *>(p.scales)[(size_t)grp * p.n + n0 + 1] : 0.0f;
+                }
+                // (128 + z) of slots t and t+4 as two bf16 -> two f32 by shifting
+                const uint32_t zz = nib_lo(zw[v] >> (4 * t), kmask, kmagic);
+                const float u0 = s0 * __uint_as_float(zz << 16), u1 = s1 * __uint_as_float(zz & 0xFFFF0000u);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    float(&a4)[4] = acc[v][t][mt];
+                    float(&t4)[4] = tot[v][t][mt];
+                    t4[0] = fmaf(s0, a4[0], fmaf(-u0, sx[mt][0], t4[0]));
+                    t4[1] = fmaf(s0, a4[1], fmaf(-u0, sx[mt][1], t4[1]));
+                    t4[2] = fmaf(s1, a4[2], fmaf(-u1, sx[mt][0], t4[2]));
+                    t4[3] = fmaf(s1, a4[3], fmaf(-u1, sx[mt][1], t4[3]));
+                    a4[0] = a4[1] = a4[2] = a4[3] = 0.0f;
+                }
+            }
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) sx[mt][0] = sx[mt][1] = sx[mt][2] = sx[mt][3] = 0.0f;
+    };
+
+    const uint32_t ones[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};
+    const __nv_bfloat16 *xw = xs + (size_t)g * xrow + warp * steps * 16 + 4 * c;
+    int to_fold = min(steps, gsteps - (step_beg % gsteps)); // steps left in the current group
+
+    for (int s0 = 0; s0 < steps; s0 += D) {
+#pragma unroll
+        for (int d = 0; d < D; d++) {
+            const int s = s0 + d;
+            if (s < steps) {
+                uint32_t w[4][V], xb[MT][2];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int v = 0; v < V; v++) w[i][v] = buf[d][i][v];
+                if (s + D < steps) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) ld_stream<V>(buf[d][i], wsrc + (size_t)(16 * (s + D) + i) * row_stride);
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    const uint2 t2 = *reinterpret_cast<const uint2 *>(xw + (size_t)8 * mt * xrow + s * 16);
+                    xb[mt][0] = t2.x; xb[mt][1] = t2.y;
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) mma_bf16_16816(sx[mt], ones, xb[mt]);
+#pragma unroll
+                for (int v = 0; v < V; v++) {
+                    // rows (4c, 4c+1) -> first k pair, rows (4c+2, 4c+3) -> second k pair
+                    const uint32_t pa[4] = {gather_byte<0>(w[0][v], w[1][v]), gather_byte<1>(w[0][v], w[1][v]),
+                                            gather_byte<2>(w[0][v], w[1][v]), gather_byte<3>(w[0][v], w[1][v])};
+                    const uint32_t pb[4] = {gather_byte<0>(w[2][v], w[3][v]), gather_byte<1>(w[2][v], w[3][v]),
+                                            gather_byte<2>(w[2][v], w[3][v]), gather_byte<3>(w[2][v], w[3][v])};
+#pragma unroll
+                    for (int t = 0; t < 4; t++) {
+                        // tile t: MMA row g = column 2t of the word (slot t), row g+8 = column 2t+1 (slot t+4)
+                        uint32_t a[4];
+                        if (t & 1) {
+                            a[0] = nib_hi(pa[t >> 1], kmask, kmagic); a[1] = nib_hi(pa[2 + (t >> 1)], kmask, kmagic);
+                            a[2] = nib_hi(pb[t >> 1], kmask, kmagic); a[3] = nib_hi(pb[2 + (t >> 1)], kmask, kmagic);
+                        } else {
+                            a[0] = nib_lo(pa[t >> 1], kmask, kmagic); a[1] = nib_lo(pa[2 + (t >> 1)], kmask, kmagic);
+                            a[2] = nib_lo(pb[t >> 1], kmask, kmagic); a[3] = nib_lo(pb[2 + (t >> 1)], kmask, kmagic);
+                        }
+#pragma unroll
+                        for (int mt = 0; mt < MT; mt++) mma_bf16_16816(acc[v][t][mt], a, xb[mt]);
+                    }
+                }
+                if (--to_fold == 0) {
+                    fold();
+                    if (s + 1 < steps) {
+                        grp += 1;
+                        fetch_group(grp);
+                        to_fold = min(gsteps, steps - s - 1);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads(); // x is no longer needed: the partials reuse its shared memory
+
+    // The four totals of one MMA tile go out as one 16-byte store to red[warp][tile][lane].
+    float4 *red = reinterpret_cast<float4 *>(smem);
+    if (2 * c < p.m) { // otherwise this lane holds no valid token in any 8-token tile
+#pragma unroll
+        for (int v = 0; v < V; v++)
+#pragma unroll
+            for (int t = 0; t < 4; t++)
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+                    if (8 * mt + 2 * c < p.m) {
+                        const float(&t4)[4] = tot[v][t][mt];
+                        red[((size_t)warp * (NACC / 4) + (v * 4 + t) * MT + mt) * 32 + lane] =
+                            make_float4(t4[0], t4[1], t4[2], t4[3]);
+                    }
+    }
+
+    cg::cluster_group cluster = cg::this_cluster();
+    if (nranks > 1) cluster.sync(); else __syncthreads();
+
+    // Every tile slot (tile, lane) that holds a real token is summed by one thread of the cluster
+    // over the KW * R slices in ascending k order (bank-conflict-free: lane-minor, 16-byte loads).
+    const int cluster_threads = nranks * KW * 32;
+    for (int o = rank * KW * 32 + tid; o < (NACC / 4) * 32; o += cluster_threads) {
+        const int tile = o >> 5, ol = o & 31;
+        // tile = (v*4 + t)*MT + mt; components: token 8mt + 2c + {0,1}, out column 8(word) + 2t + {0,1}
+        const int mt = tile % MT, vt = tile / MT, t = vt & 3, v = vt >> 2;
+        const int og = ol >> 2, oc = ol & 3;
+        const int word = jtile + og * V + v;
+        const int row = 8 * mt + 2 * oc;
+        if (word < p.packed_out && row < p.m) {
+            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int q = 0; q < nranks; q++) {
+                const float4 *src = nranks > 1 ? cluster.map_shared_rank(red, q) : red;
+#pragma unroll
+                for (int ks = 0; ks < KW; ks++) {
+                    const float4 pv = src[((size_t)ks * (NACC / 4) + tile) * 32 + ol];
+                    sum.x += pv.x; sum.y += pv.y; sum.z += pv.z; sum.w += pv.w;
+                }
+            }
+            const size_t col = (size_t)word * 8 + 2 * t;
+            float b0 = 0.0f, b1 = 0.0f;
+            if (p.bias) { b0 = load_as_f32(p.bias, p.bias_dtype, col); b1 = load_as_f32(p.bias, p.bias_dtype, col + 1); }
+            store_as(p.y, p.y_dtype, (size_t)row * p.n + col, sum.x + b0);
+            store_as(p.y, p.y_dtype, (size_t)row * p.n + col + 1, sum.z + b1);
+            if (row + 1 < p.m) {
+                store_as(p.y, p.y_dtype, (size_t)(row + 1) * p.n + col, sum.y + b0);
+                store_as(p.y, p.y_dtype, (size_t)(row + 1) * p.n + col + 1, sum.w + b1);
+            }
+        }
+    }
+    if (nranks > 1) cluster.sync();
+}
+
+template <int MT, int V, int D, int MINB>
+static int launch_awq_gemv_group(const AwqGemvParams &p, int nranks, cudaStream_t stream)
+{
+    constexpr int NACC = V * 4 * MT * 4;
+    const size_t xbytes = (size_t)8 * MT * (GK_KW * p.steps_per_cta * 16 + 16) * sizeof(__nv_bfloat16);
+    const size_t red = (size_t)GK_KW * NACC * 32 * sizeof(float);
+    const size_t smem = xbytes > red ? xbytes : red;
+    auto kern = awq_gemv_group_kernel<MT, V, D, MINB>;
+    static size_t configured[64] = {};
+    int device = 0;
+    OXQ_CUDA(cudaGetDevice(&device));
+    if (device >= 64 || configured[device] < smem) {
+        OXQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (device < 64) configured[device] = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ceil_div(p.packed_out, 8 * V), nranks, 1);
+    cfg.blockDim = dim3(GK_KW * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = nranks;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    OXQ_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+    return OXQ_OK;
+}
+
 template <int MT, int V, int NW>
 static int launch_awq_gemv(const AwqGemvParams &p, int ksplit, cudaStream_t stream)
 {
@@ -347,6 +644,44 @@ OXQ_EXPORT int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight,
     if (p.packed_out % v != 0) v = 1;
     constexpr int NW = 4;
     const int total_steps = k / 16;
+    cudaStream_t st = (cudaStream_t)stream;
+
+    // Main path: contiguous k slices, 4 warps x R CTAs, each slice a whole number of groups or a
+    // divisor of one group; R is chosen for about 2000 warps in flight (13 per SM).
+    {
+        const int fv_default = mt == 1 ? 2 : 1;
+        int fv = fv_default;
+        while (fv > 1 && p.packed_out % fv != 0) fv /= 2;
+        int r_force = 0;
+        bool ok = aligned(scales, 16);
+        if (const char *env = getenv("OXQ_AWQ_GEMV_FAST")) { // bench-harness knob: "0" disables, else "V[,R]"
+            int ev = 0, er = 0;
+            const int got = sscanf(env, "%d,%d", &ev, &er);
+            if (got >= 1 && ev == 0) ok = false;
+            if (got >= 1 && (ev == 1 || ev == 2 || ev == 4) && p.packed_out % ev == 0 && 16 * ev * mt <= 64) fv = ev;
+            if (got >= 2 && (er == 1 || er == 2 || er == 4 || er == 8)) r_force = er;
+        }
+        const int gsteps = group_size / 16;
+        const int n_tiles = ceil_div(p.packed_out, 8 * fv);
+        int r = 0;
+        for (int cand : {8, 4, 2, 1}) {
+            if (total_steps % (GK_KW * cand) != 0) continue;
+            const int sl = total_steps / (GK_KW * cand);
+            if (!(sl % gsteps == 0 || gsteps % sl == 0)) continue;
+            if ((size_t)8 * mt * (GK_KW * sl * 16 + 16) * 2 > 160 * 1024) continue;
+            if (r_force ? cand == r_force : (r == 0 || n_tiles * GK_KW * cand >= 1700)) r = cand;
+        }
+        if (ok && r != 0 && (mt == 1 || getenv("OXQ_AWQ_GEMV_FAST"))) { // measured: the ring kernel below is faster for m > 8
+            p.steps_per_cta = total_steps / (GK_KW * r);
+            if (mt == 1 && fv == 4) return launch_awq_gemv_group<1, 4, 2, 2>(p, r, st);
+            if (mt == 1 && fv == 2) return launch_awq_gemv_group<1, 2, 4, 4>(p, r, st);
+            if (mt == 1 && fv == 1) return launch_awq_gemv_group<1, 1, 4, 4>(p, r, st);
+            if (mt == 2 && fv == 2) return launch_awq_gemv_group<2, 2, 2, 2>(p, r, st);
+            if (mt == 2 && fv == 1) return launch_awq_gemv_group<2, 1, 4, 4>(p, r, st);
+            if (mt == 4 && fv == 1) return launch_awq_gemv_group<4, 1, 4, 2>(p, r, st);
+        }
+    }
+
     // Enough CTAs for about two per SM; the k split is the cluster size (portable maximum 8).
     const int n_tiles = ceil_div(p.packed_out, 8 * v * NW);
     int ksplit = 1;
@@ -359,7 +694,6 @@ OXQ_EXPORT int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight,
         }
     }
     p.steps_per_cta = ceil_div(total_steps, ksplit);
-    cudaStream_t st = (cudaStream_t)stream;
     if (mt == 1 && v == 1) return launch_awq_gemv<1, 1, NW>(p, ksplit, st);
     if (mt == 1 && v == 2) return launch_awq_gemv<1, 2, NW>(p, ksplit, st);
     if (mt == 1 && v == 4) return launch_awq_gemv<1, 4, NW>(p, ksplit, st);
