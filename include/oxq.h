@@ -111,6 +111,46 @@ int oxq_mxfp4_dequant(const uint8_t *blocks, const uint8_t *scales, void *w_out,
 int oxq_mxfp4_gemv(const void *x, int x_dtype, const uint8_t *blocks, const uint8_t *scales, const void *bias,
                    int bias_dtype, void *y, int y_dtype, int m, int k, int n, void *stream);
 
+/* ------------------------------------------------- prefill-sized matmuls
+ * m > 32 (any m >= 1 is accepted): weight rows are dequantized in slabs into
+ * `workspace` by the bit-exact kernels above and contracted on the tensor
+ * cores (tcgen05, TMEM accumulators, TMA-fed operands), bf16 x bf16 -> f32.
+ * `workspace` is caller-owned DEVICE memory, 256-byte aligned, of at least
+ * oxq_gemm_workspace_bytes(n, k) bytes; its first word is a flag that a
+ * kernel sets if one of its bounded waits ran out (see oxq_gemm_check).
+ * Calls sharing a workspace must be stream-ordered. */
+
+size_t oxq_gemm_workspace_bytes(int n, int k);
+
+/* Synchronises `stream`, reads the flag word of `workspace` and returns
+ * OXQ_ERR_DEVICE_FLAG if a tensor-core kernel gave up on a wait. */
+int oxq_gemm_check(const void *workspace, void *stream);
+
+/* PackedQuantLinear::forward prefill branch: maybe_mpp_quant_matmul, else
+ * dequantize_w4 + matmul (linear.rs:494-524, metal_ops.rs:2771-2797). */
+int oxq_awq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
+                 int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+                 int group_size, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Same branch for GPTQ-packed weights (dequantize_gptq_packed + matmul, linear.rs:509-520). */
+int oxq_gptq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
+                  int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+                  int group_size, int bits, int sym, void *workspace, size_t workspace_bytes, void *stream);
+
+/* QLinear::forward prefill branch: gguf_quant_mul_mm (linear.rs:268-285, metal_ops.rs:5973). */
+int oxq_gguf_gemm(int ggml_type, const void *x, int x_dtype, const void *blocks, const void *bias, int bias_dtype,
+                  void *y, int y_dtype, int m, int k, int n, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Fp8Linear::forward for m beyond the GEMV range (linear.rs:96-145). */
+int oxq_fp8_gemm(const void *x, int x_dtype, const uint8_t *weight, const float *scale_inv, int s_out, int s_in,
+                 const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, void *workspace,
+                 size_t workspace_bytes, void *stream);
+
+/* Mxfp4Linear::forward mul_mm branch (metal_ops.rs:6204-6222). */
+int oxq_mxfp4_gemm(const void *x, int x_dtype, const uint8_t *blocks, const uint8_t *scales, const void *bias,
+                   int bias_dtype, void *y, int y_dtype, int m, int k, int n, void *workspace, size_t workspace_bytes,
+                   void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -28,8 +28,16 @@ SIGNATURES = {
     "oxq_fp8_gemv": [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "oxq_mxfp4_dequant": [_vp, _vp, _vp, _i, _i, _i, _vp],
     "oxq_mxfp4_gemv": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
+    "oxq_gemm_workspace_bytes": [_i, _i],
+    "oxq_gemm_check": [_vp, _vp],
+    "oxq_awq_gemm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp],
+    "oxq_gptq_gemm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp],
+    "oxq_gguf_gemm": [_i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp],
+    "oxq_fp8_gemm": [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp],
+    "oxq_mxfp4_gemm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp],
 }
-_RESTYPE = {"oxq_status_string": ctypes.c_char_p, "oxq_last_error": ctypes.c_char_p}
+_RESTYPE = {"oxq_status_string": ctypes.c_char_p, "oxq_last_error": ctypes.c_char_p,
+            "oxq_gemm_workspace_bytes": ctypes.c_size_t}
 
 _lib = None
 

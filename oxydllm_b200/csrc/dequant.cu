@@ -16,10 +16,11 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
 awq_dequant_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict__ qzeros,
                    const void *__restrict__ scales, int scales_dtype, OutT *__restrict__ w_out, int k, int n,
-                   int group_size)
+                   int group_size, int n_full, int n_off)
 {
+    // Output rows are out columns [n_off, n_off + n) of a layer with n_full columns (n_off % 8 == 0).
     __shared__ float tile[64][AWQ_TK + 1];
-    const int packed_out = n >> 3;
+    const int packed_out = n >> 3, packed_full = n_full >> 3, jw_off = n_off >> 3;
     const int k0 = blockIdx.y * AWQ_TK;
     const int jw0 = blockIdx.x * 8;
     const int t = threadIdx.x;
@@ -29,13 +30,13 @@ awq_dequant_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restr
         const int kk = k0 + r;
         if (kk < k && jw < packed_out) {
             const int g = kk / group_size;
-            const uint32_t w = qweight[(size_t)kk * packed_out + jw];
-            const uint32_t z = qzeros[(size_t)g * packed_out + jw];
+            const uint32_t w = qweight[(size_t)kk * packed_full + jw_off + jw];
+            const uint32_t z = qzeros[(size_t)g * packed_full + jw_off + jw];
 #pragma unroll
             for (int col = 0; col < 8; col++) {
                 const int sh = 4 * awq_slot_of_col(col);
                 const int q = (int)((w >> sh) & 0xFu) - (int)((z >> sh) & 0xFu);
-                const float s = load_as_f32(scales, scales_dtype, (size_t)g * n + (size_t)jw * 8 + col);
+                const float s = load_as_f32(scales, scales_dtype, (size_t)g * n_full + n_off + (size_t)jw * 8 + col);
                 tile[(t & 7) * 8 + col][r] = __fmul_rn((float)q, s);
             }
         }
@@ -55,20 +56,20 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
 gptq_dequant_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict__ qzeros,
                     const void *__restrict__ scales, int scales_dtype, OutT *__restrict__ w_out, int k, int n,
-                    int group_size, int bits, int sym)
+                    int group_size, int bits, int sym, int n_full, int n_off)
 {
     const int pf = 32 / bits;
     const uint32_t mask = (1u << bits) - 1u;
     const size_t total = (size_t)n * k;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
-        const int o = (int)(idx / k), i = (int)(idx % k);
+        const int o = n_off + (int)(idx / k), i = (int)(idx % k);
         const int g = i / group_size;
-        const uint32_t q = (qweight[(size_t)(i / pf) * n + o] >> ((i % pf) * bits)) & mask;
+        const uint32_t q = (qweight[(size_t)(i / pf) * n_full + o] >> ((i % pf) * bits)) & mask;
         uint32_t zero;
         if (sym) zero = (1u << (bits - 1)) - 1u;
-        else zero = (qzeros[(size_t)g * (n / pf) + o / pf] >> ((o % pf) * bits)) & mask;
-        const float s = load_as_f32(scales, scales_dtype, (size_t)g * n + o);
+        else zero = (qzeros[(size_t)g * (n_full / pf) + o / pf] >> ((o % pf) * bits)) & mask;
+        const float s = load_as_f32(scales, scales_dtype, (size_t)g * n_full + o);
         w_out[idx] = narrow<OutT>(__fmul_rn((float)((int)q - ((int)zero + 1)), s));
     }
 }
@@ -94,7 +95,7 @@ gguf_dequant_kernel(const uint8_t *__restrict__ blocks, OutT *__restrict__ w_out
 template <typename OutT>
 __global__ void __launch_bounds__(256)
 fp8_dequant_kernel(const uint8_t *__restrict__ weight, const float *__restrict__ scale_inv, int s_in, int block_out,
-                   int block_in, OutT *__restrict__ w_out, int n, int k)
+                   int block_in, OutT *__restrict__ w_out, int n, int k, int row_off)
 {
     const size_t total4 = (size_t)n * k / 4;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
@@ -105,7 +106,7 @@ fp8_dequant_kernel(const uint8_t *__restrict__ weight, const float *__restrict__
 #pragma unroll
         for (int u = 0; u < 4; u++) {
             float v = e4m3_to_f32((w >> (8 * u)) & 0xFFu);
-            if (scale_inv) v = __fmul_rn(scale_inv[(size_t)(r / block_out) * s_in + (c + u) / block_in], v);
+            if (scale_inv) v = __fmul_rn(scale_inv[(size_t)((row_off + r) / block_out) * s_in + (c + u) / block_in], v);
             w_out[e + u] = narrow<OutT>(v);
         }
     }
@@ -134,6 +135,67 @@ static int grid_for(size_t work_items, int block = 256)
     return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
+// ---- row-range (slab) dequantization to bf16 for the tensor-core GEMM -----------------------
+// Rows [n_off, n_off + n_cnt) of the dense [n, k] weight into a contiguous [n_cnt, k] bf16 buffer.
+int awq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                          __nv_bfloat16 *out, int k, int n_full, int group_size, int n_off, int n_cnt, cudaStream_t st)
+{
+    dim3 grid(ceil_div(n_cnt / 8, 8), ceil_div(k, AWQ_TK));
+    awq_dequant_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(qweight, qzeros, scales, scales_dtype, out, k, n_cnt,
+                                                             group_size, n_full, n_off);
+    OXQ_LAUNCH_CHECK("awq_dequant_kernel");
+    return OXQ_OK;
+}
+
+int gptq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                           __nv_bfloat16 *out, int k, int n_full, int group_size, int bits, int sym, int n_off,
+                           int n_cnt, cudaStream_t st)
+{
+    gptq_dequant_kernel<__nv_bfloat16><<<grid_for((size_t)n_cnt * k), 256, 0, st>>>(
+        qweight, qzeros, scales, scales_dtype, out, k, n_cnt, group_size, bits, sym, n_full, n_off);
+    OXQ_LAUNCH_CHECK("gptq_dequant_kernel");
+    return OXQ_OK;
+}
+
+int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *out, int k, int n_off, int n_cnt,
+                           cudaStream_t st)
+{
+    int bel, bby;
+    gguf_block_layout(ggml_type, bel, bby);
+    const uint8_t *b = blocks + (size_t)n_off * (k / bel) * bby;
+    const size_t total = (size_t)n_cnt * k;
+    const int grid = grid_for(total);
+    switch (ggml_type) {
+    case OXQ_GGML_Q4_0: gguf_dequant_kernel<OXQ_GGML_Q4_0, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
+    case OXQ_GGML_Q8_0: gguf_dequant_kernel<OXQ_GGML_Q8_0, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
+    case OXQ_GGML_Q4_K: gguf_dequant_kernel<OXQ_GGML_Q4_K, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
+    default: gguf_dequant_kernel<OXQ_GGML_Q6_K, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
+    }
+    OXQ_LAUNCH_CHECK("gguf_dequant_kernel");
+    return OXQ_OK;
+}
+
+int fp8_dequant_rows_bf16(const uint8_t *weight, const float *scale_inv, int s_in, int block_out, int block_in,
+                          __nv_bfloat16 *out, int k, int n_off, int n_cnt, cudaStream_t st)
+{
+    fp8_dequant_kernel<__nv_bfloat16><<<grid_for((size_t)n_cnt * k / 4), 256, 0, st>>>(
+        weight + (size_t)n_off * k, scale_inv, s_in, block_out, block_in, out, n_cnt, k, n_off);
+    OXQ_LAUNCH_CHECK("fp8_dequant_kernel");
+    return OXQ_OK;
+}
+
+bool gguf_block_layout_host(int ggml_type, int &bel, int &bby) { return gguf_block_layout(ggml_type, bel, bby); }
+
+int mxfp4_dequant_rows_bf16(const uint8_t *blocks, const uint8_t *scales, __nv_bfloat16 *out, int k, int n_off,
+                            int n_cnt, cudaStream_t st)
+{
+    const size_t total_bytes = (size_t)n_cnt * k / 2;
+    mxfp4_dequant_kernel<__nv_bfloat16><<<grid_for(total_bytes), 256, 0, st>>>(
+        blocks + (size_t)n_off * (k / 2), scales + (size_t)n_off * (k / 32), out, total_bytes);
+    OXQ_LAUNCH_CHECK("mxfp4_dequant_kernel");
+    return OXQ_OK;
+}
+
 } // namespace oxq
 
 using namespace oxq;
@@ -158,7 +220,7 @@ OXQ_EXPORT int oxq_awq_dequant(const uint32_t *qweight, const uint32_t *qzeros, 
                 "quant in_features (%d) not divisible by group size (%d)", k, group_size);
     dim3 grid(ceil_div(n / 8, 8), ceil_div(k, AWQ_TK));
     DISPATCH_OUT(out_dtype, awq_dequant_kernel<OutT><<<grid, 256, 0, (cudaStream_t)stream>>>(
-                                qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size));
+                                qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size, n, 0));
     OXQ_LAUNCH_CHECK("awq_dequant_kernel");
     return OXQ_OK;
 }
@@ -179,7 +241,7 @@ OXQ_EXPORT int oxq_gptq_dequant(const uint32_t *qweight, const uint32_t *qzeros,
                 "GPTQ in_features %d not divisible by pack_factor %d / group size %d", k, pf, group_size);
     const int use_sym = (sym != 0 || qzeros == nullptr) ? 1 : 0;
     DISPATCH_OUT(out_dtype, gptq_dequant_kernel<OutT><<<grid_for((size_t)n * k), 256, 0, (cudaStream_t)stream>>>(
-                                qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size, bits, use_sym));
+                                qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size, bits, use_sym, n, 0));
     OXQ_LAUNCH_CHECK("gptq_dequant_kernel");
     return OXQ_OK;
 }
@@ -234,7 +296,7 @@ OXQ_EXPORT int oxq_fp8_dequant(const uint8_t *weight, const float *scale_inv, in
         bi = k / s_in;
     }
     DISPATCH_OUT(out_dtype, fp8_dequant_kernel<OutT><<<grid_for((size_t)n * k / 4), 256, 0, (cudaStream_t)stream>>>(
-                                weight, scale_inv, s_in, bo, bi, (OutT *)w_out, n, k));
+                                weight, scale_inv, s_in, bo, bi, (OutT *)w_out, n, k, 0));
     OXQ_LAUNCH_CHECK("fp8_dequant_kernel");
     return OXQ_OK;
 }

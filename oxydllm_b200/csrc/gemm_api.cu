@@ -1,0 +1,190 @@
+// C-ABI entry points of the prefill-sized (m > 32) quantized matmuls: dequantize a slab of weight
+// rows into the caller's workspace (bit-exact kernels of dequant.cu), run the tcgen05 GEMM of
+// gemm_tc.cu on it, repeat. The slab (<= 32 MiB) is written and re-read while it is still in L2.
+#include "oxq_common.cuh"
+
+namespace oxq {
+int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int n,
+                 int k, int n_off, int ldy, int *flag, cudaStream_t stream);
+int awq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                          __nv_bfloat16 *out, int k, int n_full, int group_size, int n_off, int n_cnt, cudaStream_t st);
+int gptq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                           __nv_bfloat16 *out, int k, int n_full, int group_size, int bits, int sym, int n_off,
+                           int n_cnt, cudaStream_t st);
+int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *out, int k, int n_off, int n_cnt,
+                           cudaStream_t st);
+int fp8_dequant_rows_bf16(const uint8_t *weight, const float *scale_inv, int s_in, int block_out, int block_in,
+                          __nv_bfloat16 *out, int k, int n_off, int n_cnt, cudaStream_t st);
+int mxfp4_dequant_rows_bf16(const uint8_t *blocks, const uint8_t *scales, __nv_bfloat16 *out, int k, int n_off,
+                            int n_cnt, cudaStream_t st);
+bool gguf_block_layout_host(int ggml_type, int &bel, int &bby);
+
+constexpr size_t WS_HEADER = 256;               // flag word + padding, keeps the slab 256-byte aligned
+constexpr size_t SLAB_TARGET_BYTES = 32u << 20; // dequantized rows per GEMM launch
+
+static int slab_rows(int n, int k)
+{
+    long long rows = (long long)(SLAB_TARGET_BYTES / ((size_t)k * 2)) / 256 * 256;
+    if (rows < 256) rows = 256;
+    return rows >= n ? n : (int)rows;
+}
+
+struct GemmCommon {
+    const void *x, *bias;
+    void *y;
+    int bias_dtype, y_dtype, m, k, n;
+    int *flag;
+    __nv_bfloat16 *slab;
+    int rows;
+    cudaStream_t st;
+};
+
+static int prepare(const char *who, GemmCommon &c, const void *x, int x_dtype, const void *bias, int bias_dtype,
+                   void *y, int y_dtype, int m, int k, int n, void *workspace, size_t workspace_bytes, void *stream)
+{
+    OXQ_REQUIRE(x && y, OXQ_ERR_NULL, "%s: null pointer", who);
+    OXQ_REQUIRE(x_dtype == OXQ_BF16, OXQ_ERR_UNSUPPORTED, "%s: activations must be bf16", who);
+    OXQ_REQUIRE(valid_dtype(y_dtype) && (!bias || valid_dtype(bias_dtype)), OXQ_ERR_UNSUPPORTED, "%s: unsupported dtype", who);
+    OXQ_REQUIRE(m >= 1 && k > 0 && n > 0, OXQ_ERR_BAD_SHAPE, "%s: non-positive size", who);
+    OXQ_REQUIRE(k % 8 == 0, OXQ_ERR_UNSUPPORTED, "%s: in_features (%d) must be a multiple of 8", who, k);
+    const size_t need = WS_HEADER + (size_t)slab_rows(n, k) * k * 2;
+    OXQ_REQUIRE(workspace != nullptr && workspace_bytes >= need, OXQ_ERR_WORKSPACE,
+                "%s: workspace of %zu bytes needed, got %zu", who, need, workspace_bytes);
+    OXQ_REQUIRE(aligned(workspace, 256), OXQ_ERR_BAD_ALIGN, "%s: workspace must be 256-byte aligned", who);
+    c.x = x; c.bias = bias; c.y = y; c.bias_dtype = bias_dtype; c.y_dtype = y_dtype; c.m = m; c.k = k; c.n = n;
+    c.flag = reinterpret_cast<int *>(workspace);
+    c.slab = reinterpret_cast<__nv_bfloat16 *>(reinterpret_cast<unsigned char *>(workspace) + WS_HEADER);
+    c.rows = slab_rows(n, k);
+    c.st = (cudaStream_t)stream;
+    OXQ_CUDA(cudaMemsetAsync(c.flag, 0, sizeof(int), c.st));
+    return OXQ_OK;
+}
+
+template <typename Dequant> static int run_slabs(const GemmCommon &c, Dequant dequant)
+{
+    for (int n_off = 0; n_off < c.n; n_off += c.rows) {
+        const int cnt = c.n - n_off < c.rows ? c.n - n_off : c.rows;
+        int rc = dequant(n_off, cnt);
+        if (rc) return rc;
+        rc = gemm_bf16_tn(c.x, c.slab, c.bias, c.bias_dtype, c.y, c.y_dtype, c.m, cnt, c.k, n_off, c.n, c.flag, c.st);
+        if (rc) return rc;
+    }
+    return OXQ_OK;
+}
+
+} // namespace oxq
+
+using namespace oxq;
+
+OXQ_EXPORT size_t oxq_gemm_workspace_bytes(int n, int k)
+{
+    if (n <= 0 || k <= 0) return WS_HEADER;
+    return WS_HEADER + (size_t)slab_rows(n, k) * k * 2;
+}
+
+OXQ_EXPORT int oxq_gemm_check(const void *workspace, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(workspace, OXQ_ERR_NULL, "oxq_gemm_check: null workspace");
+    int flag = 0;
+    OXQ_CUDA(cudaMemcpyAsync(&flag, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    OXQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    OXQ_REQUIRE(flag == 0, OXQ_ERR_DEVICE_FLAG, "tensor-core GEMM: bounded wait %d ran out (1 = ring slot, 2 = tile data, 3 = accumulator)", flag);
+    return OXQ_OK;
+}
+
+OXQ_EXPORT int oxq_awq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros,
+                            const void *scales, int scales_dtype, const void *bias, int bias_dtype, void *y,
+                            int y_dtype, int m, int k, int n, int group_size, void *workspace, size_t workspace_bytes,
+                            void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(qweight && qzeros && scales, OXQ_ERR_NULL, "oxq_awq_gemm: null pointer");
+    OXQ_REQUIRE(valid_dtype(scales_dtype), OXQ_ERR_UNSUPPORTED, "oxq_awq_gemm: unsupported scales dtype");
+    OXQ_REQUIRE(group_size > 0 && n % 8 == 0 && k % group_size == 0, OXQ_ERR_BAD_SHAPE,
+                "oxq_awq_gemm: out_features %d must be a multiple of 8 and in_features %d a multiple of the group size %d",
+                n, k, group_size);
+    GemmCommon c;
+    int rc = prepare("oxq_awq_gemm", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n, workspace, workspace_bytes, stream);
+    if (rc) return rc;
+    return run_slabs(c, [&](int n_off, int cnt) {
+        return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, n_off, cnt, c.st);
+    });
+}
+
+OXQ_EXPORT int oxq_gptq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros,
+                             const void *scales, int scales_dtype, const void *bias, int bias_dtype, void *y,
+                             int y_dtype, int m, int k, int n, int group_size, int bits, int sym, void *workspace,
+                             size_t workspace_bytes, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(qweight && scales, OXQ_ERR_NULL, "oxq_gptq_gemm: null pointer");
+    OXQ_REQUIRE(valid_dtype(scales_dtype), OXQ_ERR_UNSUPPORTED, "oxq_gptq_gemm: unsupported scales dtype");
+    OXQ_REQUIRE(bits == 4 || bits == 8, OXQ_ERR_UNSUPPORTED, "dequantize_gptq: only 4/8-bit supported, got %d", bits);
+    const int pf = 32 / bits;
+    OXQ_REQUIRE(group_size > 0 && n % pf == 0 && k % pf == 0 && k % group_size == 0, OXQ_ERR_BAD_SHAPE,
+                "oxq_gptq_gemm: shape [%d, %d] incompatible with pack factor %d / group size %d", n, k, pf, group_size);
+    const int use_sym = (sym != 0 || qzeros == nullptr) ? 1 : 0;
+    GemmCommon c;
+    int rc = prepare("oxq_gptq_gemm", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n, workspace, workspace_bytes, stream);
+    if (rc) return rc;
+    return run_slabs(c, [&](int n_off, int cnt) {
+        return gptq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, bits, use_sym,
+                                      n_off, cnt, c.st);
+    });
+}
+
+OXQ_EXPORT int oxq_gguf_gemm(int ggml_type, const void *x, int x_dtype, const void *blocks, const void *bias,
+                             int bias_dtype, void *y, int y_dtype, int m, int k, int n, void *workspace,
+                             size_t workspace_bytes, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(blocks, OXQ_ERR_NULL, "oxq_gguf_gemm: null pointer");
+    int bel, bby;
+    OXQ_REQUIRE(gguf_block_layout_host(ggml_type, bel, bby), OXQ_ERR_UNSUPPORTED, "unsupported GGML type %d", ggml_type);
+    OXQ_REQUIRE(k > 0 && k % bel == 0, OXQ_ERR_BAD_SHAPE, "GGUF in_features %d is not a multiple of the block size %d", k, bel);
+    OXQ_REQUIRE(aligned(blocks, 2), OXQ_ERR_BAD_ALIGN, "GGUF blocks must be 2-byte aligned");
+    GemmCommon c;
+    int rc = prepare("oxq_gguf_gemm", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n, workspace, workspace_bytes, stream);
+    if (rc) return rc;
+    return run_slabs(c, [&](int n_off, int cnt) {
+        return gguf_dequant_rows_bf16(ggml_type, (const uint8_t *)blocks, c.slab, k, n_off, cnt, c.st);
+    });
+}
+
+OXQ_EXPORT int oxq_fp8_gemm(const void *x, int x_dtype, const uint8_t *weight, const float *scale_inv, int s_out,
+                            int s_in, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+                            void *workspace, size_t workspace_bytes, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(weight, OXQ_ERR_NULL, "oxq_fp8_gemm: null pointer");
+    OXQ_REQUIRE(aligned(weight, 4), OXQ_ERR_BAD_ALIGN, "FP8 weight must be 4-byte aligned");
+    int bo = n > 0 ? n : 1, bi = k > 0 ? k : 1;
+    if (scale_inv) {
+        OXQ_REQUIRE(s_out > 0 && s_in > 0 && n % s_out == 0 && k % s_in == 0, OXQ_ERR_BAD_SHAPE,
+                    "block-wise FP8 weight_scale_inv [%d, %d] does not tile weight [%d, %d] evenly", s_out, s_in, n, k);
+        bo = n / s_out;
+        bi = k / s_in;
+    }
+    GemmCommon c;
+    int rc = prepare("oxq_fp8_gemm", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n, workspace, workspace_bytes, stream);
+    if (rc) return rc;
+    return run_slabs(c, [&](int n_off, int cnt) {
+        return fp8_dequant_rows_bf16(weight, scale_inv, scale_inv ? s_in : 1, bo, bi, c.slab, k, n_off, cnt, c.st);
+    });
+}
+
+OXQ_EXPORT int oxq_mxfp4_gemm(const void *x, int x_dtype, const uint8_t *blocks, const uint8_t *scales,
+                              const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+                              void *workspace, size_t workspace_bytes, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(blocks && scales, OXQ_ERR_NULL, "oxq_mxfp4_gemm: null pointer");
+    OXQ_REQUIRE(k > 0 && k % 32 == 0, OXQ_ERR_BAD_SHAPE, "MXFP4: cols %d must be a multiple of 32", k);
+    GemmCommon c;
+    int rc = prepare("oxq_mxfp4_gemm", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n, workspace, workspace_bytes, stream);
+    if (rc) return rc;
+    return run_slabs(c, [&](int n_off, int cnt) {
+        return mxfp4_dequant_rows_bf16(blocks, scales, c.slab, k, n_off, cnt, c.st);
+    });
+}

@@ -1,0 +1,338 @@
+// Prefill-sized matmuls on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+//   y[m, n] = x[m, k] . W[n, k]^T (+ bias),  x bf16, W bf16 (a dequantized slab), f32 accumulation
+//
+// One CTA computes a 128 x BN output tile (BN = 256). Warp-specialised:
+//   warp 0     TMA producer: x tile [128 x 64] and W tile [BN x 64] per k block, both K-major,
+//              128-byte swizzle, 4-stage ring guarded by full/empty mbarriers;
+//   warp 1     MMA issuer: one elected lane issues tcgen05.mma (cta_group::1, kind::f16, M=128,
+//              N=BN, K=16) on shared-memory descriptors, accumulator in TMEM (BN columns);
+//              tcgen05.commit releases ring slots and finally signals the epilogue;
+//   warps 2-5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, bias, narrowing, stores.
+// Every wait is bounded (wall-clock limit); on expiry the kernel records a code in the caller's
+// flag word, all roles fall through, TMEM is released and the kernel returns.
+//
+// The quantized entry points dequantize W in slabs of rows into the caller's workspace with the
+// bit-exact dequantization kernels and run this GEMM per slab: the B operand the tensor cores
+// see is exactly the dense weight the reference materialises (awq.rs:325-440, linear.rs:96-141).
+#include <cuda.h>
+
+#include "oxq_common.cuh"
+
+namespace oxq {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BN = 256;
+constexpr int TC_BK = 64;
+constexpr int TC_STAGES = 4;
+constexpr int TC_UMMA_K = 16;
+constexpr uint32_t TC_A_BYTES = TC_BM * TC_BK * 2;
+constexpr uint32_t TC_B_BYTES = TC_BN * TC_BK * 2;
+constexpr uint32_t TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr size_t TC_SMEM_BYTES = 1024 /* alignment slack */ + (size_t)TC_STAGES * TC_STAGE_BYTES + 256 /* barriers */;
+constexpr unsigned long long TC_WAIT_LIMIT_NS = 2000000000ull; // 2 s
+
+struct GemmParams {
+    const void *bias;
+    void *y;
+    int *flag;
+    int bias_dtype, y_dtype;
+    int m, n, k;      // n = rows of W in this call (a slab); y columns [n_off, n_off + n)
+    int n_off, ldy;   // ldy = full out_features
+};
+
+// ---- PTX wrappers ---------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false (and `code` recorded) when the barrier did not flip within the limit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *flag, int code)
+{
+    if (mbar_test(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; i++)
+            if (mbar_test(bar, parity)) return true;
+        if (global_ns() - t0 > TC_WAIT_LIMIT_NS) {
+            atomicCAS(flag, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 x bf16 -> f32.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// Arrive on an mbarrier once all tcgen05.mma issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row
+// groups 1024 bytes apart (SBO), descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr)
+{
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// Instruction descriptor: D f32, A and B bf16, both K-major, N and M of the instruction.
+__host__ __device__ constexpr uint32_t tc_idesc(int m, int n)
+{
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u; // swizzled tiles need 1024-byte alignment
+    unsigned char *base_ptr = smem_raw + (base - raw);
+    const uint32_t bars = base + TC_STAGES * TC_STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (TC_STAGES + s); };
+    const uint32_t tmem_full_bar = bars + 8u * (2 * TC_STAGES);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + TC_STAGES * TC_STAGE_BYTES + 8 * (2 * TC_STAGES + 1));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
+    const int k_iters = (p.k + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tmem_full_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) { // the allocating warp also frees
+        tmem_alloc(smem_u32(tmem_slot), TC_BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            for (int it = 0; it < k_iters; it++) {
+                const int s = it % TC_STAGES;
+                const uint32_t round = it / TC_STAGES;
+                if (!mbar_wait(empty_bar(s), (round & 1) ^ 1, p.flag, 1)) break;
+                mbar_arrive_expect_tx(full_bar(s), TC_STAGE_BYTES);
+                const uint32_t sa = base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                tma_load_2d(sa, &map_a, full_bar(s), it * TC_BK, m0);
+                tma_load_2d(sb, &map_b, full_bar(s), it * TC_BK, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc = tc_idesc(TC_BM, TC_BN);
+            bool ok = true;
+            for (int it = 0; it < k_iters && ok; it++) {
+                const int s = it % TC_STAGES;
+                const uint32_t round = it / TC_STAGES;
+                ok = mbar_wait(full_bar(s), round & 1, p.flag, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                const uint64_t da = kmajor_sw128_desc(sa), db = kmajor_sw128_desc(sb);
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / TC_UMMA_K; kk++) {
+                    // 16 bf16 along k = 32 bytes inside the 128-byte swizzled row: +2 in the address field
+                    umma_bf16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (it | kk) != 0);
+                }
+                umma_commit(empty_bar(s)); // slot reusable once these MMAs have read it
+            }
+            umma_commit(tmem_full_bar);    // accumulator complete (arrives even after an aborted loop)
+        }
+    } else {
+        // Epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 only.
+        const int quad = warp & 3;
+        const int row = m0 + quad * 32 + lane;
+        const bool done = mbar_wait(tmem_full_bar, 0, p.flag, 3);
+        tc_fence_after();
+        if (done) {
+            const bool vec_ok = p.y_dtype == OXQ_BF16 && (p.ldy % 8 == 0) && (p.n_off % 8 == 0) &&
+                                (reinterpret_cast<uintptr_t>(p.y) & 15) == 0;
+#pragma unroll 1
+            for (int cb = 0; cb < TC_BN / 32; cb++) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + cb * 32, r);
+                tmem_ld_wait();
+                const int col0 = n0 + cb * 32; // column inside this slab
+                if (row < p.m && col0 < p.n) {
+                    const size_t out = (size_t)row * p.ldy + p.n_off + col0;
+                    if (vec_ok && col0 + 32 <= p.n) {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
+                            if (p.bias) {
+                                v0 += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j);
+                                v1 += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j + 1);
+                            }
+                            __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                            packed[j] = *reinterpret_cast<uint32_t *>(&h);
+                        }
+                        uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.y) + out);
+#pragma unroll
+                        for (int q = 0; q < 4; q++)
+                            dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < p.n; j++) {
+                            float v = __uint_as_float(r[j]);
+                            if (p.bias) v += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + j);
+                            store_as(p.y, p.y_dtype, out + j, v);
+                        }
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TC_BN);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] tensor, box [box_rows, 64 cols], 128-byte swizzle, zero fill.
+static int make_map_bf16(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    OXQ_REQUIRE(fn != nullptr, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return OXQ_OK;
+}
+
+// y[:, n_off : n_off + n] = x[m, k] . w[n, k]^T (+ bias) with x, w bf16 row-major.
+int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int n,
+                 int k, int n_off, int ldy, int *flag, cudaStream_t stream)
+{
+    OXQ_REQUIRE(aligned(x, 16) && aligned(w, 16), OXQ_ERR_BAD_ALIGN, "tensor-core GEMM operands must be 16-byte aligned");
+    OXQ_REQUIRE(k % 8 == 0, OXQ_ERR_UNSUPPORTED, "tensor-core GEMM needs in_features %% 8 == 0 (got %d)", k);
+    CUtensorMap map_a, map_b;
+    int rc = make_map_bf16(&map_a, x, (uint64_t)m, (uint64_t)k, TC_BM);
+    if (rc) return rc;
+    rc = make_map_bf16(&map_b, w, (uint64_t)n, (uint64_t)k, TC_BN);
+    if (rc) return rc;
+    static bool configured[64] = {};
+    int device = 0;
+    OXQ_CUDA(cudaGetDevice(&device));
+    if (device >= 64 || !configured[device]) {
+        OXQ_CUDA(cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+        if (device < 64) configured[device] = true;
+    }
+    GemmParams p;
+    p.bias = bias; p.y = y; p.flag = flag; p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
+    p.m = m; p.n = n; p.k = k; p.n_off = n_off; p.ldy = ldy;
+    const dim3 grid(ceil_div(m, TC_BM), ceil_div(n, TC_BN));
+    gemm_bf16_tn_kernel<<<grid, 192, TC_SMEM_BYTES, stream>>>(map_a, map_b, p);
+    OXQ_LAUNCH_CHECK("gemm_bf16_tn_kernel");
+    return OXQ_OK;
+}
+
+} // namespace oxq

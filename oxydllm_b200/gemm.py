@@ -1,36 +1,82 @@
-"""Prefill-sized (m > 32) matmuls of the quantized linears.
+"""Prefill-sized (m > 32) matmuls of the quantized linears on the tensor cores.
 
-Until a format has a tensor-core GEMM entry point, batches are cut into
-decode-sized row chunks and run on the GEMV kernels, the same strategy as the
-reference's ``chunked_batch_gemv`` (linear.rs:458-480).
+Thin callers of the ``oxq_*_gemm`` entry points. The dequantization slab
+workspace is caller-owned device memory: one cached ``torch`` buffer per
+device and size, shared by stream-ordered calls.
 """
 from __future__ import annotations
 
-from .linear import GEMV_MAX_M
+import ctypes
+
+import torch
+
+from . import _lib
+
+_workspaces: dict = {}
 
 
-def _chunks(m: int):
-    for r in range(0, m, GEMV_MAX_M):
-        yield r, min(GEMV_MAX_M, m - r)
+def workspace_bytes(n: int, k: int) -> int:
+    return int(_lib.load().oxq_gemm_workspace_bytes(n, k))
+
+
+def workspace(n: int, k: int, device) -> torch.Tensor:
+    """A device buffer large enough for ``oxq_*_gemm`` on an ``[n, k]`` weight (grown on demand, reused)."""
+    need = workspace_bytes(n, k)
+    key = torch.device(device).index or 0
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.zeros(need, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def check(ws: torch.Tensor) -> None:
+    """Synchronise and raise if a tensor-core kernel recorded a timed-out wait in ``ws``."""
+    _lib.call("oxq_gemm_check", ctypes.c_void_p(ws.data_ptr()),
+              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+
+def _p(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _st():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _bias(b):
+    from .linear import _dt
+    return _p(b), (_dt(b.dtype) if b is not None else 0)
 
 
 def awq_matmul(lin, x2, y):
-    for r, rows in _chunks(x2.shape[0]):
-        lin._gemv(x2[r:r + rows], y[r:r + rows], rows)
-
-
-def _via_forward(lin, x2, y):
-    for r, rows in _chunks(x2.shape[0]):
-        y[r:r + rows] = lin.forward(x2[r:r + rows])
+    from .linear import _dt
+    ws = workspace(lin.out_features, lin.in_features, x2.device)
+    bp, bd = _bias(lin.bias)
+    _lib.call("oxq_awq_gemm", _p(x2), _dt(x2.dtype), _p(lin.qweight), _p(lin.qzeros), _p(lin.scales),
+              _dt(lin.scales.dtype), bp, bd, _p(y), _dt(y.dtype), x2.shape[0], lin.in_features, lin.out_features,
+              lin.group_size, _p(ws), ws.numel(), _st())
 
 
 def fp8_matmul(lin, s, s_out, s_in, x2, y):
-    _via_forward(lin, x2, y)
+    from .linear import _dt
+    ws = workspace(lin.out_features, lin.in_features, x2.device)
+    bp, bd = _bias(lin.bias)
+    _lib.call("oxq_fp8_gemm", _p(x2), _dt(x2.dtype), _p(lin.weight), _p(s), s_out, s_in, bp, bd, _p(y), _dt(y.dtype),
+              x2.shape[0], lin.in_features, lin.out_features, _p(ws), ws.numel(), _st())
 
 
 def gguf_matmul(lin, x2, y):
-    _via_forward(lin, x2, y)
+    from .linear import _dt
+    ws = workspace(lin.out_features, lin.in_features, x2.device)
+    bp, bd = _bias(lin.bias)
+    _lib.call("oxq_gguf_gemm", lin.ggml_type, _p(x2), _dt(x2.dtype), _p(lin.blocks), bp, bd, _p(y), _dt(y.dtype),
+              x2.shape[0], lin.in_features, lin.out_features, _p(ws), ws.numel(), _st())
 
 
 def mxfp4_matmul(lin, x2, y):
-    _via_forward(lin, x2, y)
+    from .linear import _dt
+    ws = workspace(lin.out_features, lin.in_features, x2.device)
+    bp, bd = _bias(lin.bias)
+    _lib.call("oxq_mxfp4_gemm", _p(x2), _dt(x2.dtype), _p(lin.blocks), _p(lin.scales), bp, bd, _p(y), _dt(y.dtype),
+              x2.shape[0], lin.in_features, lin.out_features, _p(ws), ws.numel(), _st())

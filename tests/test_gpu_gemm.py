@@ -1,0 +1,97 @@
+"""Tensor-core (tcgen05) prefill matmuls against the CPU oracle: y = x @ deq(W)^T in f32 with the
+weights first rounded to bf16 (what the tensor cores are fed; the reference's GPU paths round the
+dequantized weight to the activation dtype too, linear.rs:143, mpp_gemm.metal:143). Tolerance:
+max|err| <= 2e-2 * ||row||_inf."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oxydllm_b200 import formats as F
+from oxydllm_b200 import gemm
+from oxydllm_b200 import linear as L
+from oxydllm_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    return (t.to(dtype) if dtype is not None else t).cuda()
+
+
+def words(a):
+    return dev(a.view(np.int32))
+
+
+def check(y, ref, label):
+    gemm.check(gemm.workspace(1, 8, y.device))  # no bounded wait ran out
+    got = y.float().cpu().numpy()
+    assert np.isfinite(got).all(), f"{label}: non-finite"
+    err = np.abs(got - ref)
+    row_inf = np.abs(ref).max(axis=1, keepdims=True)
+    assert (err <= 2e-2 * row_inf + 1e-6).all(), f"{label}: max err {err.max()} row_inf {row_inf.max()}"
+
+
+@pytest.mark.parametrize("m,k,n,g", [(70, 192, 104, 64), (70, 160, 104, 32), (128, 256, 256, 128), (33, 64, 8, 64),
+                                     (300, 1024, 520, 128), (2048, 512, 768, 128)])
+def test_awq_gemm(cuda, m, k, n, g):
+    # (70,192,104,64), (70,160,104,32): partial tiles of metal_ops.rs:5004-5055
+    qw, qz, sc = synth.awq_layer(k, n, g, seed=m)
+    x = synth.activations(m, k, seed=m + 1)
+    bias = synth.bf16_round(np.random.default_rng(2).standard_normal(n).astype(np.float32))
+    ref = oracle.linear(x, oracle.round_bf16(oracle.awq_dequant(qw, qz, sc)), bias)
+    lin = L.PackedQuantLinear(L.QuantWeight.new_awq(4, words(qw), words(qz), dev(sc)), dev(bias, torch.bfloat16))
+    y = lin.forward(dev(x, torch.bfloat16))
+    assert y.shape == (m, n)
+    check(y, ref, f"awq gemm {m}x{k}x{n}")
+
+
+def test_awq_gemm_matches_gemv_rows(cuda):
+    k, n, g = 512, 512, 128
+    qw, qz, sc = synth.awq_layer(k, n, g, seed=3)
+    lin = L.PackedQuantLinear(L.QuantWeight.new_awq(4, words(qw), words(qz), dev(sc)))
+    x = dev(synth.activations(64, k, seed=4), torch.bfloat16)
+    big = lin.forward(x).float()
+    small = lin.forward(x[:8]).float()
+    assert torch.allclose(big[:8], small, rtol=2e-2, atol=2e-2 * float(small.abs().max()))
+
+
+@pytest.mark.parametrize("ggml_type", [F.GGML_Q4_0, F.GGML_Q8_0, F.GGML_Q4_K, F.GGML_Q6_K])
+@pytest.mark.parametrize("n,k,m", [(512, 2048, 33), (1001, 512, 70), (2048, 2048, 9 * 8)])
+def test_gguf_gemm(cuda, ggml_type, n, k, m):
+    # shapes/m of metal_ops.rs:6386-6470 (m in {33, 70}, odd n = 1001)
+    w = np.array([((i % 17) - 8) * 0.05 for i in range(n * k)], np.float32).reshape(n, k)
+    data = F.GGML_QUANTIZE[ggml_type](w)
+    x = synth.activations(m, k, seed=n)
+    ref = oracle.linear(x, oracle.round_bf16(oracle.gguf_dequant(ggml_type, data, n, k)))
+    y = L.QLinear(ggml_type, dev(data), n, k).forward(dev(x, torch.bfloat16))
+    check(y, ref, f"gguf gemm type={ggml_type}")
+
+
+@pytest.mark.parametrize("n,k,m", [(256, 1024, 64), (1792, 4096, 2048 // 8), (384, 128, 40)])
+def test_fp8_gemm(cuda, n, k, m):
+    q, s = synth.fp8_layer(n, k, seed=n)
+    x = synth.activations(m, k, seed=7)
+    ref = oracle.linear(x, oracle.round_bf16(oracle.fp8_dequant(q, s)))
+    y = L.Fp8Linear(dev(q), dev(s)).forward(dev(x, torch.bfloat16))
+    check(y, ref, f"fp8 gemm {n}x{k} m={m}")
+
+
+@pytest.mark.parametrize("n,k,m", [(10, 64, 33), (2880, 2880, 200), (5760, 2880, 64)])
+def test_mxfp4_gemm(cuda, n, k, m):
+    # (10, 64, 33) from metal_ops.rs:6621-6670; 2880 = GPT-OSS hidden (k tail of 64 inside a 128 tile)
+    b, s = synth.mxfp4_layer(n, k, seed=n)
+    bias = synth.bf16_round(np.random.default_rng(1).standard_normal(n).astype(np.float32) * 0.02)
+    x = synth.activations(m, k, seed=3)
+    ref = oracle.linear(x, oracle.mxfp4_dequant(b, s, n, k), bias)  # MXFP4 values are exact in bf16
+    y = L.Mxfp4Linear(dev(b), dev(s), dev(bias, torch.bfloat16), k, n).forward(dev(x, torch.bfloat16))
+    check(y, ref, f"mxfp4 gemm {n}x{k} m={m}")
+
+
+def test_workspace_too_small_is_rejected(cuda):
+    import ctypes
+    from oxydllm_b200 import _lib
+    one = ctypes.c_void_p(256)
+    with pytest.raises(_lib.OxqError, match="workspace of"):
+        _lib.call("oxq_awq_gemm", one, 2, one, one, one, 1, None, 0, one, 2, 64, 256, 256, 128, one, 16, None)
