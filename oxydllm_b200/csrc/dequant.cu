@@ -128,6 +128,102 @@ mxfp4_dequant_kernel(const uint8_t *__restrict__ blocks, const uint8_t *__restri
     }
 }
 
+
+// ---- slab producers for the tensor-core GEMM (bf16 out, same bits as the kernels above) --------
+// AWQ: a CTA of 256 threads owns 256 out columns x 64 input rows. The 64 x 32 packed words are
+// staged with coalesced 128-byte row reads; then thread t produces the 64 k values of out
+// column t (its nibble slot, zero point and scale are fixed for the tile) and writes its row
+// of the dense weight as eight 16-byte stores (one full 128-byte line).
+__global__ void __launch_bounds__(256)
+awq_slab_bf16_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict__ qzeros,
+                     const void *__restrict__ scales, int scales_dtype, __nv_bfloat16 *__restrict__ out, int k,
+                     int n_cnt, int group_size, int n_full, int n_off)
+{
+    __shared__ uint32_t raw[64][33];
+    const int t = threadIdx.x;
+    const int packed_full = n_full >> 3;
+    const int jw0 = (n_off >> 3) + blockIdx.x * 32; // first packed word of the tile (absolute)
+    const int k0 = blockIdx.y * 64;
+    const int jw_end = (n_off + n_cnt) >> 3;
+    for (int idx = t; idx < 64 * 32; idx += 256) {
+        const int r = idx >> 5, j = idx & 31;
+        uint32_t w = 0;
+        if (k0 + r < k && jw0 + j < jw_end) w = __ldcs(qweight + (size_t)(k0 + r) * packed_full + jw0 + j);
+        raw[r][j] = w;
+    }
+    __syncthreads();
+    const int col = blockIdx.x * 256 + t; // column inside the slab
+    if (col >= n_cnt) return;
+    const int jl = t >> 3, sh = 4 * awq_slot_of_col(t & 7);
+    const size_t nn = (size_t)n_off + col;
+    // group_size is a multiple of 64 or divides it: at most 64 / min(group_size, 64) groups per tile
+    __nv_bfloat16 *dst = out + (size_t)col * k + k0;
+    const bool group8 = (group_size % 8) == 0; // then 8 consecutive k share zero point and scale
+#pragma unroll 1
+    for (int c8 = 0; c8 < 8; c8++) {
+        if (k0 + c8 * 8 >= k) break;
+        uint32_t packed[4];
+        int z = 0;
+        float sc = 0.0f;
+        if (group8) {
+            const int g = (k0 + c8 * 8) / group_size;
+            z = (int)((__ldg(qzeros + (size_t)g * packed_full + jw0 + jl) >> sh) & 0xFu);
+            sc = load_as_f32(scales, scales_dtype, (size_t)g * n_full + nn);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u += 2) {
+            float v[2];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int r = c8 * 8 + u + h;
+                if (!group8) {
+                    const int g = min(k0 + r, k - 1) / group_size;
+                    z = (int)((__ldg(qzeros + (size_t)g * packed_full + jw0 + jl) >> sh) & 0xFu);
+                    sc = load_as_f32(scales, scales_dtype, (size_t)g * n_full + nn);
+                }
+                v[h] = __fmul_rn((float)((int)((raw[r][jl] >> sh) & 0xFu) - z), sc);
+            }
+            __nv_bfloat162 hh = __floats2bfloat162_rn(v[0], v[1]);
+            packed[u >> 1] = *reinterpret_cast<uint32_t *>(&hh);
+        }
+        if (k0 + c8 * 8 + 8 <= k && (k % 8) == 0)
+            *reinterpret_cast<uint4 *>(dst + c8 * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        else
+            for (int u = 0; u < 8 && k0 + c8 * 8 + u < k; u++)
+                dst[c8 * 8 + u] = reinterpret_cast<__nv_bfloat16 *>(packed)[u];
+    }
+}
+
+// FP8: 16 bytes in, 32 bytes out per thread; one scale lookup per 16 elements
+// (requires the scale block along k to be a multiple of 16).
+__global__ void __launch_bounds__(256)
+fp8_slab_bf16_kernel(const uint8_t *__restrict__ weight, const float *__restrict__ scale_inv, int s_in, int block_out,
+                     int block_in, __nv_bfloat16 *__restrict__ out, int n_cnt, int k, int row_off)
+{
+    const size_t total16 = (size_t)n_cnt * k / 16;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total16;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t e = idx * 16;
+        const int r = (int)(e / k), c = (int)(e % k);
+        const uint4 w = __ldcs(reinterpret_cast<const uint4 *>(weight) + idx);
+        const float s = scale_inv ? scale_inv[(size_t)((row_off + r) / block_out) * s_in + c / block_in] : 1.0f;
+        const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                float a = e4m3_to_f32((wv[q] >> (16 * h)) & 0xFFu), b = e4m3_to_f32((wv[q] >> (16 * h + 8)) & 0xFFu);
+                if (scale_inv) { a = __fmul_rn(s, a); b = __fmul_rn(s, b); }
+                __nv_bfloat162 hh = __floats2bfloat162_rn(a, b);
+                o[2 * q + h] = *reinterpret_cast<uint32_t *>(&hh);
+            }
+        uint4 *dst = reinterpret_cast<uint4 *>(out + e);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 static int grid_for(size_t work_items, int block = 256)
 {
     size_t blocks = (work_items + block - 1) / block;
@@ -140,10 +236,10 @@ static int grid_for(size_t work_items, int block = 256)
 int awq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
                           __nv_bfloat16 *out, int k, int n_full, int group_size, int n_off, int n_cnt, cudaStream_t st)
 {
-    dim3 grid(ceil_div(n_cnt / 8, 8), ceil_div(k, AWQ_TK));
-    awq_dequant_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(qweight, qzeros, scales, scales_dtype, out, k, n_cnt,
-                                                             group_size, n_full, n_off);
-    OXQ_LAUNCH_CHECK("awq_dequant_kernel");
+    dim3 grid(ceil_div(n_cnt, 256), ceil_div(k, 64));
+    awq_slab_bf16_kernel<<<grid, 256, 0, st>>>(qweight, qzeros, scales, scales_dtype, out, k, n_cnt, group_size,
+                                               n_full, n_off);
+    OXQ_LAUNCH_CHECK("awq_slab_bf16_kernel");
     return OXQ_OK;
 }
 
@@ -178,6 +274,12 @@ int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *
 int fp8_dequant_rows_bf16(const uint8_t *weight, const float *scale_inv, int s_in, int block_out, int block_in,
                           __nv_bfloat16 *out, int k, int n_off, int n_cnt, cudaStream_t st)
 {
+    if (k % 16 == 0 && block_in % 16 == 0 && aligned(weight, 16)) {
+        fp8_slab_bf16_kernel<<<grid_for((size_t)n_cnt * k / 16), 256, 0, st>>>(
+            weight + (size_t)n_off * k, scale_inv, s_in, block_out, block_in, out, n_cnt, k, n_off);
+        OXQ_LAUNCH_CHECK("fp8_slab_bf16_kernel");
+        return OXQ_OK;
+    }
     fp8_dequant_kernel<__nv_bfloat16><<<grid_for((size_t)n_cnt * k / 4), 256, 0, st>>>(
         weight + (size_t)n_off * k, scale_inv, s_in, block_out, block_in, out, n_cnt, k, n_off);
     OXQ_LAUNCH_CHECK("fp8_dequant_kernel");
