@@ -151,6 +151,29 @@ int oxq_mxfp4_gemm(const void *x, int x_dtype, const uint8_t *blocks, const uint
                    int bias_dtype, void *y, int y_dtype, int m, int k, int n, void *workspace, size_t workspace_bytes,
                    void *stream);
 
+/* No counterpart in the reference. oxq_awq_gemm for callers that cannot
+ * allocate device memory: code running inside a host runtime that owns the
+ * only allocator and does not lend it out, a plugin loaded after the process
+ * has handed all free memory to a pool, or a call made while allocation is
+ * forbidden (for instance between the start and end of a stream capture).
+ * The dequantization slab and the flag word live in a fixed 8 MiB (+256 B)
+ * device array inside the library image, held by every GPU that loads the
+ * library until the process exits. Limits and rules:
+ *   - in_features <= oxq_awq_gemm_noalloc_max_k() (16384), otherwise
+ *     OXQ_ERR_WORKSPACE is returned and nothing is launched;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture;
+ *   - all calls share the one array: the flag word is cleared by each call,
+ *     the slab is overwritten; calls that may overlap on the GPU (different
+ *     streams without ordering) race on it and give wrong results;
+ *   - it calls no cudaMalloc/cudaFree and no allocating library routine.
+ * oxq_awq_gemm_noalloc_check is oxq_gemm_check on that built-in array. */
+size_t oxq_awq_gemm_noalloc_max_k(void);
+int oxq_awq_gemm_noalloc(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros,
+                         const void *scales, int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype,
+                         int m, int k, int n, int group_size, void *stream);
+int oxq_awq_gemm_noalloc_check(void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -188,3 +188,65 @@ OXQ_EXPORT int oxq_mxfp4_gemm(const void *x, int x_dtype, const uint8_t *blocks,
         return mxfp4_dequant_rows_bf16(blocks, scales, c.slab, k, n_off, cnt, c.st);
     });
 }
+
+// ---- entry point that allocates nothing ----------------------------------------------------------
+// Scratch for oxq_awq_gemm_noalloc: a fixed device array that lives in the library image, so a
+// caller that must not (or cannot) call cudaMalloc still has somewhere to dequantize into.
+// Every GPU that loads the library holds these bytes until the process exits.
+constexpr size_t NOALLOC_SLAB_BYTES = 8u << 20;
+constexpr size_t NOALLOC_SCRATCH_BYTES = WS_HEADER + NOALLOC_SLAB_BYTES;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+// In host code the symbol above is only a handle; the device address is looked up once per device.
+static void *g_noalloc_scratch_addr[64] = {};
+
+OXQ_EXPORT size_t oxq_awq_gemm_noalloc_max_k(void) { return NOALLOC_SLAB_BYTES / (256 * 2); }
+
+OXQ_EXPORT int oxq_awq_gemm_noalloc(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros,
+                                    const void *scales, int scales_dtype, const void *bias, int bias_dtype, void *y,
+                                    int y_dtype, int m, int k, int n, int group_size, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(x && y && qweight && qzeros && scales, OXQ_ERR_NULL, "oxq_awq_gemm_noalloc: null pointer");
+    OXQ_REQUIRE(x_dtype == OXQ_BF16, OXQ_ERR_UNSUPPORTED, "oxq_awq_gemm_noalloc: activations must be bf16");
+    OXQ_REQUIRE(valid_dtype(scales_dtype) && valid_dtype(y_dtype) && (!bias || valid_dtype(bias_dtype)),
+                OXQ_ERR_UNSUPPORTED, "oxq_awq_gemm_noalloc: unsupported dtype");
+    OXQ_REQUIRE(m >= 1 && k > 0 && n > 0 && group_size > 0, OXQ_ERR_BAD_SHAPE, "oxq_awq_gemm_noalloc: non-positive size");
+    OXQ_REQUIRE(n % 8 == 0 && k % group_size == 0 && k % 8 == 0, OXQ_ERR_BAD_SHAPE,
+                "oxq_awq_gemm_noalloc: out_features %d must be a multiple of 8, in_features %d of 8 and of the group size %d",
+                n, k, group_size);
+    // The built-in scratch must hold at least one 256-row slab of the dequantized weight.
+    OXQ_REQUIRE((size_t)k <= oxq_awq_gemm_noalloc_max_k(), OXQ_ERR_WORKSPACE,
+                "oxq_awq_gemm_noalloc: in_features %d exceeds the built-in scratch (max %zu); use oxq_awq_gemm with a "
+                "caller workspace", k, oxq_awq_gemm_noalloc_max_k());
+    int device = 0;
+    OXQ_CUDA(cudaGetDevice(&device));
+    OXQ_REQUIRE(device >= 0 && device < 64, OXQ_ERR_UNSUPPORTED, "oxq_awq_gemm_noalloc: device index %d out of range", device);
+    if (g_noalloc_scratch_addr[device] == nullptr) {
+        // First call on this device (keep it outside any stream capture): resolve the device address.
+        void *addr = nullptr;
+        OXQ_CUDA(cudaGetSymbolAddress(&addr, g_noalloc_scratch));
+        g_noalloc_scratch_addr[device] = addr;
+    }
+    unsigned char *scratch = reinterpret_cast<unsigned char *>(g_noalloc_scratch_addr[device]);
+    GemmCommon c;
+    c.x = x; c.bias = bias; c.y = y; c.bias_dtype = bias_dtype; c.y_dtype = y_dtype; c.m = m; c.k = k; c.n = n;
+    c.flag = reinterpret_cast<int *>(scratch);
+    c.slab = reinterpret_cast<__nv_bfloat16 *>(scratch + WS_HEADER);
+    long long rows = (long long)(NOALLOC_SLAB_BYTES / ((size_t)k * 2)) / 256 * 256;
+    c.rows = rows >= n ? n : (int)rows;
+    c.st = (cudaStream_t)stream;
+    OXQ_CUDA(cudaMemsetAsync(c.flag, 0, sizeof(int), c.st)); // the array keeps the previous call's contents
+    return run_slabs(c, [&](int n_off, int cnt) {
+        return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, n_off, cnt, c.st);
+    });
+}
+
+OXQ_EXPORT int oxq_awq_gemm_noalloc_check(void *stream)
+{
+    clear_error();
+    int device = 0;
+    OXQ_CUDA(cudaGetDevice(&device));
+    OXQ_REQUIRE(device >= 0 && device < 64 && g_noalloc_scratch_addr[device] != nullptr, OXQ_ERR_NULL,
+                "oxq_awq_gemm_noalloc_check: no call of oxq_awq_gemm_noalloc has run on this device yet");
+    return oxq_gemm_check(g_noalloc_scratch_addr[device], stream);
+}
