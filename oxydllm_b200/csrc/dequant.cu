@@ -131,16 +131,16 @@ mxfp4_dequant_kernel(const uint8_t *__restrict__ blocks, const uint8_t *__restri
 
 // ---- slab producers for the tensor-core GEMM (bf16 out, same bits as the kernels above) --------
 // AWQ: a CTA of 256 threads owns 256 out columns x 64 input rows. The 64 x 32 packed words are
-// staged with coalesced 128-byte row reads; then thread t produces the 64 k values of out
-// column t (its nibble slot, zero point and scale are fixed for the tile) and writes its row
-// of the dense weight as eight 16-byte stores (one full 128-byte line).
+// staged with coalesced 128-byte row reads; then each warp walks 32 out columns, and for one
+// column the 32 lanes produce the 64 k values (two each) and store them as one contiguous
+// 128-byte line of the dense [n, k] weight. Nibble slot, zero point and scale are warp-uniform.
 __global__ void __launch_bounds__(256)
 awq_slab_bf16_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict__ qzeros,
                      const void *__restrict__ scales, int scales_dtype, __nv_bfloat16 *__restrict__ out, int k,
                      int n_cnt, int group_size, int n_full, int n_off)
 {
     __shared__ uint32_t raw[64][33];
-    const int t = threadIdx.x;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int packed_full = n_full >> 3;
     const int jw0 = (n_off >> 3) + blockIdx.x * 32; // first packed word of the tile (absolute)
     const int k0 = blockIdx.y * 64;
@@ -152,45 +152,44 @@ awq_slab_bf16_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__res
         raw[r][j] = w;
     }
     __syncthreads();
-    const int col = blockIdx.x * 256 + t; // column inside the slab
-    if (col >= n_cnt) return;
-    const int jl = t >> 3, sh = 4 * awq_slot_of_col(t & 7);
-    const size_t nn = (size_t)n_off + col;
-    // group_size is a multiple of 64 or divides it: at most 64 / min(group_size, 64) groups per tile
-    __nv_bfloat16 *dst = out + (size_t)col * k + k0;
-    const bool group8 = (group_size % 8) == 0; // then 8 consecutive k share zero point and scale
-#pragma unroll 1
-    for (int c8 = 0; c8 < 8; c8++) {
-        if (k0 + c8 * 8 >= k) break;
-        uint32_t packed[4];
+    const int ka = k0 + 2 * lane, kb = ka + 1; // this lane's two input rows
+    const bool pair_ok = kb < k && (k % 2) == 0;
+    const bool tile_one_group = (group_size % 64) == 0; // then the 64 rows of the tile share zero point and scale
+    const int g_tile = k0 / group_size;
+#pragma unroll 4
+    for (int i = 0; i < 32; i++) {
+        const int cl = warp * 32 + i;           // column inside the tile
+        const int col = blockIdx.x * 256 + cl;  // column inside the slab
+        if (col >= n_cnt) break;
+        const int jl = cl >> 3, sh = 4 * awq_slot_of_col(cl & 7);
+        const size_t nn = (size_t)n_off + col;
         int z = 0;
         float sc = 0.0f;
-        if (group8) {
-            const int g = (k0 + c8 * 8) / group_size;
-            z = (int)((__ldg(qzeros + (size_t)g * packed_full + jw0 + jl) >> sh) & 0xFu);
-            sc = load_as_f32(scales, scales_dtype, (size_t)g * n_full + nn);
+        if (tile_one_group) {
+            z = (int)((__ldg(qzeros + (size_t)g_tile * packed_full + jw0 + jl) >> sh) & 0xFu);
+            sc = load_as_f32(scales, scales_dtype, (size_t)g_tile * n_full + nn);
         }
+        float v[2];
 #pragma unroll
-        for (int u = 0; u < 8; u += 2) {
-            float v[2];
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int r = c8 * 8 + u + h;
-                if (!group8) {
-                    const int g = min(k0 + r, k - 1) / group_size;
-                    z = (int)((__ldg(qzeros + (size_t)g * packed_full + jw0 + jl) >> sh) & 0xFu);
-                    sc = load_as_f32(scales, scales_dtype, (size_t)g * n_full + nn);
-                }
-                v[h] = __fmul_rn((float)((int)((raw[r][jl] >> sh) & 0xFu) - z), sc);
+        for (int h = 0; h < 2; h++) {
+            if (!tile_one_group) {
+                const int g = min(ka + h, k - 1) / group_size;
+                z = (int)((__ldg(qzeros + (size_t)g * packed_full + jw0 + jl) >> sh) & 0xFu);
+                sc = load_as_f32(scales, scales_dtype, (size_t)g * n_full + nn);
             }
-            __nv_bfloat162 hh = __floats2bfloat162_rn(v[0], v[1]);
-            packed[u >> 1] = *reinterpret_cast<uint32_t *>(&hh);
+            const int d = (int)((raw[2 * lane + h][jl] >> sh) & 0xFu) - z;
+            // exact int -> float for |d| <= 15 without the conversion unit: 1.5 * 2^23 + d, minus 1.5 * 2^23
+            const float df = __uint_as_float(0x4B400000u + (uint32_t)d) - 12582912.0f;
+            v[h] = __fmul_rn(df, sc);
         }
-        if (k0 + c8 * 8 + 8 <= k && (k % 8) == 0)
-            *reinterpret_cast<uint4 *>(dst + c8 * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        else
-            for (int u = 0; u < 8 && k0 + c8 * 8 + u < k; u++)
-                dst[c8 * 8 + u] = reinterpret_cast<__nv_bfloat16 *>(packed)[u];
+        __nv_bfloat16 *dst = out + (size_t)col * k;
+        if (pair_ok) {
+            __nv_bfloat162 hh = __floats2bfloat162_rn(v[0], v[1]);
+            *reinterpret_cast<__nv_bfloat162 *>(dst + ka) = hh;
+        } else {
+            if (ka < k) dst[ka] = __float2bfloat16_rn(v[0]);
+            if (kb < k) dst[kb] = __float2bfloat16_rn(v[1]);
+        }
     }
 }
 

@@ -1,6 +1,7 @@
 // C-ABI entry points of the prefill-sized (m > 32) quantized matmuls: dequantize a slab of weight
 // rows into the caller's workspace (bit-exact kernels of dequant.cu), run the tcgen05 GEMM of
-// gemm_tc.cu on it, repeat. The slab (<= 32 MiB) is written and re-read while it is still in L2.
+// gemm_tc.cu on it, repeat. A weight of up to 128 MiB (as bf16) is one slab; larger ones are cut so that each slab is a
+// whole number of rounds of the persistent GEMM grid.
 #include "oxq_common.cuh"
 
 namespace oxq {
@@ -19,14 +20,28 @@ int mxfp4_dequant_rows_bf16(const uint8_t *blocks, const uint8_t *scales, __nv_b
                             int n_cnt, cudaStream_t st);
 bool gguf_block_layout_host(int ggml_type, int &bel, int &bby);
 
-constexpr size_t WS_HEADER = 256;               // flag word + padding, keeps the slab 256-byte aligned
-constexpr size_t SLAB_TARGET_BYTES = 32u << 20; // dequantized rows per GEMM launch
+constexpr size_t WS_HEADER = 256;                // flag word + padding, keeps the slab 256-byte aligned
+constexpr size_t SLAB_LIMIT_BYTES = 128u << 20;  // dequantized rows held at once (whole weight if it fits)
 
+// Rows of the workspace slab for an [n, k] weight: everything if it fits the limit, else the limit.
 static int slab_rows(int n, int k)
 {
-    long long rows = (long long)(SLAB_TARGET_BYTES / ((size_t)k * 2)) / 256 * 256;
+    long long rows = (long long)(SLAB_LIMIT_BYTES / ((size_t)k * 2)) / 256 * 256;
     if (rows < 256) rows = 256;
     return rows >= n ? n : (int)rows;
+}
+
+// When the weight needs several slabs, make each one a whole number of persistent-grid rounds:
+// tiles_m x (rows / 256) tiles should be a multiple of the SM count (148 = 4 x 37 SMs).
+static int slab_rows_for_m(int cap_rows, int n, int m)
+{
+    if (cap_rows >= n) return n;
+    const int tiles_m = (m + 127) / 128;
+    int g = tiles_m, b = 148;
+    while (b) { const int t = g % b; g = b; b = t; } // gcd(tiles_m, 148)
+    const int q = 148 / g * 256;                      // rows per balanced group of n tiles
+    if (q <= cap_rows) return cap_rows / q * q;
+    return cap_rows / 256 * 256;
 }
 
 struct GemmCommon {
@@ -54,7 +69,7 @@ static int prepare(const char *who, GemmCommon &c, const void *x, int x_dtype, c
     c.x = x; c.bias = bias; c.y = y; c.bias_dtype = bias_dtype; c.y_dtype = y_dtype; c.m = m; c.k = k; c.n = n;
     c.flag = reinterpret_cast<int *>(workspace);
     c.slab = reinterpret_cast<__nv_bfloat16 *>(reinterpret_cast<unsigned char *>(workspace) + WS_HEADER);
-    c.rows = slab_rows(n, k);
+    c.rows = slab_rows_for_m(slab_rows(n, k), n, m);
     c.st = (cudaStream_t)stream;
     OXQ_CUDA(cudaMemsetAsync(c.flag, 0, sizeof(int), c.st));
     return OXQ_OK;
@@ -89,7 +104,8 @@ OXQ_EXPORT int oxq_gemm_check(const void *workspace, void *stream)
     int flag = 0;
     OXQ_CUDA(cudaMemcpyAsync(&flag, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     OXQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-    OXQ_REQUIRE(flag == 0, OXQ_ERR_DEVICE_FLAG, "tensor-core GEMM: bounded wait %d ran out (1 = ring slot, 2 = tile data, 3 = accumulator)", flag);
+    OXQ_REQUIRE(flag == 0, OXQ_ERR_DEVICE_FLAG,
+                "tensor-core GEMM: bounded wait %d ran out (1 = ring slot, 2 = tile data, 3 = accumulator ready, 4 = accumulator free)", flag);
     return OXQ_OK;
 }
 

@@ -2,11 +2,12 @@
 //
 //   y[m, n] = x[m, k] . W[n, k]^T (+ bias),  x bf16, W bf16 (a dequantized slab), f32 accumulation
 //
-// One CTA computes a 128 x BN output tile (BN = 256). Warp-specialised:
+// A persistent CTA per SM walks 128 x BN output tiles (BN <= 256 picked per call). Warp-specialised:
 //   warp 0     TMA producer: x tile [128 x 64] and W tile [BN x 64] per k block, both K-major,
 //              128-byte swizzle, 4-stage ring guarded by full/empty mbarriers;
 //   warp 1     MMA issuer: one elected lane issues tcgen05.mma (cta_group::1, kind::f16, M=128,
-//              N=BN, K=16) on shared-memory descriptors, accumulator in TMEM (BN columns);
+//              N=BN, K=16) on shared-memory descriptors into one of two TMEM accumulators, so the
+//              epilogue of a tile overlaps the MMAs of the next;
 //              tcgen05.commit releases ring slots and finally signals the epilogue;
 //   warps 2-5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, bias, narrowing, stores.
 // Every wait is bounded (wall-clock limit); on expiry the kernel records a code in the caller's
@@ -30,6 +31,7 @@ constexpr uint32_t TC_A_BYTES = TC_BM * TC_BK * 2;
 constexpr uint32_t TC_B_BYTES = TC_BN * TC_BK * 2;
 constexpr uint32_t TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr size_t TC_SMEM_BYTES = 1024 /* alignment slack */ + (size_t)TC_STAGES * TC_STAGE_BYTES + 256 /* barriers */;
+constexpr int TC_BN_CHOICES[] = {256, 224, 192, 160, 128};
 constexpr unsigned long long TC_WAIT_LIMIT_NS = 2000000000ull; // 2 s
 
 struct GemmParams {
@@ -39,6 +41,7 @@ struct GemmParams {
     int bias_dtype, y_dtype;
     int m, n, k;      // n = rows of W in this call (a slab); y columns [n_off, n_off + n)
     int n_off, ldy;   // ldy = full out_features
+    int tiles_m, tiles_n, bn; // tile grid of this call; bn = tile width (multiple of 32, <= 256)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------
@@ -154,6 +157,9 @@ __host__ __device__ constexpr uint32_t tc_idesc(int m, int n)
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Persistent kernel: CTA c handles tiles c, c + gridDim.x, ... (m fastest, so CTAs running together
+// share W tiles through L2). Two TMEM accumulators (2 x 256 columns) let the epilogue of one tile
+// overlap the MMAs of the next. `bn` (a multiple of 32, <= 256) is the tile width chosen by the host.
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p)
@@ -165,23 +171,28 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t bars = base + TC_STAGES * TC_STAGE_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (TC_STAGES + s); };
-    const uint32_t tmem_full_bar = bars + 8u * (2 * TC_STAGES);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + TC_STAGES * TC_STAGE_BYTES + 8 * (2 * TC_STAGES + 1));
+    auto tmem_full_bar = [&](int b) { return bars + 8u * (2 * TC_STAGES + b); };
+    auto tmem_empty_bar = [&](int b) { return bars + 8u * (2 * TC_STAGES + 2 + b); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + TC_STAGES * TC_STAGE_BYTES + 8 * (2 * TC_STAGES + 4));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
     const int k_iters = (p.k + TC_BK - 1) / TC_BK;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const uint32_t stage_tx = TC_A_BYTES + (uint32_t)p.bn * TC_BK * 2;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; s++) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(tmem_full_bar, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(tmem_full_bar(b), 1);
+            mbar_init(tmem_empty_bar(b), 4); // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) { // the allocating warp also frees
-        tmem_alloc(smem_u32(tmem_slot), TC_BN);
+        tmem_alloc(smem_u32(tmem_slot), 2 * TC_BN);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -191,50 +202,68 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0) {
         if (elect_one()) {
-            for (int it = 0; it < k_iters; it++) {
-                const int s = it % TC_STAGES;
-                const uint32_t round = it / TC_STAGES;
-                if (!mbar_wait(empty_bar(s), (round & 1) ^ 1, p.flag, 1)) break;
-                mbar_arrive_expect_tx(full_bar(s), TC_STAGE_BYTES);
-                const uint32_t sa = base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
-                tma_load_2d(sa, &map_a, full_bar(s), it * TC_BK, m0);
-                tma_load_2d(sb, &map_b, full_bar(s), it * TC_BK, n0);
+            uint32_t it = 0; // k blocks issued so far by this CTA, across tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % p.tiles_m) * TC_BM, n0 = (tile / p.tiles_m) * p.bn;
+                for (int kb = 0; kb < k_iters; kb++, it++) {
+                    const int s = it % TC_STAGES;
+                    ok = mbar_wait(empty_bar(s), ((it / TC_STAGES) & 1) ^ 1, p.flag, 1);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                    const uint32_t sa = base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                    tma_load_2d(sa, &map_a, full_bar(s), kb * TC_BK, m0);
+                    tma_load_2d(sb, &map_b, full_bar(s), kb * TC_BK, n0);
+                }
             }
         }
     } else if (warp == 1) {
         if (elect_one()) {
-            constexpr uint32_t idesc = tc_idesc(TC_BM, TC_BN);
+            const uint32_t idesc = tc_idesc(TC_BM, p.bn);
+            uint32_t it = 0, local = 0;
             bool ok = true;
-            for (int it = 0; it < k_iters && ok; it++) {
-                const int s = it % TC_STAGES;
-                const uint32_t round = it / TC_STAGES;
-                ok = mbar_wait(full_bar(s), round & 1, p.flag, 2);
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+                const int buf = local & 1;
+                ok = mbar_wait(tmem_empty_bar(buf), ((local >> 1) & 1) ^ 1, p.flag, 4);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sa = base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
-                const uint64_t da = kmajor_sw128_desc(sa), db = kmajor_sw128_desc(sb);
+                const uint32_t d_tmem = tmem_base + buf * TC_BN;
+                for (int kb = 0; kb < k_iters; kb++, it++) {
+                    const int s = it % TC_STAGES;
+                    ok = mbar_wait(full_bar(s), (it / TC_STAGES) & 1, p.flag, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                    const uint64_t da = kmajor_sw128_desc(sa), db = kmajor_sw128_desc(sb);
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / TC_UMMA_K; kk++) {
-                    // 16 bf16 along k = 32 bytes inside the 128-byte swizzled row: +2 in the address field
-                    umma_bf16(tmem_base, da + 2 * kk, db + 2 * kk, idesc, (it | kk) != 0);
+                    for (int kk = 0; kk < TC_BK / TC_UMMA_K; kk++) {
+                        // 16 bf16 along k = 32 bytes inside the 128-byte swizzled row: +2 in the address field
+                        umma_bf16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
+                    }
+                    umma_commit(empty_bar(s)); // slot reusable once these MMAs have read it
                 }
-                umma_commit(empty_bar(s)); // slot reusable once these MMAs have read it
+                umma_commit(tmem_full_bar(buf)); // accumulator complete (arrives even after an aborted loop)
             }
-            umma_commit(tmem_full_bar);    // accumulator complete (arrives even after an aborted loop)
         }
     } else {
         // Epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 only.
         const int quad = warp & 3;
-        const int row = m0 + quad * 32 + lane;
-        const bool done = mbar_wait(tmem_full_bar, 0, p.flag, 3);
-        tc_fence_after();
-        if (done) {
-            const bool vec_ok = p.y_dtype == OXQ_BF16 && (p.ldy % 8 == 0) && (p.n_off % 8 == 0) &&
-                                (reinterpret_cast<uintptr_t>(p.y) & 15) == 0;
+        const bool vec_ok = p.y_dtype == OXQ_BF16 && (p.ldy % 8 == 0) && (p.n_off % 8 == 0) &&
+                            (reinterpret_cast<uintptr_t>(p.y) & 15) == 0;
+        uint32_t local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+            const int buf = local & 1;
+            const int m0 = (tile % p.tiles_m) * TC_BM, n0 = (tile / p.tiles_m) * p.bn;
+            const int row = m0 + quad * 32 + lane;
+            ok = mbar_wait(tmem_full_bar(buf), (local >> 1) & 1, p.flag, 3);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll 1
-            for (int cb = 0; cb < TC_BN / 32; cb++) {
+            for (int cb = 0; cb < p.bn / 32; cb++) {
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + cb * 32, r);
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * TC_BN + cb * 32, r);
                 tmem_ld_wait();
                 const int col0 = n0 + cb * 32; // column inside this slab
                 if (row < p.m && col0 < p.n) {
@@ -256,21 +285,28 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int q = 0; q < 4; q++)
                             dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                     } else {
-                        for (int j = 0; j < 32 && col0 + j < p.n; j++) {
-                            float v = __uint_as_float(r[j]);
-                            if (p.bias) v += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + j);
-                            store_as(p.y, p.y_dtype, out + j, v);
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (col0 + j < p.n) {
+                                float v = __uint_as_float(r[j]);
+                                if (p.bias) v += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + j);
+                                store_as(p.y, p.y_dtype, out + j, v);
+                            }
                         }
                     }
                 }
             }
+            // This warp has drained its quarter of the accumulator: hand the buffer back.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tmem_empty_bar(buf)) : "memory");
         }
         tc_fence_before();
     }
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TC_BN);
+        tmem_dealloc(tmem_base, 2 * TC_BN);
     }
 }
 
@@ -308,16 +344,45 @@ static int make_map_bf16(CUtensorMap *map, const void *ptr, uint64_t rows, uint6
     return OXQ_OK;
 }
 
+static int sm_count()
+{
+    static int count[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+    if (count[device] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || v <= 0) v = 148;
+        count[device] = v;
+    }
+    return count[device];
+}
+
+// Tile width that minimises (rounds of the persistent grid) x (time of one tile ~ bn + fixed cost).
+int gemm_pick_bn(int m, int n)
+{
+    const int sms = sm_count(), tiles_m = ceil_div(m, TC_BM);
+    long long best_cost = -1;
+    int best = TC_BN;
+    for (int bn : TC_BN_CHOICES) {
+        const long long tiles = (long long)tiles_m * ceil_div(n, bn);
+        const long long rounds = (tiles + sms - 1) / sms;
+        const long long cost = rounds * (bn + 24);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
 // y[:, n_off : n_off + n] = x[m, k] . w[n, k]^T (+ bias) with x, w bf16 row-major.
 int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int n,
                  int k, int n_off, int ldy, int *flag, cudaStream_t stream)
 {
     OXQ_REQUIRE(aligned(x, 16) && aligned(w, 16), OXQ_ERR_BAD_ALIGN, "tensor-core GEMM operands must be 16-byte aligned");
     OXQ_REQUIRE(k % 8 == 0, OXQ_ERR_UNSUPPORTED, "tensor-core GEMM needs in_features %% 8 == 0 (got %d)", k);
+    const int bn = gemm_pick_bn(m, n);
     CUtensorMap map_a, map_b;
     int rc = make_map_bf16(&map_a, x, (uint64_t)m, (uint64_t)k, TC_BM);
     if (rc) return rc;
-    rc = make_map_bf16(&map_b, w, (uint64_t)n, (uint64_t)k, TC_BN);
+    rc = make_map_bf16(&map_b, w, (uint64_t)n, (uint64_t)k, (uint32_t)bn);
     if (rc) return rc;
     static bool configured[64] = {};
     int device = 0;
@@ -329,8 +394,9 @@ int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype,
     GemmParams p;
     p.bias = bias; p.y = y; p.flag = flag; p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
     p.m = m; p.n = n; p.k = k; p.n_off = n_off; p.ldy = ldy;
-    const dim3 grid(ceil_div(m, TC_BM), ceil_div(n, TC_BN));
-    gemm_bf16_tn_kernel<<<grid, 192, TC_SMEM_BYTES, stream>>>(map_a, map_b, p);
+    p.tiles_m = ceil_div(m, TC_BM); p.tiles_n = ceil_div(n, bn); p.bn = bn;
+    const int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
+    gemm_bf16_tn_kernel<<<tiles < sms ? tiles : sms, 192, TC_SMEM_BYTES, stream>>>(map_a, map_b, p);
     OXQ_LAUNCH_CHECK("gemm_bf16_tn_kernel");
     return OXQ_OK;
 }
