@@ -151,6 +151,31 @@ int oxq_mxfp4_gemm(const void *x, int x_dtype, const uint8_t *blocks, const uint
                    int bias_dtype, void *y, int y_dtype, int m, int k, int n, void *workspace, size_t workspace_bytes,
                    void *stream);
 
+/* ------------------------------------------------------- GPT-OSS MoE layer
+ * MoeFeedForward::forward for GptOss experts (moe.rs:466-499 routing, 563-607
+ * dispatch_sparse, 152-173 expert math; tensor layout of load_gpt_oss,
+ * moe.rs:407-434): gu_blocks u8 [E, 2*inter, hidden/32, 16], gu_scales u8
+ * [E, 2*inter, hidden/32], gu_bias [E, 2*inter] (gate = even, up = odd rows),
+ * dn_blocks u8 [E, hidden, inter/32, 16], dn_scales, dn_bias [E, hidden].
+ * router_logits f32 [tokens, E] are the router linear's output. Only experts
+ * in [expert_lo, expert_hi) are evaluated (expert parallelism: the outputs of
+ * the ranks add up to the full layer); pass 0, E for the whole layer.
+ * Everything runs on `stream` without a host round trip. `workspace`: device
+ * memory of oxq_gptoss_moe_workspace_bytes(tokens, top_k, expert_hi -
+ * expert_lo, hidden, inter) bytes, 256-byte aligned; oxq_gemm_check applies. */
+size_t oxq_gptoss_moe_workspace_bytes(int tokens, int top_k, int num_local_experts, int hidden, int inter);
+int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *router_logits, int tokens, int num_experts,
+                           int top_k, int norm_topk, int hidden, int inter, const uint8_t *gu_blocks,
+                           const uint8_t *gu_scales, const void *gu_bias, const uint8_t *dn_blocks,
+                           const uint8_t *dn_scales, const void *dn_bias, int bias_dtype, float limit, int expert_lo,
+                           int expert_hi, void *out, int out_dtype, void *workspace, size_t workspace_bytes,
+                           void *stream);
+
+/* Routing alone: softmax over all experts, top-k (ties: lower index), optional
+ * renormalisation (moe.rs:472-487). top_idx i32 [tokens, top_k], top_w f32. */
+int oxq_moe_route(const float *router_logits, int tokens, int num_experts, int top_k, int norm_topk, int32_t *top_idx,
+                  float *top_w, void *stream);
+
 /* No counterpart in the reference. oxq_awq_gemm for callers that cannot
  * allocate device memory: code running inside a host runtime that owns the
  * only allocator and does not lend it out, a plugin loaded after the process

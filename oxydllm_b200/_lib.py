@@ -35,12 +35,16 @@ SIGNATURES = {
     "oxq_gguf_gemm": [_i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp],
     "oxq_fp8_gemm": [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp],
     "oxq_mxfp4_gemm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp],
+    "oxq_gptoss_moe_workspace_bytes": [_i, _i, _i, _i, _i],
+    "oxq_gptoss_moe_forward": [_vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, ctypes.c_float,
+                               _i, _i, _vp, _i, _vp, _sz, _vp],
+    "oxq_moe_route": [_vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "oxq_awq_gemm_noalloc_max_k": [],
     "oxq_awq_gemm_noalloc": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "oxq_awq_gemm_noalloc_check": [_vp],
 }
 _RESTYPE = {"oxq_status_string": ctypes.c_char_p, "oxq_last_error": ctypes.c_char_p,
-            "oxq_gemm_workspace_bytes": ctypes.c_size_t, "oxq_awq_gemm_noalloc_max_k": ctypes.c_size_t}
+            "oxq_gemm_workspace_bytes": ctypes.c_size_t, "oxq_gptoss_moe_workspace_bytes": ctypes.c_size_t, "oxq_awq_gemm_noalloc_max_k": ctypes.c_size_t}
 
 _lib = None
 

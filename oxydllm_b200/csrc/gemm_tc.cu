@@ -310,6 +310,176 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// ---- grouped (ragged-batch) variant for the MoE expert layer -----------------------------------
+// Same pipeline; the tiles come from a device-side table built by the routing kernels, so no host
+// round trip is needed: entry = {first row in the expert-sorted activation matrix, valid rows,
+// expert id}. B rows of expert e start at (e - e_first) * nw in the dequantized slab.
+// epi 0: out[row, col] = acc + bias[e, col]                      (bf16, [rows, nw])
+// epi 1: GPT-OSS clamped SwiGLU on interleaved (gate, up) columns (bf16, [rows, nw / 2]):
+//        gate = min(g, limit), up = clamp(u, +-limit), out = (up + 1) * gate * sigmoid(1.702 gate)
+struct GroupedParams {
+    const int4 *entries;
+    const int *grp_beg;
+    const void *bias;
+    void *out;
+    int *flag;
+    int group, e_first, nw, k, tiles_n, bn, bias_dtype, ldo, epi;
+    float limit;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GroupedParams p)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char *base_ptr = smem_raw + (base - raw);
+    const uint32_t bars = base + TC_STAGES * TC_STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (TC_STAGES + s); };
+    auto tmem_full_bar = [&](int b) { return bars + 8u * (2 * TC_STAGES + b); };
+    auto tmem_empty_bar = [&](int b) { return bars + 8u * (2 * TC_STAGES + 2 + b); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + TC_STAGES * TC_STAGE_BYTES + 8 * (2 * TC_STAGES + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_iters = (p.k + TC_BK - 1) / TC_BK;
+    const int mt_beg = p.grp_beg[p.group];
+    const int num_mt = p.grp_beg[p.group + 1] - mt_beg;
+    const int num_tiles = num_mt * p.tiles_n;
+    const uint32_t stage_tx = TC_A_BYTES + (uint32_t)p.bn * TC_BK * 2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(tmem_full_bar(b), 1);
+            mbar_init(tmem_empty_bar(b), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 2 * TC_BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int4 en = p.entries[mt_beg + tile % num_mt];
+                const int n0 = (tile / num_mt) * p.bn;
+                const int brow = (en.z - p.e_first) * p.nw + n0;
+                for (int kb = 0; kb < k_iters; kb++, it++) {
+                    const int s = it % TC_STAGES;
+                    ok = mbar_wait(empty_bar(s), ((it / TC_STAGES) & 1) ^ 1, p.flag, 1);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                    const uint32_t sa = base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                    tma_load_2d(sa, &map_a, full_bar(s), kb * TC_BK, en.x);
+                    tma_load_2d(sb, &map_b, full_bar(s), kb * TC_BK, brow);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            const uint32_t idesc = tc_idesc(TC_BM, p.bn);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+                const int buf = local & 1;
+                ok = mbar_wait(tmem_empty_bar(buf), ((local >> 1) & 1) ^ 1, p.flag, 4);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * TC_BN;
+                for (int kb = 0; kb < k_iters; kb++, it++) {
+                    const int s = it % TC_STAGES;
+                    ok = mbar_wait(full_bar(s), (it / TC_STAGES) & 1, p.flag, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                    const uint64_t da = kmajor_sw128_desc(sa), db = kmajor_sw128_desc(sb);
+#pragma unroll
+                    for (int kk = 0; kk < TC_BK / TC_UMMA_K; kk++)
+                        umma_bf16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
+                    umma_commit(empty_bar(s));
+                }
+                umma_commit(tmem_full_bar(buf));
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        uint32_t local = 0;
+        bool ok = true;
+        __nv_bfloat16 *outp = reinterpret_cast<__nv_bfloat16 *>(p.out);
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+            const int buf = local & 1;
+            const int4 en = p.entries[mt_beg + tile % num_mt];
+            const int n0 = (tile / num_mt) * p.bn;
+            const int r_in = quad * 32 + lane;
+            const size_t row = (size_t)en.x + r_in;
+            ok = mbar_wait(tmem_full_bar(buf), (local >> 1) & 1, p.flag, 3);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int cb = 0; cb < p.bn / 32; cb++) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * TC_BN + cb * 32, r);
+                tmem_ld_wait();
+                const int col0 = n0 + cb * 32;
+                if (r_in < en.y && col0 < p.nw) {
+                    const size_t bcol = (size_t)en.z * p.nw + col0;
+                    if (p.epi == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            if (col0 + j < p.nw) { // nw is even
+                                float v0 = __uint_as_float(r[j]), v1 = __uint_as_float(r[j + 1]);
+                                if (p.bias) {
+                                    v0 += load_as_f32(p.bias, p.bias_dtype, bcol + j);
+                                    v1 += load_as_f32(p.bias, p.bias_dtype, bcol + j + 1);
+                                }
+                                *reinterpret_cast<__nv_bfloat162 *>(outp + row * p.ldo + col0 + j) = __floats2bfloat162_rn(v0, v1);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            if (col0 + j < p.nw) {
+                                float gate = __uint_as_float(r[j]), up = __uint_as_float(r[j + 1]);
+                                if (p.bias) {
+                                    gate += load_as_f32(p.bias, p.bias_dtype, bcol + j);
+                                    up += load_as_f32(p.bias, p.bias_dtype, bcol + j + 1);
+                                }
+                                gate = fminf(gate, p.limit);
+                                up = fminf(fmaxf(up, -p.limit), p.limit);
+                                const float sig = 1.0f / (expf(-1.702f * gate) + 1.0f);
+                                outp[row * p.ldo + ((col0 + j) >> 1)] = __float2bfloat16_rn((up + 1.0f) * (gate * sig));
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tmem_empty_bar(buf)) : "memory");
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * TC_BN);
+    }
+}
+
 // ---- host side ---------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -398,6 +568,43 @@ int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype,
     const int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
     gemm_bf16_tn_kernel<<<tiles < sms ? tiles : sms, 192, TC_SMEM_BYTES, stream>>>(map_a, map_b, p);
     OXQ_LAUNCH_CHECK("gemm_bf16_tn_kernel");
+    return OXQ_OK;
+}
+
+// Grouped GEMM over the m tiles of expert group `group`: a = expert-sorted activations [a_rows, k],
+// w = dequantized slab [slab_experts * nw, k]; out rows follow the sorted order.
+int gemm_grouped(const void *a, int a_rows, const void *w, int slab_experts, int e_first, int nw, int k,
+                 const int4 *entries, const int *grp_beg, int group, const void *bias, int bias_dtype, void *out,
+                 int ldo, int epi, float limit, int *flag, cudaStream_t stream)
+{
+    OXQ_REQUIRE(aligned(a, 16) && aligned(w, 16), OXQ_ERR_BAD_ALIGN, "grouped GEMM operands must be 16-byte aligned");
+    OXQ_REQUIRE(k % 8 == 0 && nw % 2 == 0, OXQ_ERR_UNSUPPORTED, "grouped GEMM needs in_features %% 8 == 0 and even out_features");
+    int bn = TC_BN; // widest tile whose last column tile wastes the least
+    {
+        long long best = -1;
+        for (int c : TC_BN_CHOICES) {
+            const long long cost = (long long)ceil_div(nw, c) * (c + 24);
+            if (best < 0 || cost < best) { best = cost; bn = c; }
+        }
+    }
+    CUtensorMap map_a, map_b;
+    int rc = make_map_bf16(&map_a, a, (uint64_t)a_rows, (uint64_t)k, TC_BM);
+    if (rc) return rc;
+    rc = make_map_bf16(&map_b, w, (uint64_t)slab_experts * nw, (uint64_t)k, (uint32_t)bn);
+    if (rc) return rc;
+    static bool configured[64] = {};
+    int device = 0;
+    OXQ_CUDA(cudaGetDevice(&device));
+    if (device >= 64 || !configured[device]) {
+        OXQ_CUDA(cudaFuncSetAttribute(gemm_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+        if (device < 64) configured[device] = true;
+    }
+    GroupedParams p;
+    p.entries = entries; p.grp_beg = grp_beg; p.bias = bias; p.out = out; p.flag = flag;
+    p.group = group; p.e_first = e_first; p.nw = nw; p.k = k; p.tiles_n = ceil_div(nw, bn); p.bn = bn;
+    p.bias_dtype = bias_dtype; p.ldo = ldo; p.epi = epi; p.limit = limit;
+    gemm_grouped_kernel<<<sm_count(), 192, TC_SMEM_BYTES, stream>>>(map_a, map_b, p);
+    OXQ_LAUNCH_CHECK("gemm_grouped_kernel");
     return OXQ_OK;
 }
 

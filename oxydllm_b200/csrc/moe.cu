@@ -1,0 +1,341 @@
+// GPT-OSS MoE expert layer on MXFP4 weights, device-side end to end (no host round trip):
+//   route (softmax, top-k, renormalise) -> count / plan / scatter tokens per expert ->
+//   gather rows -> [dequantize expert group -> grouped tcgen05 GEMM + clamped SwiGLU]* ->
+//   [dequantize -> grouped GEMM (down)]* -> weighted combine in ascending expert order.
+// Mirrors MoeFeedForward::forward + dispatch_sparse + MoeExpert::GptOss (moe.rs:466-499,
+// 563-607, 152-173); every reduction has a fixed order, so results are run-to-run identical.
+#include "oxq_common.cuh"
+
+namespace oxq {
+
+int mxfp4_dequant_rows_bf16(const uint8_t *blocks, const uint8_t *scales, __nv_bfloat16 *out, int k, int n_off,
+                            int n_cnt, cudaStream_t st);
+int gemm_grouped(const void *a, int a_rows, const void *w, int slab_experts, int e_first, int nw, int k,
+                 const int4 *entries, const int *grp_beg, int group, const void *bias, int bias_dtype, void *out,
+                 int ldo, int epi, float limit, int *flag, cudaStream_t stream);
+
+constexpr int MOE_MAX_EXPERTS = 256;
+constexpr int MOE_MAX_TOPK = 8;
+
+// One warp per token: f32 softmax over all experts, k rounds of arg-max (ties: lower index),
+// optional renormalisation by the sum of the selected probabilities (moe.rs:472-487).
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float *__restrict__ logits, int tokens, int experts, int top_k, int norm_topk,
+                 int *__restrict__ top_idx, float *__restrict__ top_w)
+{
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= tokens) return;
+    const float *l = logits + (size_t)warp * experts;
+    constexpr int PER = MOE_MAX_EXPERTS / 32;
+    float v[PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        const int e = lane + 32 * i;
+        v[i] = e < experts ? l[e] : -INFINITY;
+        mx = fmaxf(mx, v[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+        const int e = lane + 32 * i;
+        v[i] = e < experts ? expf(v[i] - mx) : 0.0f;
+        sum += v[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+#pragma unroll
+    for (int i = 0; i < PER; i++) v[i] = (lane + 32 * i) < experts ? v[i] / sum : -1.0f;
+
+    float denom = 0.0f, picked_w[MOE_MAX_TOPK];
+    int picked_e[MOE_MAX_TOPK];
+    for (int s = 0; s < top_k; s++) {
+        float best = -2.0f;
+        int best_e = 0x7FFFFFFF;
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const int e = lane + 32 * i;
+            if (v[i] > best) { best = v[i]; best_e = e; } // increasing e within a lane: first maximum wins
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+            const int oe = __shfl_xor_sync(0xFFFFFFFFu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        picked_w[s] = best;
+        picked_e[s] = best_e;
+        denom += best;
+        if ((best_e & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < PER; i++)
+                if (lane + 32 * i == best_e) v[i] = -1.0f; // taken
+        }
+    }
+    if (lane == 0)
+        for (int s = 0; s < top_k; s++) {
+            top_idx[(size_t)warp * top_k + s] = picked_e[s];
+            top_w[(size_t)warp * top_k + s] = norm_topk ? picked_w[s] / denom : picked_w[s];
+        }
+}
+
+// counts[e - e_lo] = number of (token, slot) pairs routed to expert e, for e in [e_lo, e_hi).
+__global__ void __launch_bounds__(256)
+moe_count_kernel(const int *__restrict__ top_idx, int pairs, int e_lo, int *__restrict__ counts)
+{
+    __shared__ int part[8];
+    const int e = e_lo + blockIdx.x;
+    int c = 0;
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) c += top_idx[i] == e;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int w = 0; w < 8; w++) t += part[w];
+        counts[blockIdx.x] = t;
+    }
+}
+
+// offsets = exclusive scan of counts; m-tile table (128 rows each) per expert in ascending order;
+// grp_beg[g] = first m tile of expert group g (experts_per_group experts each).
+__global__ void moe_plan_kernel(const int *__restrict__ counts, int n_exp, int e_lo, int experts_per_group,
+                                int *__restrict__ offsets, int4 *__restrict__ entries, int *__restrict__ grp_beg)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int off = 0, mt = 0, g = 0;
+    for (int i = 0; i < n_exp; i++) {
+        if (i % experts_per_group == 0) grp_beg[g++] = mt;
+        offsets[i] = off;
+        const int c = counts[i];
+        for (int r = 0; r < c; r += 128) entries[mt++] = make_int4(off + r, min(128, c - r), e_lo + i, 0);
+        off += c;
+    }
+    offsets[n_exp] = off;
+    grp_beg[g] = mt;
+}
+
+// Stable partition: position of pair i among the pairs of its expert, in pair (= token) order.
+// One CTA per expert; a block-wide ballot scan keeps the order deterministic.
+__global__ void __launch_bounds__(1024)
+moe_scatter_kernel(const int *__restrict__ top_idx, int pairs, int e_lo, const int *__restrict__ offsets,
+                   int *__restrict__ perm, int *__restrict__ inv)
+{
+    __shared__ int warp_cnt[32];
+    __shared__ int base_s;
+    const int e = e_lo + blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) base_s = offsets[blockIdx.x];
+    __syncthreads();
+    for (int start = 0; start < pairs; start += 1024) {
+        const int i = start + threadIdx.x;
+        const bool hit = i < pairs && top_idx[i] == e;
+        const unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
+        if (lane == 0) warp_cnt[warp] = __popc(ballot);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < 32; w++) {
+            const int c = warp_cnt[w];
+            if (w < warp) before += c;
+            total += c;
+        }
+        if (hit) {
+            const int pos = base_s + before + __popc(ballot & ((1u << lane) - 1u));
+            perm[pos] = i;
+            inv[i] = pos;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) base_s += total;
+        __syncthreads();
+    }
+}
+
+// xs[pos, :] = x[perm[pos] / top_k, :]  (one warp per row, 16-byte copies)
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const __nv_bfloat16 *__restrict__ x, const int *__restrict__ perm, const int *__restrict__ total_rows,
+                  int top_k, int hidden, __nv_bfloat16 *__restrict__ xs)
+{
+    const int rows = *total_rows;
+    const int lane = threadIdx.x & 31;
+    for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < rows; row += (gridDim.x * blockDim.x) >> 5) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(x + (size_t)(perm[row] / top_k) * hidden);
+        uint4 *dst = reinterpret_cast<uint4 *>(xs + (size_t)row * hidden);
+        for (int c = lane; c < hidden / 8; c += 32) dst[c] = src[c];
+    }
+}
+
+// out[t, :] = sum over the token's slots whose expert is in [e_lo, e_hi), in ascending expert id,
+// of w * yp[inv[pair], :] (f32 accumulation, one rounding). Tokens without such a slot get zeros.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16 *__restrict__ yp, const int *__restrict__ top_idx, const float *__restrict__ top_w,
+                   const int *__restrict__ inv, int tokens, int top_k, int hidden, int e_lo, int e_hi, void *out,
+                   int out_dtype)
+{
+    const int chunks = hidden / 8;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < (size_t)tokens * chunks;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / chunks), c = (int)(idx % chunks);
+        int order[MOE_MAX_TOPK];
+        for (int s = 0; s < top_k; s++) order[s] = s;
+        for (int a = 1; a < top_k; a++) // insertion sort by expert id (k <= 8)
+            for (int b = a; b > 0 && top_idx[(size_t)t * top_k + order[b]] < top_idx[(size_t)t * top_k + order[b - 1]]; b--) {
+                const int tmp = order[b]; order[b] = order[b - 1]; order[b - 1] = tmp;
+            }
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int s = 0; s < top_k; s++) {
+            const size_t pair = (size_t)t * top_k + order[s];
+            const int e = top_idx[pair];
+            if (e < e_lo || e >= e_hi) continue;
+            const float w = top_w[pair];
+            const uint4 v = reinterpret_cast<const uint4 *>(yp + (size_t)inv[pair] * hidden)[c];
+            const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                acc[2 * q] = fmaf(w, __uint_as_float(vv[q] << 16), acc[2 * q]);
+                acc[2 * q + 1] = fmaf(w, __uint_as_float(vv[q] & 0xFFFF0000u), acc[2 * q + 1]);
+            }
+        }
+        for (int q = 0; q < 8; q++) store_as(out, out_dtype, (size_t)t * hidden + c * 8 + q, acc[q]);
+    }
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct MoeLayout {
+    size_t top_idx, top_w, counts, offsets, grp_beg, entries, perm, inv, xs, h, slab, total;
+    int group_experts, n_groups, max_mt;
+};
+
+static MoeLayout moe_layout(int tokens, int top_k, int n_exp, int hidden, int inter)
+{
+    MoeLayout L;
+    const size_t pairs = (size_t)tokens * top_k;
+    // Experts dequantized at once: as many as fit 144 MiB of bf16 gate_up weights, at least one.
+    const size_t per_expert = (size_t)2 * inter * hidden * 2;
+    int ge = (int)((144u << 20) / per_expert);
+    if (ge < 1) ge = 1;
+    if (ge > n_exp) ge = n_exp;
+    L.group_experts = ge;
+    L.n_groups = (n_exp + ge - 1) / ge;
+    L.max_mt = (int)(pairs / 128) + n_exp + 1;
+    size_t off = 256;
+    L.top_idx = off; off = align_up(off + pairs * 4, 256);
+    L.top_w = off; off = align_up(off + pairs * 4, 256);
+    L.counts = off; off = align_up(off + (size_t)n_exp * 4, 256);
+    L.offsets = off; off = align_up(off + (size_t)(n_exp + 1) * 4, 256);
+    L.grp_beg = off; off = align_up(off + (size_t)(L.n_groups + 1) * 4, 256);
+    L.entries = off; off = align_up(off + (size_t)L.max_mt * 16, 256);
+    L.perm = off; off = align_up(off + pairs * 4, 256);
+    L.inv = off; off = align_up(off + pairs * 4, 256);
+    L.xs = off; off = align_up(off + (pairs + 128) * hidden * 2, 256); // also the down-projection output
+    L.h = off; off = align_up(off + (pairs + 128) * inter * 2, 256);
+    L.slab = off; off = align_up(off + (size_t)ge * per_expert, 256);
+    L.total = off;
+    return L;
+}
+
+} // namespace oxq
+
+using namespace oxq;
+
+OXQ_EXPORT size_t oxq_gptoss_moe_workspace_bytes(int tokens, int top_k, int num_local_experts, int hidden, int inter)
+{
+    if (tokens <= 0 || top_k <= 0 || num_local_experts <= 0 || hidden <= 0 || inter <= 0) return 0;
+    return moe_layout(tokens, top_k, num_local_experts, hidden, inter).total;
+}
+
+OXQ_EXPORT int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *router_logits, int tokens, int num_experts,
+                                      int top_k, int norm_topk, int hidden, int inter, const uint8_t *gu_blocks,
+                                      const uint8_t *gu_scales, const void *gu_bias, const uint8_t *dn_blocks,
+                                      const uint8_t *dn_scales, const void *dn_bias, int bias_dtype, float limit,
+                                      int expert_lo, int expert_hi, void *out, int out_dtype, void *workspace,
+                                      size_t workspace_bytes, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(x && router_logits && gu_blocks && gu_scales && dn_blocks && dn_scales && out, OXQ_ERR_NULL,
+                "oxq_gptoss_moe_forward: null pointer");
+    OXQ_REQUIRE(x_dtype == OXQ_BF16, OXQ_ERR_UNSUPPORTED, "oxq_gptoss_moe_forward: activations must be bf16");
+    OXQ_REQUIRE(valid_dtype(out_dtype) && (!(gu_bias || dn_bias) || valid_dtype(bias_dtype)), OXQ_ERR_UNSUPPORTED,
+                "oxq_gptoss_moe_forward: unsupported dtype");
+    OXQ_REQUIRE(tokens > 0 && num_experts > 0 && num_experts <= MOE_MAX_EXPERTS && top_k > 0 && top_k <= MOE_MAX_TOPK &&
+                    top_k <= num_experts,
+                OXQ_ERR_BAD_SHAPE, "oxq_gptoss_moe_forward: tokens %d, experts %d (max %d), top_k %d (max %d)", tokens,
+                num_experts, MOE_MAX_EXPERTS, top_k, MOE_MAX_TOPK);
+    OXQ_REQUIRE(hidden % 32 == 0 && inter % 32 == 0, OXQ_ERR_BAD_SHAPE,
+                "Mxfp4Linear: in_features (%d, %d) must be a multiple of 32", hidden, inter);
+    OXQ_REQUIRE(0 <= expert_lo && expert_lo < expert_hi && expert_hi <= num_experts, OXQ_ERR_BAD_SHAPE,
+                "oxq_gptoss_moe_forward: expert range [%d, %d) outside 0..%d", expert_lo, expert_hi, num_experts);
+    const int n_exp = expert_hi - expert_lo;
+    const MoeLayout L = moe_layout(tokens, top_k, n_exp, hidden, inter);
+    OXQ_REQUIRE(workspace && workspace_bytes >= L.total, OXQ_ERR_WORKSPACE,
+                "oxq_gptoss_moe_forward: workspace of %zu bytes needed, got %zu", L.total, workspace_bytes);
+    OXQ_REQUIRE(aligned(workspace, 256) && aligned(x, 16), OXQ_ERR_BAD_ALIGN,
+                "oxq_gptoss_moe_forward: workspace must be 256-byte and x 16-byte aligned");
+
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned char *ws = reinterpret_cast<unsigned char *>(workspace);
+    int *flag = reinterpret_cast<int *>(ws);
+    int *top_idx = reinterpret_cast<int *>(ws + L.top_idx);
+    float *top_w = reinterpret_cast<float *>(ws + L.top_w);
+    int *counts = reinterpret_cast<int *>(ws + L.counts), *offsets = reinterpret_cast<int *>(ws + L.offsets);
+    int *grp_beg = reinterpret_cast<int *>(ws + L.grp_beg);
+    int4 *entries = reinterpret_cast<int4 *>(ws + L.entries);
+    int *perm = reinterpret_cast<int *>(ws + L.perm), *inv = reinterpret_cast<int *>(ws + L.inv);
+    __nv_bfloat16 *xs = reinterpret_cast<__nv_bfloat16 *>(ws + L.xs), *h = reinterpret_cast<__nv_bfloat16 *>(ws + L.h);
+    __nv_bfloat16 *slab = reinterpret_cast<__nv_bfloat16 *>(ws + L.slab);
+    const int pairs = tokens * top_k;
+
+    OXQ_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), st));
+    moe_route_kernel<<<ceil_div(tokens * 32, 256), 256, 0, st>>>(router_logits, tokens, num_experts, top_k, norm_topk,
+                                                                 top_idx, top_w);
+    moe_count_kernel<<<n_exp, 256, 0, st>>>(top_idx, pairs, expert_lo, counts);
+    moe_plan_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, L.group_experts, offsets, entries, grp_beg);
+    moe_scatter_kernel<<<n_exp, 1024, 0, st>>>(top_idx, pairs, expert_lo, offsets, perm, inv);
+    moe_gather_kernel<<<148 * 8, 256, 0, st>>>((const __nv_bfloat16 *)x, perm, offsets + n_exp, top_k, hidden, xs);
+    OXQ_LAUNCH_CHECK("moe routing kernels");
+
+    const int a_rows = pairs + 128;
+    const size_t gu_rows = (size_t)2 * inter, nbh = hidden / 32, nbi = inter / 32;
+    for (int g = 0; g < L.n_groups; g++) { // gate_up + SwiGLU: h = act(xs . W_gu^T + b_gu)
+        const int e0 = expert_lo + g * L.group_experts;
+        const int ne = (e0 + L.group_experts <= expert_hi) ? L.group_experts : expert_hi - e0;
+        int rc = mxfp4_dequant_rows_bf16(gu_blocks + (size_t)e0 * gu_rows * nbh * 16, gu_scales + (size_t)e0 * gu_rows * nbh,
+                                         slab, hidden, 0, (int)(ne * gu_rows), st);
+        if (rc) return rc;
+        rc = gemm_grouped(xs, a_rows, slab, ne, e0, (int)gu_rows, hidden, entries, grp_beg, g, gu_bias, bias_dtype, h,
+                          inter, 1, limit, flag, st);
+        if (rc) return rc;
+    }
+    for (int g = 0; g < L.n_groups; g++) { // down: yp = h . W_dn^T + b_dn (into the xs buffer)
+        const int e0 = expert_lo + g * L.group_experts;
+        const int ne = (e0 + L.group_experts <= expert_hi) ? L.group_experts : expert_hi - e0;
+        int rc = mxfp4_dequant_rows_bf16(dn_blocks + (size_t)e0 * hidden * nbi * 16, dn_scales + (size_t)e0 * hidden * nbi,
+                                         slab, inter, 0, ne * hidden, st);
+        if (rc) return rc;
+        rc = gemm_grouped(h, a_rows, slab, ne, e0, hidden, inter, entries, grp_beg, g, dn_bias, bias_dtype, xs, hidden,
+                          0, limit, flag, st);
+        if (rc) return rc;
+    }
+    moe_combine_kernel<<<148 * 8, 256, 0, st>>>(xs, top_idx, top_w, inv, tokens, top_k, hidden, expert_lo, expert_hi, out,
+                                                out_dtype);
+    OXQ_LAUNCH_CHECK("moe_combine_kernel");
+    return OXQ_OK;
+}
+
+// Routing alone (moe.rs:472-487): top_idx i32 [tokens, top_k], top_w f32 [tokens, top_k].
+OXQ_EXPORT int oxq_moe_route(const float *router_logits, int tokens, int num_experts, int top_k, int norm_topk,
+                             int32_t *top_idx, float *top_w, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(router_logits && top_idx && top_w, OXQ_ERR_NULL, "oxq_moe_route: null pointer");
+    OXQ_REQUIRE(tokens > 0 && num_experts > 0 && num_experts <= MOE_MAX_EXPERTS && top_k > 0 && top_k <= MOE_MAX_TOPK &&
+                    top_k <= num_experts,
+                OXQ_ERR_BAD_SHAPE, "oxq_moe_route: tokens %d, experts %d (max %d), top_k %d (max %d)", tokens, num_experts,
+                MOE_MAX_EXPERTS, top_k, MOE_MAX_TOPK);
+    moe_route_kernel<<<ceil_div(tokens * 32, 256), 256, 0, (cudaStream_t)stream>>>(router_logits, tokens, num_experts,
+                                                                                    top_k, norm_topk, top_idx, top_w);
+    OXQ_LAUNCH_CHECK("moe_route_kernel");
+    return OXQ_OK;
+}

@@ -1,0 +1,89 @@
+"""GPT-OSS MXFP4 MoE layer on the device against the CPU oracle (f32 chain of the reference's CPU path).
+Tolerance: max|err| <= 2e-2 * ||row||_inf (bf16 activations between the two expert GEMMs)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oxydllm_b200 import moe, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    return (t.to(dtype) if dtype is not None else t).cuda()
+
+
+def build(d):
+    return moe.GptOssMoe(dev(d["gu_blocks"]), dev(d["gu_scales"]), dev(d["gu_bias"], torch.bfloat16),
+                         dev(d["dn_blocks"]), dev(d["dn_scales"]), dev(d["dn_bias"], torch.bfloat16),
+                         hidden=d["x"].shape[1], inter=d["dn_blocks"].shape[2] * 32, top_k=4)
+
+
+@pytest.mark.parametrize("tokens,experts", [(1, 4), (5, 32), (64, 32), (777, 8)])
+def test_route_matches_oracle(cuda, tokens, experts):
+    logits = np.random.default_rng(tokens).standard_normal((tokens, experts)).astype(np.float32)
+    k = min(4, experts)
+    idx, w = moe.route(dev(logits), k)
+    ridx, rw = oracle.moe_route(logits, k, True)
+    assert np.array_equal(idx.cpu().numpy(), ridx)  # N(0,1) logits: no ties
+    assert np.allclose(w.cpu().numpy(), rw, rtol=1e-5, atol=1e-7)
+    idx2, w2 = moe.route(dev(logits), k, norm_topk=False)
+    _, rw2 = oracle.moe_route(logits, k, False)
+    assert np.allclose(w2.cpu().numpy(), rw2, rtol=1e-5, atol=1e-7)
+
+
+def test_route_ties_take_lower_index(cuda):
+    logits = np.zeros((3, 8), np.float32)
+    idx, w = moe.route(dev(logits), 4)
+    assert idx.cpu().tolist() == [[0, 1, 2, 3]] * 3
+    assert np.allclose(w.cpu().numpy(), 0.25)
+
+
+@pytest.mark.parametrize("tokens,experts,hidden,inter", [(40, 4, 64, 64), (300, 8, 128, 96), (129, 32, 256, 256),
+                                                         (3, 4, 64, 32)])
+def test_moe_layer_matches_oracle(cuda, tokens, experts, hidden, inter):
+    d = synth.gptoss_moe(experts, hidden, inter, tokens, seed=tokens)
+    # larger weights than N(0, 0.02) so that the clamps and the sigmoid gate are exercised
+    rng = np.random.default_rng(1)
+    d["x"] = synth.bf16_round(rng.standard_normal((tokens, hidden)).astype(np.float32) * 4.0)
+    layer = build(d)
+    y = layer.forward_with_logits(dev(d["x"], torch.bfloat16), dev(d["logits"]))
+    layer.check()
+    idx, w = oracle.moe_route(d["logits"], 4, True)
+    ref = oracle.gptoss_moe(d["x"], idx, w, d["gu_blocks"], d["gu_scales"], d["gu_bias"], d["dn_blocks"], d["dn_scales"],
+                            d["dn_bias"], hidden, inter, 7.0)
+    got = y.float().cpu().numpy()
+    assert got.shape == ref.shape and np.isfinite(got).all()
+    row_inf = np.abs(ref).max(axis=1, keepdims=True)
+    assert (np.abs(got - ref) <= 2e-2 * row_inf + 1e-5).all(), np.abs(got - ref).max()
+
+
+def test_moe_expert_ranges_add_up_and_are_deterministic(cuda):
+    d = synth.gptoss_moe(8, 128, 128, 200, seed=5)
+    layer = build(d)
+    x, lg = dev(d["x"], torch.bfloat16), dev(d["logits"])
+    full = layer.forward_with_logits(x, lg).float()
+    again = layer.forward_with_logits(x, lg).float()
+    assert torch.equal(full, again)
+    parts = sum(layer.forward_with_logits(x, lg, (lo, lo + 2)).float() for lo in range(0, 8, 2))
+    layer.check()
+    assert torch.allclose(parts, full, rtol=2e-2, atol=2e-2 * float(full.abs().max()))
+    ref_lo = oracle.gptoss_moe(d["x"], *oracle.moe_route(d["logits"], 4, True), d["gu_blocks"], d["gu_scales"], d["gu_bias"],
+                               d["dn_blocks"], d["dn_scales"], d["dn_bias"], 128, 128, 7.0, expert_range=(0, 2))
+    got_lo = layer.forward_with_logits(x, lg, (0, 2)).float().cpu().numpy()
+    assert (np.abs(got_lo - ref_lo) <= 2e-2 * np.abs(ref_lo).max(axis=1, keepdims=True) + 1e-4).all()
+
+
+def test_moe_gpt_oss_shape_slice(cuda):
+    """GPT-OSS-20B expert shape (hidden = inter = 2880, 45 k blocks of 64) with 4 experts and 256 tokens."""
+    d = synth.gptoss_moe(4, 2880, 2880, 256, seed=9)
+    layer = build(d)
+    y = layer.forward_with_logits(dev(d["x"], torch.bfloat16), dev(d["logits"]))
+    layer.check()
+    idx, w = oracle.moe_route(d["logits"], 4, True)
+    ref = oracle.gptoss_moe(d["x"], idx, w, d["gu_blocks"], d["gu_scales"], d["gu_bias"], d["dn_blocks"], d["dn_scales"],
+                            d["dn_bias"], 2880, 2880, 7.0)
+    got = y.float().cpu().numpy()
+    assert (np.abs(got - ref) <= 2e-2 * np.abs(ref).max(axis=1, keepdims=True) + 1e-5).all()
