@@ -1,0 +1,183 @@
+"""Multi-GPU forms of the two operators that shard naturally (one process per GPU, torch.distributed).
+
+* Tensor parallel column split of a packed linear + all-gather of the outputs. AWQ packs 8
+  consecutive out columns per word, so any split at a multiple of 8 columns is a pure slice of
+  ``qweight[:, a/8:b/8]``, ``qzeros[:, a/8:b/8]``, ``scales[:, a:b]`` -- the property
+  ``concat_awq_along_out`` relies on (awq.rs:256-323). The reference itself has no multi-GPU
+  execution; parity is "sharded result == unsharded result".
+* Expert parallel GPT-OSS MoE with all-to-all token dispatch and combine: experts are independent
+  and the combine is a sum (moe.rs:593-605). Tokens start data-parallel; each rank routes its own
+  tokens, sends every (token, slot) row to the rank that owns the expert, runs its local experts
+  on what it received, sends the rows back, and the owner of the token adds them in ascending
+  expert order.
+
+The index arithmetic lives in plain functions (``column_shard``, ``expert_shard``,
+``plan_dispatch``, ``combine_rows``) so that it can be exercised with gloo on CPU; the classes bind
+them to the CUDA operators.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+# ----------------------------------------------------------------------------- sharding arithmetic
+def column_shard(n: int, world: int, rank: int, multiple: int = 8) -> tuple[int, int]:
+    """Out-column range ``[a, b)`` of ``rank``: near-equal shards whose bounds are multiples of ``multiple``."""
+    if n % multiple:
+        raise ValueError(f"out_features {n} not divisible by {multiple}")
+    units = n // multiple
+    base, rem = divmod(units, world)
+    a = rank * base + min(rank, rem)
+    b = a + base + (1 if rank < rem else 0)
+    return a * multiple, b * multiple
+
+
+def expert_shard(num_experts: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous expert range ``[lo, hi)`` owned by ``rank``."""
+    base, rem = divmod(num_experts, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+def owner_of_expert(expert: torch.Tensor, num_experts: int, world: int) -> torch.Tensor:
+    """Rank that owns each expert id under :func:`expert_shard`."""
+    base, rem = divmod(num_experts, world)
+    cut = rem * (base + 1)
+    if base == 0:
+        return expert.clone()
+    return torch.where(expert < cut, expert // (base + 1), rem + (expert - cut) // base)
+
+
+def plan_dispatch(top_idx: torch.Tensor, num_experts: int, world: int):
+    """Order in which this rank's (token, slot) pairs are sent: grouped by destination rank, pair order kept.
+
+    Returns ``(send_order, send_counts)``: ``send_order[i]`` is the flat pair index (token * k + slot)
+    of the i-th row sent, ``send_counts[r]`` the number of rows going to rank ``r``.
+    """
+    flat = top_idx.reshape(-1).to(torch.int64)
+    dest = owner_of_expert(flat, num_experts, world)
+    send_order = torch.sort(dest, stable=True).indices
+    send_counts = torch.bincount(dest, minlength=world)
+    return send_order, send_counts
+
+
+def combine_rows(rows: torch.Tensor, send_order: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum over slots, in ascending expert id, of top_w[t, s] * rows[position of pair (t, s)] (f32 accumulate)."""
+    t, k = top_idx.shape
+    pos = torch.empty_like(send_order)
+    pos[send_order] = torch.arange(send_order.numel(), device=send_order.device)
+    per_pair = rows.to(torch.float32)[pos].reshape(t, k, -1)
+    order = torch.sort(top_idx.to(torch.int64), dim=1, stable=True).indices
+    acc = torch.zeros((t, rows.shape[1]), dtype=torch.float32, device=rows.device)
+    for s in range(k):
+        sel = order[:, s]
+        w = torch.gather(top_w, 1, sel[:, None])
+        acc += w * torch.gather(per_pair, 1, sel[:, None, None].expand(t, 1, per_pair.shape[2]))[:, 0]
+    return acc
+
+
+def all_to_all_rows(rows: torch.Tensor, send_counts: Sequence[int], recv_counts: Sequence[int], group=None) -> torch.Tensor:
+    """Variable-size all-to-all of matrix rows (works for NCCL and gloo)."""
+    out = rows.new_empty((int(sum(recv_counts)),) + tuple(rows.shape[1:]))
+    dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=[int(c) for c in recv_counts],
+                           input_split_sizes=[int(c) for c in send_counts], group=group)
+    return out
+
+
+def exchange_counts(send_counts: torch.Tensor, group=None) -> torch.Tensor:
+    recv = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv, send_counts, group=group)
+    return recv
+
+
+# ----------------------------------------------------------------------------- tensor parallel linear
+class ColumnParallelLinear:
+    """Column-split linear: ``local`` computes ``x @ W[a:b]^T``; ``forward`` all-gathers the shards.
+
+    ``local`` is any callable ``x[m, k] -> y[m, b - a]`` (an operator of :mod:`linear` built on the
+    sliced tensors). ``chunks`` > 1 cuts the batch into row chunks and overlaps the all-gather of one
+    chunk with the matmul of the next.
+    """
+
+    def __init__(self, local: Callable[[torch.Tensor], torch.Tensor], out_features: int, group=None, chunks: int = 1,
+                 multiple: int = 8):
+        self.local, self.n, self.group, self.chunks = local, out_features, group, max(1, chunks)
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.bounds = [column_shard(out_features, self.world, r, multiple) for r in range(self.world)]
+        self.width = max(b - a for a, b in self.bounds)
+
+    @staticmethod
+    def slice_awq(qweight, qzeros, scales, a: int, b: int):
+        """Columns ``[a, b)`` of an AWQ triplet (pure slices of the packed tensors)."""
+        return qweight[:, a // 8:b // 8].contiguous(), qzeros[:, a // 8:b // 8].contiguous(), scales[:, a:b].contiguous()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        m = x.shape[0]
+        out = x.new_empty((m, self.n))
+        step = (m + self.chunks - 1) // self.chunks
+        pending = []
+        for r0 in range(0, m, step):
+            r1 = min(m, r0 + step)
+            y = self.local(x[r0:r1])
+            if y.shape[1] != self.width:  # uneven shards: pad to the widest so the gather is regular
+                y = torch.nn.functional.pad(y, (0, self.width - y.shape[1]))
+            flat = y.new_empty((self.world * (r1 - r0), self.width))  # rank-major concatenation
+            work = dist.all_gather_into_tensor(flat, y.contiguous(), group=self.group, async_op=True)
+            pending.append((work, flat.view(self.world, r1 - r0, self.width), r0, r1))
+        for work, gathered, r0, r1 in pending:
+            work.wait()
+            for r, (a, b) in enumerate(self.bounds):
+                out[r0:r1, a:b] = gathered[r, :, :b - a]
+        return out
+
+
+# ----------------------------------------------------------------------------- expert parallel MoE
+class ExpertParallelMoe:
+    """All-to-all expert parallelism around a local expert function.
+
+    ``route(logits) -> (top_idx int32 [t, k], top_w f32 [t, k])`` and
+    ``local_experts(rows[r, hidden], expert_ids[r]) -> y[r, hidden]`` (each row through its expert,
+    weight 1) are supplied by the caller: the CUDA operators in production, anything else in tests.
+    """
+
+    def __init__(self, num_experts: int, route: Callable, local_experts: Callable, group=None):
+        self.num_experts, self.route, self.local_experts, self.group = num_experts, route, local_experts, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        top_idx, top_w = self.route(logits)
+        k = top_idx.shape[1]
+        send_order, send_counts = plan_dispatch(top_idx, self.num_experts, self.world)
+        recv_counts = exchange_counts(send_counts, self.group)
+        sc, rc = send_counts.tolist(), recv_counts.tolist()  # the one host read-back: buffer sizes
+        rows = x[send_order // k]
+        ids = top_idx.reshape(-1)[send_order].to(torch.int32)
+        got_rows = all_to_all_rows(rows, sc, rc, self.group)
+        got_ids = all_to_all_rows(ids[:, None], sc, rc, self.group)[:, 0]
+        y = self.local_experts(got_rows, got_ids) if got_rows.shape[0] else got_rows
+        back = all_to_all_rows(y.to(x.dtype), rc, sc, self.group)
+        return combine_rows(back, send_order, top_idx, top_w).to(x.dtype)
+
+
+def gptoss_local_experts(layer) -> Callable:
+    """``local_experts`` callable over a :class:`moe.GptOssMoe` holding ALL expert tensors (only the local
+    ones are touched): each received row goes through its expert with weight one."""
+    def run(rows: torch.Tensor, expert_ids: torch.Tensor) -> torch.Tensor:
+        e = layer.num_experts
+        # one-hot logits: softmax puts all mass on the row's expert; top-1 routing then reproduces the given ids
+        logits = torch.full((rows.shape[0], e), -30000.0, dtype=torch.float32, device=rows.device)
+        logits.scatter_(1, expert_ids.to(torch.int64)[:, None], 0.0)
+        saved = layer.top_k
+        layer.top_k = 1
+        try:
+            world = dist.get_world_size() if dist.is_initialized() else 1
+            rank = dist.get_rank() if dist.is_initialized() else 0
+            return layer.forward_with_logits(rows, logits, expert_shard(e, world, rank))
+        finally:
+            layer.top_k = saved
+    return run
