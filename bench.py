@@ -216,6 +216,10 @@ def run_gpu(args):
         torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
 
+    extras = None
+    if not args.no_extras:
+        extras = run_extras(args, world, rank, layers[0])
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_baseline(budget_s=12.0)
@@ -250,8 +254,163 @@ def run_gpu(args):
     }
     if cpu is not None:
         out["cpu_baseline"] = cpu
+    if extras is not None:
+        out["other_configs"] = extras
     print(json.dumps(out), flush=True)
 
+
+
+# --------------------------------------------------------------------------- other configurations
+def _timed_ms(torch, dist, world, fn, iters):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def run_extras(args, world, rank, c1_layer):
+    """Configs 0, 2, 3, 4 of BASELINE.json (single-GPU legs on every rank's own GPU; TP/EP legs when world > 1)."""
+    import torch
+    import torch.distributed as dist
+
+    from oxydllm_b200 import formats as F
+    from oxydllm_b200 import gemm, moe, parallel, synth
+    from oxydllm_b200 import linear as L
+
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except Exception:
+        pass
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    tf_burst = float(peaks.get("bf16_tflops", 1590.0))
+    out = {}
+    dev = lambda a, dt=None: (torch.from_numpy(np.ascontiguousarray(a)).to(dt) if dt else torch.from_numpy(np.ascontiguousarray(a))).cuda()
+
+    def graph_us(fn_once, launches, reps=20):
+        fn_once(); torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn_once()
+        for _ in range(3):
+            g.replay()
+        return _timed_ms(torch, dist, world, g.replay, reps) * 1e3 / launches
+
+    # ---- C0: GGUF Q4_K GEMV, N = K = 4096, M = 1 (16 distinct copies: 151 MB > L2)
+    try:
+        n = k = 4096
+        copies = [L.QLinear(F.GGML_Q4_K, dev(synth.gguf_layer(F.GGML_Q4_K, n, k, seed=100 * rank + i)), n, k) for i in range(2)]
+        base = copies[0].blocks
+        lins = copies + [L.QLinear(F.GGML_Q4_K, torch.roll(base, 144 * (i + 1)), n, k) for i in range(14)]
+        x = dev(synth.activations(1, k, seed=1), torch.bfloat16)
+        us = graph_us(lambda: [lin.forward(x) for lin in lins], len(lins))
+        b = n * (k // 256) * 144 + k * 2 + n * 2
+        out["c0_q4k_gemv_m1"] = {"us_per_launch": round(us, 2), "gbs": round(b / us / 1e3, 1),
+                                  "frac_of_hbm_peak": round(b / us / 1e3 / hbm, 4), "algorithmic_bytes": b}
+        del lins, copies
+    except Exception as e:  # keep the headline line alive
+        out["c0_q4k_gemv_m1"] = {"error": str(e)[:200]}
+
+    # ---- C2: AWQ prefill GEMM M = 2048, K = 4096, N in {4096, 14336}
+    try:
+        m = 2048
+        x = dev(synth.activations(m, K, seed=2), torch.bfloat16)
+        res = {}
+        for n in (4096, 14336):
+            a, b_ = 0, n
+            qw, qz, sc = parallel.ColumnParallelLinear.slice_awq(c1_layer.qweight, c1_layer.qzeros, c1_layer.scales, a, b_)
+            lin = L.PackedQuantLinear(L.QuantWeight.new_awq(4, qw, qz, sc))
+            y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+            for _ in range(3):
+                gemm.awq_matmul(lin, x, y)
+            ms = _timed_ms(torch, dist, world, lambda: gemm.awq_matmul(lin, x, y), 10)
+            tf = 2.0 * m * n * K / ms / 1e9
+            res[f"n{n}"] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_bf16_burst_peak": round(tf / tf_burst, 4)}
+        gemm.check(gemm.workspace(1, 8, "cuda"))
+        if world > 1:  # tensor-parallel column split of N = 14336 + all-gather
+            n = 14336
+            a, b_ = parallel.column_shard(n, world, rank)
+            qw, qz, sc = parallel.ColumnParallelLinear.slice_awq(c1_layer.qweight, c1_layer.qzeros, c1_layer.scales, a, b_)
+            shard = L.PackedQuantLinear(L.QuantWeight.new_awq(4, qw, qz, sc))
+            tp = parallel.ColumnParallelLinear(shard.forward, n, chunks=2)
+            for _ in range(3):
+                tp.forward(x)
+            ms = _timed_ms(torch, dist, world, lambda: tp.forward(x), 10)
+            tf = 2.0 * m * n * K / ms / 1e9
+            res[f"n{n}_tp{world}_allgather"] = {"ms": round(ms, 4), "tflops_whole_job": round(tf, 1)}
+        out["c2_awq_gemm_m2048"] = res
+    except Exception as e:
+        out["c2_awq_gemm_m2048"] = {"error": str(e)[:200]}
+
+    # ---- C3: FP8 E4M3 128x128-block GEMV (M = 1, 32) and GEMM (M = 2048), N = 14336, K = 4096
+    try:
+        n = 14336
+        q, s_ = synth.fp8_layer(n, K, seed=3 + rank)
+        base = dev(q)
+        lins = [L.Fp8Linear(base, dev(s_))] + [L.Fp8Linear(torch.roll(base, 4096 * (i + 1), 0), dev(s_)) for i in range(3)]
+        res = {}
+        for m in (1, 32):
+            x = dev(synth.activations(m, K, seed=m), torch.bfloat16)
+            us = graph_us(lambda: [lin.forward(x) for lin in lins], len(lins))
+            b = n * K + (n // 128) * (K // 128) * 4 + m * (2 * K + 2 * n)
+            res[f"gemv_m{m}"] = {"us_per_launch": round(us, 2), "gbs": round(b / us / 1e3, 1),
+                                 "frac_of_hbm_peak": round(b / us / 1e3 / hbm, 4)}
+        x = dev(synth.activations(2048, K, seed=5), torch.bfloat16)
+        for _ in range(3):
+            lins[0].forward(x)
+        ms = _timed_ms(torch, dist, world, lambda: lins[0].forward(x), 10)
+        tf = 2.0 * 2048 * n * K / ms / 1e9
+        res["gemm_m2048"] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_bf16_burst_peak": round(tf / tf_burst, 4)}
+        out["c3_fp8_block"] = res
+        del lins, base
+    except Exception as e:
+        out["c3_fp8_block"] = {"error": str(e)[:200]}
+
+    # ---- C4: GPT-OSS-20B-shaped MXFP4 MoE layer, 32 experts, top-4, 4096 tokens
+    try:
+        e, hidden, inter, tokens = 32, 2880, 2880, 4096
+        d = synth.gptoss_moe(4, hidden, inter, tokens, seed=4)  # 4 distinct experts, tiled 8x (throughput is data-independent)
+        rep = lambda a: np.concatenate([a] * (e // 4), axis=0)
+        layer = moe.GptOssMoe(dev(rep(d["gu_blocks"])), dev(rep(d["gu_scales"])), dev(rep(d["gu_bias"]), torch.bfloat16),
+                              dev(rep(d["dn_blocks"])), dev(rep(d["dn_scales"])), dev(rep(d["dn_bias"]), torch.bfloat16),
+                              hidden=hidden, inter=inter, top_k=4)
+        lg = dev(np.random.default_rng(6).standard_normal((tokens, e)).astype(np.float32))
+        x = dev(d["x"], torch.bfloat16)
+        for _ in range(2):
+            layer.forward_with_logits(x, lg)
+        layer.check()
+        ms = _timed_ms(torch, dist, world, lambda: layer.forward_with_logits(x, lg), 5)
+        fl = tokens * 4 * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden)
+        res = {"ms": round(ms, 3), "tflops": round(fl / ms / 1e9, 1), "tokens_per_s": round(tokens / ms * 1e3, 0),
+               "frac_of_bf16_burst_peak": round(fl / ms / 1e9 / tf_burst, 4),
+               "note": "4 distinct experts tiled to 32; router logits N(0,1) given, router GEMM not timed"}
+        if world > 1:  # expert parallel: tokens data-parallel, all-to-all dispatch and combine
+            t_local = tokens // world
+            sl = slice(rank * t_local, (rank + 1) * t_local)
+            ep = parallel.ExpertParallelMoe(e, lambda l_: moe.route(l_, 4, True), parallel.gptoss_local_experts(layer))
+            xl, ll = x[sl].contiguous(), lg[sl].contiguous()
+            for _ in range(2):
+                ep.forward(xl, ll)
+            ms = _timed_ms(torch, dist, world, lambda: ep.forward(xl, ll), 5)
+            res[f"ep{world}_all_to_all"] = {"ms": round(ms, 3), "tflops_whole_job": round(fl / ms / 1e9, 1),
+                                            "tokens_per_s_whole_job": round(tokens / ms * 1e3, 0)}
+        out["c4_mxfp4_moe"] = res
+    except Exception as e:
+        out["c4_mxfp4_moe"] = {"error": str(e)[:200]}
+    return out
 
 # --------------------------------------------------------------------------- CPU arm
 def cpu_sweep_once(w_f32, xs):
@@ -321,6 +480,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip configurations 0, 2, 3, 4 (headline C1 line only)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
