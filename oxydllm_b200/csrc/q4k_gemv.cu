@@ -1,0 +1,260 @@
+// GGUF Q4_K decode GEMV (1 <= m <= 16), tuned variant.
+//
+// Q4_K super-block (144 B / 256 weights): f16 d, f16 dmin, 12 bytes of 6-bit sub-block scales and
+// mins, 128 bytes of nibbles; byte t of 32-byte group iq holds element t of sub-block 2*iq (low
+// nibble) and of sub-block 2*iq+1 (high nibble); w = (d*sc)*q - dmin*mn.
+//
+// A CTA owns 16 output rows; its 8 warps take super-blocks round-robin along k and are summed in
+// warp order through shared memory. Per super-block a lane streams, straight into registers, the
+// 16-byte header of its two rows (lane/4 and lane/4 + 8) and eight 8-byte pieces of nibbles: bytes
+// [8c, 8c+8) of each 32-byte group (c = lane%4), so the four lanes of a row read 32 contiguous
+// bytes. The k order inside a sub-block is free as long as x follows it, which lets every lane
+// feed the tensor cores from its own bytes with no exchange: nibbles become f16 pairs with one
+// lop3 each -- 0x6400 | q is 1024 + q, and 0x6400 | (q << 4) is 1024 + 16 q, so the high nibbles
+// need no shift -- and go into mma.sync m16n8k16 (f16 x f16 -> f32) as the 16-row operand.
+// x is staged once per CTA as f16 (saturated to +-65504) in the matching element order, together
+// with the per-sub-block sums of x; scale, min, the 1024 offset and the factor 16 are folded in
+// f32 once per sub-block:  y += d*sc * (acc - 1024*sum_x) / {1,16} - dmin*mn * sum_x.
+#include "formats.cuh"
+
+namespace oxq {
+
+struct Q4kGemvParams {
+    const __nv_bfloat16 *x;
+    const uint8_t *blocks;
+    const void *bias;
+    void *y;
+    int bias_dtype, y_dtype;
+    int m, k, n;
+};
+
+constexpr int Q4K_WARPS = 8;
+
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t p, uint32_t mask, uint32_t magic)
+{
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(p), "r"(mask), "r"(magic));
+    return r;
+}
+
+// Byte `idx` (0..3) of v as f32, exact, without the integer-to-float unit.
+__device__ __forceinline__ float byte_to_f32(uint32_t v, int idx)
+{
+    const uint32_t bits = __byte_perm(v, 0x4B000000u, 0x7440 + idx); // [byte idx, 0, 0, 0x4B] = 2^23 + byte
+    return __uint_as_float(bits) - 8388608.0f;
+}
+
+struct Q4kRow {
+    uint4 hdr;     // d | dmin << 16, scales[0..3], scales[4..7], scales[8..11]
+    uint2 qs[4];   // bytes [8c, 8c+8) of each 32-byte nibble group
+};
+
+__device__ __forceinline__ void q4k_load_row(Q4kRow &r, const uint8_t *blk, int c)
+{
+    r.hdr = __ldcs(reinterpret_cast<const uint4 *>(blk));
+#pragma unroll
+    for (int iq = 0; iq < 4; iq++) r.qs[iq] = __ldcs(reinterpret_cast<const uint2 *>(blk + 16 + 32 * iq + 8 * c));
+}
+
+// (d*sc, dmin*mn) of the eight sub-blocks of one row's super-block.
+__device__ __forceinline__ void q4k_scales(const uint4 &hdr, float (&dsc)[8], float (&dmn)[8])
+{
+    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+    const uint32_t sc_lo = hdr.y & 0x3F3F3F3Fu, mn_lo = hdr.z & 0x3F3F3F3Fu;
+    const uint32_t sc_hi = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+    const uint32_t mn_hi = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        dsc[j] = d * byte_to_f32(sc_lo, j);
+        dmn[j] = dmin * byte_to_f32(mn_lo, j);
+        dsc[4 + j] = d * byte_to_f32(sc_hi, j);
+        dmn[4 + j] = dmin * byte_to_f32(mn_hi, j);
+    }
+}
+
+template <int MT>
+__global__ void __launch_bounds__(Q4K_WARPS * 32) q4k_gemv_kernel(const Q4kGemvParams p)
+{
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+    const int n0 = blockIdx.x * 16;
+    const int nsb = p.k >> 8;                 // super-blocks per row
+    const size_t row_bytes = (size_t)nsb * 144;
+    const int xrow = p.k + 32;                // halves per staged token row: 64 bytes of padding keep the
+                                              // 16-byte fragment reads of a quarter warp on distinct banks
+    __half *xs = reinterpret_cast<__half *>(smem);
+    float *sx = reinterpret_cast<float *>(smem + (size_t)8 * MT * xrow * sizeof(__half)); // [k/32][8*MT]
+
+    // Rows past the end re-read the last row; their results are never stored.
+    const int r0 = min(n0 + g, p.n - 1), r1 = min(n0 + g + 8, p.n - 1);
+    const uint8_t *row0 = p.blocks + (size_t)r0 * row_bytes, *row1 = p.blocks + (size_t)r1 * row_bytes;
+    Q4kRow cur0, cur1;
+    int sb = warp;
+    if (sb < nsb) {
+        q4k_load_row(cur0, row0 + (size_t)sb * 144, c);
+        q4k_load_row(cur1, row1 + (size_t)sb * 144, c);
+    }
+
+    // Stage x as f16, elements of every group of four stored as [0, 2, 1, 3] (the order in which the
+    // nibble masks deliver k), then the per-sub-block sums of the staged values.
+    // Only real tokens are staged; lanes whose token does not exist feed zeros to the tensor cores.
+    for (int idx = tid; idx < p.m * (p.k >> 2); idx += Q4K_WARPS * 32) {
+        const int row = idx / (p.k >> 2), q4 = idx % (p.k >> 2);
+        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(p.x + (size_t)row * p.k) + q4);
+        float f[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+                      __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
+#pragma unroll
+        for (int u = 0; u < 4; u++) f[u] = fminf(fmaxf(f[u], -65504.0f), 65504.0f);
+        const __half2 h02 = __floats2half2_rn(f[0], f[2]), h13 = __floats2half2_rn(f[1], f[3]);
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t *>(&h02);
+        o.y = *reinterpret_cast<const uint32_t *>(&h13);
+        *reinterpret_cast<uint2 *>(xs + (size_t)row * xrow + 4 * q4) = o;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < p.m * (p.k >> 5); idx += Q4K_WARPS * 32) {
+        const int row = idx % p.m, sub = idx / p.m;
+        const __half2 *src = reinterpret_cast<const __half2 *>(xs + (size_t)row * xrow + 32 * sub);
+        float s = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 16; u++) {
+            const float2 v = __half22float2(src[u]);
+            s += v.x + v.y;
+        }
+        sx[sub * 8 * MT + row] = s;
+    }
+    __syncthreads();
+
+    float tot[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) tot[mt][0] = tot[mt][1] = tot[mt][2] = tot[mt][3] = 0.0f;
+    uint32_t mask_lo, mask_hi, magic; // kept opaque so that they stay in registers (one immediate per LOP3)
+    asm volatile("mov.b32 %0, 0x000F000F;\n\tmov.b32 %1, 0x00F000F0;\n\tmov.b32 %2, 0x64006400;"
+                 : "=r"(mask_lo), "=r"(mask_hi), "=r"(magic));
+
+    for (; sb < nsb; sb += Q4K_WARPS) {
+        Q4kRow nxt0 = cur0, nxt1 = cur1;
+        if (sb + Q4K_WARPS < nsb) { // next super-block on its way while this one is consumed
+            q4k_load_row(nxt0, row0 + (size_t)(sb + Q4K_WARPS) * 144, c);
+            q4k_load_row(nxt1, row1 + (size_t)(sb + Q4K_WARPS) * 144, c);
+        }
+        float dsc0[8], dmn0[8], dsc1[8], dmn1[8];
+        q4k_scales(cur0.hdr, dsc0, dmn0);
+        q4k_scales(cur1.hdr, dsc1, dmn1);
+#pragma unroll
+        for (int iq = 0; iq < 4; iq++) {
+            float acc_lo[MT][4], acc_hi[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc_lo[mt][e] = acc_hi[mt][e] = 0.0f;
+            const int sub_lo = sb * 8 + 2 * iq; // global sub-block index of the low nibbles
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                // lane c's eight elements of each sub-block, both k steps, in one 16-byte read
+                uint4 xl = make_uint4(0u, 0u, 0u, 0u), xh = xl;
+                if (8 * mt + g < p.m) {
+                    xl = *reinterpret_cast<const uint4 *>(xs + (size_t)(8 * mt + g) * xrow + 32 * sub_lo + 8 * c);
+                    xh = *reinterpret_cast<const uint4 *>(xs + (size_t)(8 * mt + g) * xrow + 32 * (sub_lo + 1) + 8 * c);
+                }
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const uint32_t w0 = j ? cur0.qs[iq].y : cur0.qs[iq].x, w1 = j ? cur1.qs[iq].y : cur1.qs[iq].x;
+                    const uint32_t a_lo[4] = {lop3_and_or(w0, mask_lo, magic), lop3_and_or(w1, mask_lo, magic),
+                                              lop3_and_or(w0 >> 8, mask_lo, magic), lop3_and_or(w1 >> 8, mask_lo, magic)};
+                    const uint32_t a_hi[4] = {lop3_and_or(w0, mask_hi, magic), lop3_and_or(w1, mask_hi, magic),
+                                              lop3_and_or(w0 >> 8, mask_hi, magic), lop3_and_or(w1 >> 8, mask_hi, magic)};
+                    const uint32_t b_lo[2] = {j ? xl.z : xl.x, j ? xl.w : xl.y};
+                    const uint32_t b_hi[2] = {j ? xh.z : xh.x, j ? xh.w : xh.y};
+                    mma_f16_16816(acc_lo[mt], a_lo, b_lo);
+                    mma_f16_16816(acc_hi[mt], a_hi, b_hi);
+                }
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                const float2 s_lo = *reinterpret_cast<const float2 *>(sx + (size_t)sub_lo * 8 * MT + 8 * mt + 2 * c);
+                const float2 s_hi = *reinterpret_cast<const float2 *>(sx + (size_t)(sub_lo + 1) * 8 * MT + 8 * mt + 2 * c);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float sl = (e & 1) ? s_lo.y : s_lo.x, sh = (e & 1) ? s_hi.y : s_hi.x;
+                    const float dl = (e >> 1) ? dsc1[2 * iq] : dsc0[2 * iq], ml = (e >> 1) ? dmn1[2 * iq] : dmn0[2 * iq];
+                    const float dh = (e >> 1) ? dsc1[2 * iq + 1] : dsc0[2 * iq + 1], mh = (e >> 1) ? dmn1[2 * iq + 1] : dmn0[2 * iq + 1];
+                    float t = tot[mt][e];
+                    t = fmaf(dl, fmaf(-1024.0f, sl, acc_lo[mt][e]), t);
+                    t = fmaf(-ml, sl, t);
+                    t = fmaf(dh * 0.0625f, fmaf(-1024.0f, sh, acc_hi[mt][e]), t);
+                    t = fmaf(-mh, sh, t);
+                    tot[mt][e] = t;
+                }
+            }
+        }
+        cur0 = nxt0;
+        cur1 = nxt1;
+    }
+
+    __syncthreads(); // x no longer needed: reuse the front of shared memory for the warp partials
+    float *red = reinterpret_cast<float *>(smem); // [warp][MT*4][lane]
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) red[(warp * MT * 4 + mt * 4 + e) * 32 + lane] = tot[mt][e];
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < Q4K_WARPS; w++) sum += red[(w * MT * 4 + mt * 4 + e) * 32 + lane];
+                const int nn = n0 + g + 8 * (e >> 1), row = 8 * mt + 2 * c + (e & 1);
+                if (nn < p.n && row < p.m) {
+                    if (p.bias) sum += load_as_f32(p.bias, p.bias_dtype, nn);
+                    store_as(p.y, p.y_dtype, (size_t)row * p.n + nn, sum);
+                }
+            }
+    }
+}
+
+template <int MT> static int launch_q4k(const Q4kGemvParams &p, cudaStream_t st)
+{
+    const size_t smem = (size_t)8 * MT * (p.k + 32) * 2 + (size_t)(p.k / 32) * 8 * MT * 4;
+    auto kern = q4k_gemv_kernel<MT>;
+    static size_t configured[64] = {};
+    int device = 0;
+    OXQ_CUDA(cudaGetDevice(&device));
+    if (device >= 64 || configured[device] < smem) {
+        OXQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (device < 64) configured[device] = smem;
+    }
+    kern<<<ceil_div(p.n, 16), Q4K_WARPS * 32, smem, st>>>(p);
+    OXQ_LAUNCH_CHECK("q4k_gemv_kernel");
+    return OXQ_OK;
+}
+
+// True when the tuned kernel applies; otherwise the caller uses the generic row-format kernel.
+bool q4k_gemv_supported(int m, int k)
+{
+    const int mt = m <= 8 ? 1 : 2;
+    return m <= 16 && k % 256 == 0 && (size_t)8 * mt * (k + 32) * 2 + (size_t)(k / 32) * 8 * mt * 4 <= 200 * 1024;
+}
+
+int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k,
+             int n, cudaStream_t st)
+{
+    Q4kGemvParams p;
+    p.x = (const __nv_bfloat16 *)x; p.blocks = (const uint8_t *)blocks; p.bias = bias; p.y = y;
+    p.bias_dtype = bias_dtype; p.y_dtype = y_dtype; p.m = m; p.k = k; p.n = n;
+    return m <= 8 ? launch_q4k<1>(p, st) : launch_q4k<2>(p, st);
+}
+
+} // namespace oxq

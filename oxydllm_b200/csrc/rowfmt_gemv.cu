@@ -7,6 +7,8 @@
 // are the 16-row operand of mma.sync m16n8k16; the 8-column operand is up to
 // 8 tokens of x; accumulation is f32. The four warps of a CTA split k and are
 // summed in warp order through shared memory (fixed order, no atomics).
+#include <cstdlib>
+
 #include "formats.cuh"
 
 namespace oxq {
@@ -101,6 +103,10 @@ __device__ __forceinline__ void mma_bf16_row(float (&d)[4], const uint32_t (&a)[
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+
+bool q4k_gemv_supported(int m, int k);
+int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k,
+             int n, cudaStream_t st);
 
 constexpr int ROW_NW = 4;
 
@@ -203,6 +209,10 @@ OXQ_EXPORT int oxq_gguf_gemv(int ggml_type, const void *x, int x_dtype, const vo
     p.bias_dtype = bias_dtype; p.y_dtype = y_dtype; p.m = m; p.k = k; p.n = n;
     p.row_bytes = (size_t)(k / bel) * bby;
     cudaStream_t st = (cudaStream_t)stream;
+    if (ggml_type == OXQ_GGML_Q4_K && q4k_gemv_supported(m, k)) {
+        const char *env = getenv("OXQ_Q4K_FAST"); // bench-harness knob: "0" selects the generic kernel
+        if (!(env && env[0] == '0')) return q4k_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
+    }
     switch (ggml_type) {
     case OXQ_GGML_Q4_0: return launch_rowfmt<RF_Q4_0>(p, st);
     case OXQ_GGML_Q8_0: return launch_rowfmt<RF_Q8_0>(p, st);
