@@ -4,17 +4,25 @@
 // mins, 128 bytes of nibbles; byte t of 32-byte group iq holds element t of sub-block 2*iq (low
 // nibble) and of sub-block 2*iq+1 (high nibble); w = (d*sc)*q - dmin*mn.
 //
-// A CTA owns 16 output rows; its 8 warps take super-blocks round-robin along k and are summed in
-// warp order through shared memory. Per super-block a lane streams, straight into registers, the
-// 16-byte header of its two rows (lane/4 and lane/4 + 8) and eight 8-byte pieces of nibbles: bytes
-// [8c, 8c+8) of each 32-byte group (c = lane%4), so the four lanes of a row read 32 contiguous
-// bytes. The k order inside a sub-block is free as long as x follows it, which lets every lane
-// feed the tensor cores from its own bytes with no exchange: nibbles become f16 pairs with one
-// lop3 each -- 0x6400 | q is 1024 + q, and 0x6400 | (q << 4) is 1024 + 16 q, so the high nibbles
-// need no shift -- and go into mma.sync m16n8k16 (f16 x f16 -> f32) as the 16-row operand.
-// x is staged once per CTA as f16 (saturated to +-65504) in the matching element order, together
-// with the per-sub-block sums of x; scale, min, the 1024 offset and the factor 16 are folded in
-// f32 once per sub-block:  y += d*sc * (acc - 1024*sum_x) / {1,16} - dmin*mn * sum_x.
+// A thread-block cluster of KS CTAs owns 16 * row_tiles output rows: CTA r of the cluster takes the
+// r-th slice of k; inside a CTA the warps are row_tiles x k_warps, the k_warps of a row tile taking
+// the slice's super-blocks round-robin. The partial sums of an output are added in a fixed order
+// by one thread of the cluster through distributed shared memory (no workspace, no atomics).
+// Per super-block a lane streams, straight into registers, the 16-byte header of its two rows
+// (lane/4 and lane/4 + 8) and four 8-byte pieces of nibbles: bytes [8c, 8c+8) of each 32-byte
+// group (c = lane%4), so the four lanes of a row read 32 contiguous bytes. The k order inside a
+// sub-block is free as long as x follows it, which lets every lane feed the tensor cores from its
+// own bytes with no exchange: nibbles become f16 pairs with one lop3 each -- 0x6400 | q is
+// 1024 + q, and 0x6400 | (q << 4) is 1024 + 16 q, so the high nibbles need no shift -- and go
+// into mma.sync m16n8k16 (f16 x f16 -> f32) as the 16-row operand. The CTA stages its slice of x
+// as f16 (saturated to +-65504) in the matching element order, together with the per-sub-block
+// sums of x; scale, min, the 1024 offset and the factor 16 are folded in f32 once per sub-block:
+//   y += d*sc * (acc - 1024*sum_x) / {1,16} - dmin*mn * sum_x.
+#include <cooperative_groups.h>
+
+#include <cstdio>
+#include <cstdlib>
+
 #include "formats.cuh"
 
 namespace oxq {
@@ -26,9 +34,10 @@ struct Q4kGemvParams {
     void *y;
     int bias_dtype, y_dtype;
     int m, k, n;
+    int row_tiles, k_warps; // warps of a CTA = row_tiles x k_warps
 };
 
-constexpr int Q4K_WARPS = 8;
+namespace cg = cooperative_groups;
 
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
 {
@@ -82,57 +91,74 @@ __device__ __forceinline__ void q4k_scales(const uint4 &hdr, float (&dsc)[8], fl
 }
 
 template <int MT>
-__global__ void __launch_bounds__(Q4K_WARPS * 32) q4k_gemv_kernel(const Q4kGemvParams p)
+__global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4kGemvParams p)
 {
     extern __shared__ __align__(16) unsigned char smem[];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int nrt = p.row_tiles, kwn = p.k_warps, ks = (int)gridDim.y, rank = (int)blockIdx.y; // cluster = grid y extent
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
-    const int n0 = blockIdx.x * 16;
+    const int rt = warp % nrt, kw = warp / nrt;
+    const int n0 = (blockIdx.x * nrt + rt) * 16;
     const int nsb = p.k >> 8;                 // super-blocks per row
+    const int sl_sb = nsb / ks, sb_beg = rank * sl_sb, sb_end = sb_beg + sl_sb; // this CTA's slice
+    const int kl = sl_sb << 8, k_cta = sb_beg << 8;
     const size_t row_bytes = (size_t)nsb * 144;
-    const int xrow = p.k + 32;                // halves per staged token row: 64 bytes of padding keep the
+    const int xrow = kl + 32;                 // halves per staged token row: 64 bytes of padding keep the
                                               // 16-byte fragment reads of a quarter warp on distinct banks
     __half *xs = reinterpret_cast<__half *>(smem);
-    float *sx = reinterpret_cast<float *>(smem + (size_t)8 * MT * xrow * sizeof(__half)); // [k/32][8*MT]
+    float *sx = reinterpret_cast<float *>(smem + (size_t)p.m * xrow * sizeof(__half)); // [kl/32][8*MT]
+    float *red = sx + (size_t)(kl >> 5) * 8 * MT;                                       // [warp][MT*4][lane]
+    float *zeros = red + blockDim.x * MT * 4; // 16 bytes of zeros: what lanes without a token read as x
 
     // Rows past the end re-read the last row; their results are never stored.
     const int r0 = min(n0 + g, p.n - 1), r1 = min(n0 + g + 8, p.n - 1);
     const uint8_t *row0 = p.blocks + (size_t)r0 * row_bytes, *row1 = p.blocks + (size_t)r1 * row_bytes;
     Q4kRow cur0, cur1;
-    int sb = warp;
-    if (sb < nsb) {
+    int sb = sb_beg + kw;
+    if (sb < sb_end) {
         q4k_load_row(cur0, row0 + (size_t)sb * 144, c);
         q4k_load_row(cur1, row1 + (size_t)sb * 144, c);
     }
 
-    // Stage x as f16, elements of every group of four stored as [0, 2, 1, 3] (the order in which the
-    // nibble masks deliver k), then the per-sub-block sums of the staged values.
-    // Only real tokens are staged; lanes whose token does not exist feed zeros to the tensor cores.
-    for (int idx = tid; idx < p.m * (p.k >> 2); idx += Q4K_WARPS * 32) {
-        const int row = idx / (p.k >> 2), q4 = idx % (p.k >> 2);
-        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(p.x + (size_t)row * p.k) + q4);
-        float f[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
-                      __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
-#pragma unroll
-        for (int u = 0; u < 4; u++) f[u] = fminf(fmaxf(f[u], -65504.0f), 65504.0f);
-        const __half2 h02 = __floats2half2_rn(f[0], f[2]), h13 = __floats2half2_rn(f[1], f[3]);
-        uint2 o;
-        o.x = *reinterpret_cast<const uint32_t *>(&h02);
-        o.y = *reinterpret_cast<const uint32_t *>(&h13);
-        *reinterpret_cast<uint2 *>(xs + (size_t)row * xrow + 4 * q4) = o;
-    }
+    // Stage the slice of x as f16, elements of every group of four stored as [0, 2, 1, 3] (the order in
+    // which the nibble masks deliver k), with the per-sub-block sums of the staged values: eight
+    // neighbouring threads hold one 32-element sub-block. Only real tokens are staged.
+    if (tid < 4) zeros[tid] = 0.0f;
+    for (int idx = tid; idx < 8 * MT * (kl >> 5); idx += blockDim.x) sx[idx] = 0.0f; // rows without a token
     __syncthreads();
-    for (int idx = tid; idx < p.m * (p.k >> 5); idx += Q4K_WARPS * 32) {
-        const int row = idx % p.m, sub = idx / p.m;
-        const __half2 *src = reinterpret_cast<const __half2 *>(xs + (size_t)row * xrow + 32 * sub);
-        float s = 0.0f;
+    for (int row = 0; row < p.m; row++) {
+        const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)row * p.k + k_cta);
+        uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
+        for (int q4 = tid; q4 < (kl >> 2); q4 += blockDim.x) { // kl / 4 is a multiple of 64: whole warps
+            const uint2 raw = __ldg(src + q4);
+            float f[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+                          __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
 #pragma unroll
-        for (int u = 0; u < 16; u++) {
-            const float2 v = __half22float2(src[u]);
-            s += v.x + v.y;
+            for (int u = 0; u < 4; u++) f[u] = fminf(fmaxf(f[u], -65504.0f), 65504.0f);
+            const __half2 h02 = __floats2half2_rn(f[0], f[2]), h13 = __floats2half2_rn(f[1], f[3]);
+            uint2 o;
+            o.x = *reinterpret_cast<const uint32_t *>(&h02);
+            o.y = *reinterpret_cast<const uint32_t *>(&h13);
+            dst[q4] = o;
+            const float2 a = __half22float2(h02), b = __half22float2(h13); // sum what the tensor cores will see
+            float sum = (a.x + a.y) + (b.x + b.y);
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+            sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+            if ((lane & 7) == 0) sx[(q4 >> 3) * 8 * MT + row] = sum;
         }
-        sx[sub * 8 * MT + row] = s;
     }
     __syncthreads();
+
+    // This lane's x for fragment column g of token tile mt, or the zeros (stride 0).
+    const __half *xp[MT];
+    int xstep[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        const bool real = 8 * mt + g < p.m;
+        xp[mt] = real ? xs + (size_t)(8 * mt + g) * xrow + 8 * c : reinterpret_cast<const __half *>(zeros);
+        xstep[mt] = real ? 1 : 0;
+    }
 
     float tot[MT][4];
 #pragma unroll
@@ -141,15 +167,16 @@ __global__ void __launch_bounds__(Q4K_WARPS * 32) q4k_gemv_kernel(const Q4kGemvP
     asm volatile("mov.b32 %0, 0x000F000F;\n\tmov.b32 %1, 0x00F000F0;\n\tmov.b32 %2, 0x64006400;"
                  : "=r"(mask_lo), "=r"(mask_hi), "=r"(magic));
 
-    for (; sb < nsb; sb += Q4K_WARPS) {
+    for (; sb < sb_end; sb += kwn) {
         Q4kRow nxt0 = cur0, nxt1 = cur1;
-        if (sb + Q4K_WARPS < nsb) { // next super-block on its way while this one is consumed
-            q4k_load_row(nxt0, row0 + (size_t)(sb + Q4K_WARPS) * 144, c);
-            q4k_load_row(nxt1, row1 + (size_t)(sb + Q4K_WARPS) * 144, c);
+        if (sb + kwn < sb_end) { // next super-block on its way while this one is consumed
+            q4k_load_row(nxt0, row0 + (size_t)(sb + kwn) * 144, c);
+            q4k_load_row(nxt1, row1 + (size_t)(sb + kwn) * 144, c);
         }
         float dsc0[8], dmn0[8], dsc1[8], dmn1[8];
         q4k_scales(cur0.hdr, dsc0, dmn0);
         q4k_scales(cur1.hdr, dsc1, dmn1);
+        const int sub0 = (sb - sb_beg) * 8; // first sub-block of this super-block within the slice
 #pragma unroll
         for (int iq = 0; iq < 4; iq++) {
             float acc_lo[MT][4], acc_hi[MT][4];
@@ -157,15 +184,12 @@ __global__ void __launch_bounds__(Q4K_WARPS * 32) q4k_gemv_kernel(const Q4kGemvP
             for (int mt = 0; mt < MT; mt++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) acc_lo[mt][e] = acc_hi[mt][e] = 0.0f;
-            const int sub_lo = sb * 8 + 2 * iq; // global sub-block index of the low nibbles
+            const int sub_lo = sub0 + 2 * iq; // sub-block of the low nibbles
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
                 // lane c's eight elements of each sub-block, both k steps, in one 16-byte read
-                uint4 xl = make_uint4(0u, 0u, 0u, 0u), xh = xl;
-                if (8 * mt + g < p.m) {
-                    xl = *reinterpret_cast<const uint4 *>(xs + (size_t)(8 * mt + g) * xrow + 32 * sub_lo + 8 * c);
-                    xh = *reinterpret_cast<const uint4 *>(xs + (size_t)(8 * mt + g) * xrow + 32 * (sub_lo + 1) + 8 * c);
-                }
+                const uint4 xl = *reinterpret_cast<const uint4 *>(xp[mt] + xstep[mt] * (32 * sub_lo));
+                const uint4 xh = *reinterpret_cast<const uint4 *>(xp[mt] + xstep[mt] * (32 * sub_lo + 32));
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
                     const uint32_t w0 = j ? cur0.qs[iq].y : cur0.qs[iq].x, w1 = j ? cur1.qs[iq].y : cur1.qs[iq].x;
@@ -201,33 +225,40 @@ __global__ void __launch_bounds__(Q4K_WARPS * 32) q4k_gemv_kernel(const Q4kGemvP
         cur1 = nxt1;
     }
 
-    __syncthreads(); // x no longer needed: reuse the front of shared memory for the warp partials
-    float *red = reinterpret_cast<float *>(smem); // [warp][MT*4][lane]
 #pragma unroll
     for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int e = 0; e < 4; e++) red[(warp * MT * 4 + mt * 4 + e) * 32 + lane] = tot[mt][e];
-    __syncthreads();
-    if (warp == 0) {
-#pragma unroll
-        for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                float sum = 0.0f;
-#pragma unroll
-                for (int w = 0; w < Q4K_WARPS; w++) sum += red[(w * MT * 4 + mt * 4 + e) * 32 + lane];
-                const int nn = n0 + g + 8 * (e >> 1), row = 8 * mt + 2 * c + (e & 1);
-                if (nn < p.n && row < p.m) {
-                    if (p.bias) sum += load_as_f32(p.bias, p.bias_dtype, nn);
-                    store_as(p.y, p.y_dtype, (size_t)row * p.n + nn, sum);
-                }
+    if (ks > 1) cluster.sync(); else __syncthreads();
+
+    // Every (row tile, accumulator slot, lane) is summed by one thread of the cluster: slices in
+    // ascending k, the k warps of a slice in warp order.
+    const int slots = nrt * MT * 4 * 32;
+    for (int o = rank * blockDim.x + tid; o < slots; o += ks * blockDim.x) {
+        const int ln = o & 31, e = (o >> 5) & 3, mt = (o >> 7) % MT, wt = (o >> 7) / MT;
+        const int nn = (blockIdx.x * nrt + wt) * 16 + (ln >> 2) + 8 * (e >> 1), row = 8 * mt + 2 * (ln & 3) + (e & 1);
+        if (nn < p.n && row < p.m) {
+            float sum = 0.0f;
+            for (int q = 0; q < ks; q++) {
+                const float *src = ks > 1 ? cluster.map_shared_rank(red, q) : red;
+                for (int w = 0; w < kwn; w++) sum += src[((w * nrt + wt) * MT * 4 + mt * 4 + e) * 32 + ln];
             }
+            if (p.bias) sum += load_as_f32(p.bias, p.bias_dtype, nn);
+            store_as(p.y, p.y_dtype, (size_t)row * p.n + nn, sum);
+        }
     }
+    if (ks > 1) cluster.sync(); // nobody leaves while a peer may still read its shared memory
 }
 
-template <int MT> static int launch_q4k(const Q4kGemvParams &p, cudaStream_t st)
+static size_t q4k_smem(int mt, int m, int kl, int warps)
 {
-    const size_t smem = (size_t)8 * MT * (p.k + 32) * 2 + (size_t)(p.k / 32) * 8 * MT * 4;
+    return (size_t)m * (kl + 32) * 2 + (size_t)(kl / 32) * 8 * mt * 4 + (size_t)warps * mt * 4 * 32 * 4 + 16;
+}
+
+template <int MT> static int launch_q4k(const Q4kGemvParams &p, int ks, cudaStream_t st)
+{
+    const int nw = p.row_tiles * p.k_warps;
+    const size_t smem = q4k_smem(MT, p.m, p.k / ks, nw);
     auto kern = q4k_gemv_kernel<MT>;
     static size_t configured[64] = {};
     int device = 0;
@@ -236,16 +267,26 @@ template <int MT> static int launch_q4k(const Q4kGemvParams &p, cudaStream_t st)
         OXQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (device < 64) configured[device] = smem;
     }
-    kern<<<ceil_div(p.n, 16), Q4K_WARPS * 32, smem, st>>>(p);
-    OXQ_LAUNCH_CHECK("q4k_gemv_kernel");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ceil_div(p.n, 16 * p.row_tiles), ks, 1);
+    cfg.blockDim = dim3(nw * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = ks;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ks > 1 ? 1 : 0;
+    OXQ_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
     return OXQ_OK;
 }
 
 // True when the tuned kernel applies; otherwise the caller uses the generic row-format kernel.
 bool q4k_gemv_supported(int m, int k)
 {
-    const int mt = m <= 8 ? 1 : 2;
-    return m <= 16 && k % 256 == 0 && (size_t)8 * mt * (k + 32) * 2 + (size_t)(k / 32) * 8 * mt * 4 <= 200 * 1024;
+    return m <= 16 && k % 256 == 0 && q4k_smem(m <= 8 ? 1 : 2, m, k, 8) <= 200 * 1024;
 }
 
 int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k,
@@ -254,7 +295,17 @@ int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype
     Q4kGemvParams p;
     p.x = (const __nv_bfloat16 *)x; p.blocks = (const uint8_t *)blocks; p.bias = bias; p.y = y;
     p.bias_dtype = bias_dtype; p.y_dtype = y_dtype; p.m = m; p.k = k; p.n = n;
-    return m <= 8 ? launch_q4k<1>(p, st) : launch_q4k<2>(p, st);
+    // Measured on a 4096 x 4096 layer: one row tile per CTA up to 8 tokens, two (sharing the staged x) above.
+    int nrt = m > 8 ? 2 : 1, kw = m > 8 ? 4 : 8, ks = 1;
+    if (const char *env = getenv("OXQ_Q4K_GEMV_TUNE")) { // bench-harness knob: "row_tiles,k_warps,cluster"
+        int a = 0, b = 0, cc = 0;
+        if (sscanf(env, "%d,%d,%d", &a, &b, &cc) == 3 && a >= 1 && b >= 1 && a * b <= 8 && cc >= 1 && cc <= 8 &&
+            (cc & (cc - 1)) == 0 && (k / 256) % cc == 0) {
+            nrt = a; kw = b; ks = cc;
+        }
+    }
+    p.row_tiles = nrt; p.k_warps = kw;
+    return m <= 8 ? launch_q4k<1>(p, ks, st) : launch_q4k<2>(p, ks, st);
 }
 
 } // namespace oxq

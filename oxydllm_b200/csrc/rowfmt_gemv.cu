@@ -107,6 +107,9 @@ __device__ __forceinline__ void mma_bf16_row(float (&d)[4], const uint32_t (&a)[
 bool q4k_gemv_supported(int m, int k);
 int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k,
              int n, cudaStream_t st);
+bool fp8_gemv_fast_supported(int m, int k, int block_in, const void *w);
+int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale_inv, int s_in, int block_out, int block_in,
+                  const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, cudaStream_t st);
 
 constexpr int ROW_NW = 4;
 
@@ -241,6 +244,12 @@ OXQ_EXPORT int oxq_fp8_gemv(const void *x, int x_dtype, const uint8_t *weight, c
         p.s_in = s_in; p.block_out = n / s_out; p.block_in = k / s_in;
         OXQ_REQUIRE(p.block_in % 4 == 0, OXQ_ERR_UNSUPPORTED, "oxq_fp8_gemv: scale block along k (%d) must be a multiple of 4",
                     p.block_in);
+    }
+    if (fp8_gemv_fast_supported(m, k, p.block_in, weight)) {
+        const char *env = getenv("OXQ_FP8_FAST"); // bench-harness knob: "0" selects the generic kernel
+        if (!(env && env[0] == '0'))
+            return fp8_gemv_fast(x, weight, scale_inv, p.s_in, p.block_out, p.block_in, bias, bias_dtype, y, y_dtype, m, k,
+                                 n, (cudaStream_t)stream);
     }
     return launch_rowfmt<RF_FP8>(p, (cudaStream_t)stream);
 }
