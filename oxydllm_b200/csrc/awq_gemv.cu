@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(NW * 32, 1) awq_gemv_kernel(const AwqGemvParam
 
 // ---------------------------------------------------------------------------
 // Main variant: slices aligned to quantization groups, weights streamed straight
-// into registers.
+// into registers, f16 tensor cores.
 //
 // A CTA is KW warps on the SAME 8*V packed words (64*V out columns), each warp
 // on its own contiguous k slice; a cluster of R such CTAs covers all of k.
@@ -285,11 +285,14 @@ __global__ void __launch_bounds__(NW * 32, 1) awq_gemv_kernel(const AwqGemvParam
 // scale/zero fold happens at most once per group into running f32 totals.
 // Weights go from HBM to registers with streaming vector loads issued D steps
 // ahead (plain loads sustain the stream; lane-private cp.async measured about
-// half the rate). The CTA's slice of x is staged once in shared memory.
-// The integer pipe is the scarce resource here (one op per weight at half
-// issue rate), so the nibble-to-bf16 step is written as explicit three-input
-// lop3 instructions. Partials meet in (distributed) shared memory and every
-// valid output is summed by one thread of the cluster in ascending k order.
+// half the rate). The CTA's slice of x is staged once in shared memory as f16
+// (saturated to +-65504): with a 10-bit mantissa both nibbles of a byte become
+// exact f16 values with one three-input lop3 and no shift -- 0x6400 | q is
+// 1024 + q and 0x6400 | (q << 4) is 1024 + 16 q -- and the offsets and the
+// factor 16 are taken out again in f32 when a group is folded. The integer pipe
+// is the scarce resource here (one op per weight at half issue rate). Partials
+// meet in (distributed) shared memory and every valid output is summed by one
+// thread of the cluster in ascending k order.
 constexpr int GK_KW = 4;
 
 template <int V> __device__ __forceinline__ void ld_stream(uint32_t (&dst)[V], const uint32_t *p)
@@ -299,18 +302,22 @@ template <int V> __device__ __forceinline__ void ld_stream(uint32_t (&dst)[V], c
     else { const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(p)); dst[0] = t.x; dst[1 % V] = t.y; dst[2 % V] = t.z; dst[3 % V] = t.w; }
 }
 
-// (p & mask) | magic in one instruction (lut 0xEA = (a & b) | c). Mask 0x000F000F and magic
-// 0x43004300 are passed in registers: a LOP3 encodes a single immediate, so with two literals the
-// compiler re-materialises one of them with an extra move in front of every use.
-__device__ __forceinline__ uint32_t nib_lo(uint32_t p, uint32_t mask, uint32_t magic)
+// (p & mask) | magic in one instruction (lut 0xEA = (a & b) | c). Mask and magic are passed in
+// registers: a LOP3 encodes a single immediate, so with two literals the compiler re-materialises
+// one of them with an extra move in front of every use.
+__device__ __forceinline__ uint32_t and_or(uint32_t p, uint32_t mask, uint32_t magic)
 {
     uint32_t r;
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(p), "r"(mask), "r"(magic));
     return r;
 }
-__device__ __forceinline__ uint32_t nib_hi(uint32_t p, uint32_t mask, uint32_t magic)
+
+__device__ __forceinline__ void mma_f16_16816_awq(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
 {
-    return nib_lo(p >> 4, mask, magic);
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
 template <int MT, int V, int D, int MINB>
@@ -326,10 +333,11 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
     const int jtile = blockIdx.x * 8 * V;
     const int jbase = jtile + g * V;
     const bool j_ok = jbase < p.packed_out;
-    const int steps = p.steps_per_cta; // 16-row steps per warp slice, identical for all slices
+    const int steps = p.steps_per_cta; // 16-row steps per warp slice, identical for all slices; a multiple of D
     const int gsteps = p.group_size >> 4;
-    uint32_t kmask, kmagic; // opaque to constant propagation so that they stay in registers
-    asm volatile("mov.b32 %0, 0x000F000F;\n\tmov.b32 %1, 0x43004300;" : "=r"(kmask), "=r"(kmagic));
+    uint32_t mask_lo, mask_hi, kmagic; // opaque to constant propagation so that they stay in registers
+    asm volatile("mov.b32 %0, 0x000F000F;\n\tmov.b32 %1, 0x00F000F0;\n\tmov.b32 %2, 0x64006400;"
+                 : "=r"(mask_lo), "=r"(mask_hi), "=r"(kmagic));
     const int kr = KW * steps * 16;    // k range of this CTA
     const int k_cta = rank * kr;
     const int step_beg = (rank * KW + warp) * steps;
@@ -342,24 +350,33 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
 #pragma unroll
     for (int d = 0; d < D; d++)
 #pragma unroll
-        for (int i = 0; i < 4; i++)
-            if (d < steps) ld_stream<V>(buf[d][i], wsrc + (size_t)(16 * d + i) * row_stride);
+        for (int i = 0; i < 4; i++) ld_stream<V>(buf[d][i], wsrc + (size_t)(16 * d + i) * row_stride);
 
-    // x[0 .. 8*MT) x [k_cta, k_cta + kr) -> shared memory, rows padded by 32 bytes so that the
-    // 8-byte fragment reads of a half warp (4 rows x 32 bytes) fall into distinct banks.
+    // x[0 .. m) x [k_cta, k_cta + kr) -> shared memory as f16, rows padded by 32 bytes so that the
+    // 8-byte fragment reads of a half warp (4 rows x 32 bytes) fall into distinct banks. Lanes whose
+    // token does not exist read a block of zeros instead (stride 0).
     const int xrow = kr + 16; // elements
-    __nv_bfloat16 *xs = reinterpret_cast<__nv_bfloat16 *>(smem);
-    {
-        const int chunks_per_row = kr >> 3; // 16-byte chunks
-        for (int idx = tid; idx < 8 * MT * chunks_per_row; idx += KW * 32) {
-            const int row = idx / chunks_per_row, ch = idx % chunks_per_row;
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (row < p.m) val = __ldg(reinterpret_cast<const uint4 *>(p.x + (size_t)row * p.k + k_cta) + ch);
-            *reinterpret_cast<uint4 *>(xs + (size_t)row * xrow + ch * 8) = val;
+    __half *xs = reinterpret_cast<__half *>(smem);
+    uint32_t *zeros = reinterpret_cast<uint32_t *>(smem + (size_t)p.m * xrow * sizeof(__half));
+    if (tid < 4) zeros[tid] = 0u;
+    // Running totals live in shared memory, one 16-byte slot per (warp, MMA tile, lane), private to the
+    // lane until the final reduction reads them: registers are kept for weights in flight instead.
+    float4 *red = reinterpret_cast<float4 *>(zeros + 4);
+    float4 *mine = red + (size_t)warp * (NACC / 4) * 32 + lane;
+#pragma unroll
+    for (int i = 0; i < NACC / 4; i++) mine[i * 32] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int row = 0; row < p.m; row++) {
+        const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)row * p.k + k_cta);
+        uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
+        for (int q4 = tid; q4 < (kr >> 2); q4 += KW * 32) {
+            const uint2 raw = __ldg(src + q4);
+            dst[q4] = make_uint2(f32x2_to_f16x2_sat(bf16_lo_f32(raw.x), bf16_hi_f32(raw.x)),
+                                 f32x2_to_f16x2_sat(bf16_lo_f32(raw.y), bf16_hi_f32(raw.y)));
         }
     }
 
-    // Zero points and scales of the slice's first group (16-bit scales ride in registers).
+    // Zero points and scales of the slice's first group (16-bit scales ride in registers: reading them
+    // only when the group is folded would stall the warp for a full memory round trip per group).
     const bool sc16 = p.scales_dtype != OXQ_F32;
     const bool is_f16 = p.scales_dtype == OXQ_F16;
     uint32_t zw[V], sraw[V][4];
@@ -378,7 +395,7 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
     fetch_group(grp);
     __syncthreads();
 
-    float acc[V][4][MT][4], tot[V][4][MT][4], sx[MT][4];
+    float acc[V][4][MT][4], sx[MT][4];
 #pragma unroll
     for (int v = 0; v < V; v++)
 #pragma unroll
@@ -386,16 +403,19 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
 #pragma unroll
             for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-                for (int e = 0; e < 4; e++) acc[v][t][mt][e] = tot[v][t][mt][e] = 0.0f;
+                for (int e = 0; e < 4; e++) acc[v][t][mt][e] = 0.0f;
 #pragma unroll
     for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int e = 0; e < 4; e++) sx[mt][e] = 0.0f;
 
-    // tot += s * acc - (s * (128 + z)) * sum_x for the group that just ended; acc, sum_x restart.
+    // The group that just ended goes into the totals; acc and sum_x restart. Tile t holds columns
+    // 2t and 2t+1 of the word (nibbles t and t+4). Even t used low nibbles, acc = sum (1024 + q) x:
+    //   tot += s * acc - s * (1024 + z) * sum_x.
+    // Odd t used high nibbles, acc = sum (1024 + 16 q) x:  tot += (s/16) * acc - s * (64 + z) * sum_x.
     auto fold = [&]() {
 #pragma unroll
-        for (int v = 0; v < V; v++)
+        for (int v = 0; v < V; v++) {
 #pragma unroll
             for (int t = 0; t < 4; t++) {
                 float s0, s1;
@@ -409,100 +429,89 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
                     s0 = j_ok ? reinterpret_cast<const float *>(p.scales)[(size_t)grp * p.n + n0] : 0.0f;
                     s1 = j_ok ? reinterpret_cast<const float *>(p.scales)[(size_t)grp * p.n + n0 + 1] : 0.0f;
                 }
-                // (128 + z) of slots t and t+4 as two bf16 -> two f32 by shifting
-                const uint32_t zz = nib_lo(zw[v] >> (4 * t), kmask, kmagic);
-                const float u0 = s0 * __uint_as_float(zz << 16), u1 = s1 * __uint_as_float(zz & 0xFFFF0000u);
+                const uint32_t zq = zw[v] >> (4 * t);
+                const float off = (t & 1) ? 64.0f : 1024.0f;
+                const float u0 = s0 * (off + (float)(zq & 0xFu)), u1 = s1 * (off + (float)((zq >> 16) & 0xFu));
+                const float a0 = (t & 1) ? s0 * 0.0625f : s0, a1 = (t & 1) ? s1 * 0.0625f : s1;
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
                     float(&a4)[4] = acc[v][t][mt];
-                    float(&t4)[4] = tot[v][t][mt];
-                    t4[0] = fmaf(s0, a4[0], fmaf(-u0, sx[mt][0], t4[0]));
-                    t4[1] = fmaf(s0, a4[1], fmaf(-u0, sx[mt][1], t4[1]));
-                    t4[2] = fmaf(s1, a4[2], fmaf(-u1, sx[mt][0], t4[2]));
-                    t4[3] = fmaf(s1, a4[3], fmaf(-u1, sx[mt][1], t4[3]));
+                    float4 &slot = mine[((v * 4 + t) * MT + mt) * 32];
+                    float4 t4 = slot;
+                    t4.x = fmaf(a0, a4[0], fmaf(-u0, sx[mt][0], t4.x));
+                    t4.y = fmaf(a0, a4[1], fmaf(-u0, sx[mt][1], t4.y));
+                    t4.z = fmaf(a1, a4[2], fmaf(-u1, sx[mt][0], t4.z));
+                    t4.w = fmaf(a1, a4[3], fmaf(-u1, sx[mt][1], t4.w));
+                    slot = t4;
                     a4[0] = a4[1] = a4[2] = a4[3] = 0.0f;
                 }
             }
+        }
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) sx[mt][0] = sx[mt][1] = sx[mt][2] = sx[mt][3] = 0.0f;
     };
 
-    const uint32_t ones[4] = {0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u};
-    const __nv_bfloat16 *xw = xs + (size_t)g * xrow + warp * steps * 16 + 4 * c;
+    const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u}; // f16 1.0
+    const __half *xw[MT];
+    int xstep[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        const bool real = 8 * mt + g < p.m;
+        xw[mt] = real ? xs + (size_t)(8 * mt + g) * xrow + warp * steps * 16 + 4 * c : reinterpret_cast<const __half *>(zeros);
+        xstep[mt] = real ? 16 : 0;
+    }
     int to_fold = min(steps, gsteps - (step_beg % gsteps)); // steps left in the current group
 
     for (int s0 = 0; s0 < steps; s0 += D) {
+        const bool more = s0 + D < steps;
 #pragma unroll
         for (int d = 0; d < D; d++) {
-            const int s = s0 + d;
-            if (s < steps) {
-                uint32_t w[4][V], xb[MT][2];
+            uint32_t w[4][V], xb[MT][2];
 #pragma unroll
-                for (int i = 0; i < 4; i++)
+            for (int i = 0; i < 4; i++)
 #pragma unroll
-                    for (int v = 0; v < V; v++) w[i][v] = buf[d][i][v];
-                if (s + D < steps) {
+                for (int v = 0; v < V; v++) w[i][v] = buf[d][i][v];
+            if (more) {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) ld_stream<V>(buf[d][i], wsrc + (size_t)(16 * (s + D) + i) * row_stride);
+                for (int i = 0; i < 4; i++) ld_stream<V>(buf[d][i], wsrc + (size_t)(16 * (D + d) + i) * row_stride);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                const uint2 t2 = *reinterpret_cast<const uint2 *>(xw[mt]);
+                xw[mt] += xstep[mt];
+                xb[mt][0] = t2.x; xb[mt][1] = t2.y;
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) mma_f16_16816_awq(sx[mt], ones, xb[mt]);
+#pragma unroll
+            for (int v = 0; v < V; v++) {
+                // rows (4c, 4c+1) -> first k pair, rows (4c+2, 4c+3) -> second k pair
+                const uint32_t pa[4] = {gather_byte<0>(w[0][v], w[1][v]), gather_byte<1>(w[0][v], w[1][v]),
+                                        gather_byte<2>(w[0][v], w[1][v]), gather_byte<3>(w[0][v], w[1][v])};
+                const uint32_t pb[4] = {gather_byte<0>(w[2][v], w[3][v]), gather_byte<1>(w[2][v], w[3][v]),
+                                        gather_byte<2>(w[2][v], w[3][v]), gather_byte<3>(w[2][v], w[3][v])};
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    // tile t: MMA row g = column 2t of the word (nibble t), row g+8 = column 2t+1 (nibble t+4)
+                    const uint32_t mk = (t & 1) ? mask_hi : mask_lo;
+                    const uint32_t a[4] = {and_or(pa[t >> 1], mk, kmagic), and_or(pa[2 + (t >> 1)], mk, kmagic),
+                                           and_or(pb[t >> 1], mk, kmagic), and_or(pb[2 + (t >> 1)], mk, kmagic)};
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) mma_f16_16816_awq(acc[v][t][mt], a, xb[mt]);
                 }
-#pragma unroll
-                for (int mt = 0; mt < MT; mt++) {
-                    const uint2 t2 = *reinterpret_cast<const uint2 *>(xw + (size_t)8 * mt * xrow + s * 16);
-                    xb[mt][0] = t2.x; xb[mt][1] = t2.y;
-                }
-#pragma unroll
-                for (int mt = 0; mt < MT; mt++) mma_bf16_16816(sx[mt], ones, xb[mt]);
-#pragma unroll
-                for (int v = 0; v < V; v++) {
-                    // rows (4c, 4c+1) -> first k pair, rows (4c+2, 4c+3) -> second k pair
-                    const uint32_t pa[4] = {gather_byte<0>(w[0][v], w[1][v]), gather_byte<1>(w[0][v], w[1][v]),
-                                            gather_byte<2>(w[0][v], w[1][v]), gather_byte<3>(w[0][v], w[1][v])};
-                    const uint32_t pb[4] = {gather_byte<0>(w[2][v], w[3][v]), gather_byte<1>(w[2][v], w[3][v]),
-                                            gather_byte<2>(w[2][v], w[3][v]), gather_byte<3>(w[2][v], w[3][v])};
-#pragma unroll
-                    for (int t = 0; t < 4; t++) {
-                        // tile t: MMA row g = column 2t of the word (slot t), row g+8 = column 2t+1 (slot t+4)
-                        uint32_t a[4];
-                        if (t & 1) {
-                            a[0] = nib_hi(pa[t >> 1], kmask, kmagic); a[1] = nib_hi(pa[2 + (t >> 1)], kmask, kmagic);
-                            a[2] = nib_hi(pb[t >> 1], kmask, kmagic); a[3] = nib_hi(pb[2 + (t >> 1)], kmask, kmagic);
-                        } else {
-                            a[0] = nib_lo(pa[t >> 1], kmask, kmagic); a[1] = nib_lo(pa[2 + (t >> 1)], kmask, kmagic);
-                            a[2] = nib_lo(pb[t >> 1], kmask, kmagic); a[3] = nib_lo(pb[2 + (t >> 1)], kmask, kmagic);
-                        }
-#pragma unroll
-                        for (int mt = 0; mt < MT; mt++) mma_bf16_16816(acc[v][t][mt], a, xb[mt]);
-                    }
-                }
-                if (--to_fold == 0) {
-                    fold();
-                    if (s + 1 < steps) {
-                        grp += 1;
-                        fetch_group(grp);
-                        to_fold = min(gsteps, steps - s - 1);
-                    }
+            }
+            if (--to_fold == 0) {
+                fold();
+                const int done = s0 + d + 1;
+                if (done < steps) {
+                    grp += 1;
+                    fetch_group(grp);
+                    to_fold = min(gsteps, steps - done);
                 }
             }
         }
+        wsrc += (size_t)16 * D * row_stride;
     }
-    __syncthreads(); // x is no longer needed: the partials reuse its shared memory
-
-    // The four totals of one MMA tile go out as one 16-byte store to red[warp][tile][lane].
-    float4 *red = reinterpret_cast<float4 *>(smem);
-    if (2 * c < p.m) { // otherwise this lane holds no valid token in any 8-token tile
-#pragma unroll
-        for (int v = 0; v < V; v++)
-#pragma unroll
-            for (int t = 0; t < 4; t++)
-#pragma unroll
-                for (int mt = 0; mt < MT; mt++)
-                    if (8 * mt + 2 * c < p.m) {
-                        const float(&t4)[4] = tot[v][t][mt];
-                        red[((size_t)warp * (NACC / 4) + (v * 4 + t) * MT + mt) * 32 + lane] =
-                            make_float4(t4[0], t4[1], t4[2], t4[3]);
-                    }
-    }
-
     cg::cluster_group cluster = cg::this_cluster();
     if (nranks > 1) cluster.sync(); else __syncthreads();
 
@@ -544,9 +553,9 @@ template <int MT, int V, int D, int MINB>
 static int launch_awq_gemv_group(const AwqGemvParams &p, int nranks, cudaStream_t stream)
 {
     constexpr int NACC = V * 4 * MT * 4;
-    const size_t xbytes = (size_t)8 * MT * (GK_KW * p.steps_per_cta * 16 + 16) * sizeof(__nv_bfloat16);
+    const size_t xbytes = (size_t)p.m * (GK_KW * p.steps_per_cta * 16 + 16) * sizeof(__half) + 16;
     const size_t red = (size_t)GK_KW * NACC * 32 * sizeof(float);
-    const size_t smem = xbytes > red ? xbytes : red;
+    const size_t smem = xbytes + red;
     auto kern = awq_gemv_group_kernel<MT, V, D, MINB>;
     static size_t configured[64] = {};
     int device = 0;
@@ -649,17 +658,19 @@ OXQ_EXPORT int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight,
     // Main path: contiguous k slices, 4 warps x R CTAs, each slice a whole number of groups or a
     // divisor of one group; R is chosen for about 2000 warps in flight (13 per SM).
     {
-        const int fv_default = mt == 1 ? 2 : 1;
+        const int fv_default = mt <= 2 ? 2 : 1;
         int fv = fv_default;
         while (fv > 1 && p.packed_out % fv != 0) fv /= 2;
-        int r_force = 0;
+        int r_force = 0, depth = 2, minb = 4;
         bool ok = aligned(scales, 16);
-        if (const char *env = getenv("OXQ_AWQ_GEMV_FAST")) { // bench-harness knob: "0" disables, else "V[,R]"
-            int ev = 0, er = 0;
-            const int got = sscanf(env, "%d,%d", &ev, &er);
+        if (const char *env = getenv("OXQ_AWQ_GEMV_FAST")) { // bench-harness knob: "0" disables, else "V[,R[,D]]"
+            int ev = 0, er = 0, ed = 0, eb = 0;
+            const int got = sscanf(env, "%d,%d,%d,%d", &ev, &er, &ed, &eb);
+            if (got >= 4 && eb == 6) minb = 6;
             if (got >= 1 && ev == 0) ok = false;
             if (got >= 1 && (ev == 1 || ev == 2 || ev == 4) && p.packed_out % ev == 0 && 16 * ev * mt <= 64) fv = ev;
             if (got >= 2 && (er == 1 || er == 2 || er == 4 || er == 8)) r_force = er;
+            if (got >= 3 && (ed == 2 || ed == 4)) depth = ed;
         }
         const int gsteps = group_size / 16;
         const int n_tiles = ceil_div(p.packed_out, 8 * fv);
@@ -667,18 +678,21 @@ OXQ_EXPORT int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight,
         for (int cand : {8, 4, 2, 1}) {
             if (total_steps % (GK_KW * cand) != 0) continue;
             const int sl = total_steps / (GK_KW * cand);
-            if (!(sl % gsteps == 0 || gsteps % sl == 0)) continue;
-            if ((size_t)8 * mt * (GK_KW * sl * 16 + 16) * 2 > 160 * 1024) continue;
-            if (r_force ? cand == r_force : (r == 0 || n_tiles * GK_KW * cand >= 1700)) r = cand;
+            if (!(sl % gsteps == 0 || gsteps % sl == 0) || sl % depth != 0) continue;
+            if ((size_t)m * (GK_KW * sl * 16 + 16) * 2 > 160 * 1024) continue;
+            if (r_force ? cand == r_force : (r == 0 || n_tiles * GK_KW * cand >= (mt == 1 ? 1700 : 850))) r = cand;
         }
-        if (ok && r != 0 && (mt == 1 || getenv("OXQ_AWQ_GEMV_FAST"))) { // measured: the ring kernel below is faster for m > 8
+        if (ok && r != 0 && (mt <= 2 || getenv("OXQ_AWQ_GEMV_FAST"))) { // measured: the ring kernel below is faster for m > 16
             p.steps_per_cta = total_steps / (GK_KW * r);
             if (mt == 1 && fv == 4) return launch_awq_gemv_group<1, 4, 2, 2>(p, r, st);
+            if (mt == 1 && fv == 2 && depth == 2 && minb == 6) return launch_awq_gemv_group<1, 2, 2, 6>(p, r, st);
+            if (mt == 1 && fv == 2 && depth == 4 && minb == 6) return launch_awq_gemv_group<1, 2, 4, 6>(p, r, st);
+            if (mt == 1 && fv == 2 && depth == 2) return launch_awq_gemv_group<1, 2, 2, 4>(p, r, st);
             if (mt == 1 && fv == 2) return launch_awq_gemv_group<1, 2, 4, 4>(p, r, st);
             if (mt == 1 && fv == 1) return launch_awq_gemv_group<1, 1, 4, 4>(p, r, st);
             if (mt == 2 && fv == 2) return launch_awq_gemv_group<2, 2, 2, 2>(p, r, st);
-            if (mt == 2 && fv == 1) return launch_awq_gemv_group<2, 1, 4, 4>(p, r, st);
-            if (mt == 4 && fv == 1) return launch_awq_gemv_group<4, 1, 4, 2>(p, r, st);
+            if (mt == 2 && fv == 1) return launch_awq_gemv_group<2, 1, 2, 4>(p, r, st);
+            if (mt == 4 && fv == 1) return launch_awq_gemv_group<4, 1, 2, 2>(p, r, st);
         }
     }
 

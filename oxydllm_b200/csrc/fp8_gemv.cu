@@ -97,15 +97,8 @@ __global__ void __launch_bounds__(256, MT == 1 ? 4 : 3) fp8_gemv_kernel(const Fp
         uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
         for (int q4 = tid; q4 < (kl >> 2); q4 += blockDim.x) {
             const uint2 raw = __ldg(src + q4);
-            float f[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
-                          __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
-#pragma unroll
-            for (int u = 0; u < 4; u++) f[u] = fminf(fmaxf(f[u], -65504.0f), 65504.0f);
-            const __half2 h01 = __floats2half2_rn(f[0], f[1]), h23 = __floats2half2_rn(f[2], f[3]);
-            uint2 o;
-            o.x = *reinterpret_cast<const uint32_t *>(&h01);
-            o.y = *reinterpret_cast<const uint32_t *>(&h23);
-            dst[q4] = o;
+            dst[q4] = make_uint2(f32x2_to_f16x2_sat(bf16_lo_f32(raw.x), bf16_hi_f32(raw.x)),
+                                 f32x2_to_f16x2_sat(bf16_lo_f32(raw.y), bf16_hi_f32(raw.y)));
         }
     }
     __syncthreads();

@@ -95,6 +95,18 @@ __device__ __forceinline__ float e8m0_to_f32(uint32_t s)
     return __uint_as_float(s << 23);
 }
 
+// Two bf16 (one 32-bit word, element 0 in the low half) and two more -> f16 pairs (lo0, lo1) of each
+// word, saturated to the largest finite f16 (the conversion rounds to nearest even; every bf16
+// inside the f16 normal range converts exactly).
+__device__ __forceinline__ uint32_t f32x2_to_f16x2_sat(float lo, float hi)
+{
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float bf16_lo_f32(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi_f32(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
 #endif // __CUDACC__
 
 } // namespace oxq

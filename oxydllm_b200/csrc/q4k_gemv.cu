@@ -131,15 +131,11 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
         uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
         for (int q4 = tid; q4 < (kl >> 2); q4 += blockDim.x) { // kl / 4 is a multiple of 64: whole warps
             const uint2 raw = __ldg(src + q4);
-            float f[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
-                          __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u)};
-#pragma unroll
-            for (int u = 0; u < 4; u++) f[u] = fminf(fmaxf(f[u], -65504.0f), 65504.0f);
-            const __half2 h02 = __floats2half2_rn(f[0], f[2]), h13 = __floats2half2_rn(f[1], f[3]);
-            uint2 o;
-            o.x = *reinterpret_cast<const uint32_t *>(&h02);
-            o.y = *reinterpret_cast<const uint32_t *>(&h13);
+            uint2 o; // elements [0, 2] and [1, 3]
+            o.x = f32x2_to_f16x2_sat(bf16_lo_f32(raw.x), bf16_lo_f32(raw.y));
+            o.y = f32x2_to_f16x2_sat(bf16_hi_f32(raw.x), bf16_hi_f32(raw.y));
             dst[q4] = o;
+            const __half2 h02 = *reinterpret_cast<const __half2 *>(&o.x), h13 = *reinterpret_cast<const __half2 *>(&o.y);
             const float2 a = __half22float2(h02), b = __half22float2(h13); // sum what the tensor cores will see
             float sum = (a.x + a.y) + (b.x + b.y);
             sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
