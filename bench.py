@@ -44,6 +44,9 @@ def algo_bytes(m: int) -> int:
 
 BYTES_PER_STEP = LAYERS * sum(algo_bytes(m) for m in M_SWEEP)
 LAUNCHES_PER_STEP = LAYERS * len(M_SWEEP)
+# dram__bytes_read.sum + dram__bytes_write.sum of one m = 1 launch on this layer shape, from the ncu
+# capture summarised in profiles/awq_gemv_c1.md (algorithmic bytes of that launch: algo_bytes(1)).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 30_547_712 + 72_192
 
 
 def measured_peak():
@@ -248,7 +251,8 @@ def run_gpu(args):
                 "h2d_bytes_per_step": LAYERS * sum(m * K * 2 for m in M_SWEEP),
                 "d2h_bytes_per_step": LAYERS * sum(m * N * 2 for m in M_SWEEP)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": None, "kernel": "awq_gemv_kernel",
+                     "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "kernel": "awq_gemv_group_kernel (m <= 16), awq_gemv_kernel (m = 32)",
                      "peak_kind": f"{peak_kind} copy bandwidth", "per_m": per_m},
         "clocks": clocks,
     }

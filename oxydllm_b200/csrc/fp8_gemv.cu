@@ -1,4 +1,4 @@
-// FP8 E4M3 block-scaled decode GEMV (1 <= m <= 16), tuned variant.
+// FP8 E4M3 block-scaled decode GEMV (1 <= m <= 32), tuned variant.
 //
 // A thread-block cluster of KS CTAs owns 16 * NW output rows: CTA r of the cluster takes the r-th
 // slice of k, warp w of every CTA the w-th 16-row tile, and the KS partial sums of an output are
@@ -55,7 +55,7 @@ __device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t v, uint32_t &lo2, uint3
 
 // D = 64-wide k chunks in flight per warp.
 template <int MT, int D>
-__global__ void __launch_bounds__(256, MT == 1 ? 4 : 3) fp8_gemv_kernel(const Fp8GemvParams p)
+__global__ void __launch_bounds__(256, MT == 1 ? 4 : MT == 2 ? 3 : 2) fp8_gemv_kernel(const Fp8GemvParams p)
 {
     extern __shared__ __align__(16) unsigned char smem[];
     cg::cluster_group cluster = cg::this_cluster();
@@ -247,8 +247,8 @@ template <int MT, int D> static int launch_fp8(const Fp8GemvParams &p, int ks, c
 // True when the tuned kernel applies; otherwise the caller uses the generic row-format kernel.
 bool fp8_gemv_fast_supported(int m, int k, int block_in, const void *w)
 {
-    return m <= 16 && k % 512 == 0 && block_in % 64 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
-           (size_t)m * (k + 8) * 2 <= 160 * 1024;
+    return m <= 32 && k % 512 == 0 && block_in % 64 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 &&
+           (size_t)m * (k / (m > 16 ? 4 : 1) + 8) * 2 <= 160 * 1024;
 }
 
 int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale_inv, int s_in, int block_out, int block_in,
@@ -262,7 +262,8 @@ int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale_inv, int s
     // Few tokens: small row groups, so that every CTA of the grid is resident at once. More tokens:
     // more row tiles per CTA, which share the staged x.
     int nrt = 2, kw = 4, ks = 1, d = 2;
-    if (m > 8 && k % 256 == 0) { nrt = 8; kw = 1; ks = 2; }
+    if (m > 16) { nrt = 8; kw = 1; ks = 4; }
+    else if (m > 8) { nrt = 8; kw = 1; ks = 2; }
     else if (m > 2) { nrt = 4; kw = 2; ks = 2; }
     if (const char *env = getenv("OXQ_FP8_GEMV_TUNE")) { // bench-harness knob: "row_tiles,k_warps,cluster,depth"
         int a = 0, b = 0, cc = 0, dd = 0;
@@ -273,7 +274,8 @@ int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale_inv, int s
     }
     p.row_tiles = nrt; p.k_warps = kw;
     if (m <= 8) return d == 1 ? launch_fp8<1, 1>(p, ks, st) : d == 2 ? launch_fp8<1, 2>(p, ks, st) : launch_fp8<1, 4>(p, ks, st);
-    return d == 1 ? launch_fp8<2, 1>(p, ks, st) : launch_fp8<2, 2>(p, ks, st);
+    if (m <= 16) return d == 1 ? launch_fp8<2, 1>(p, ks, st) : launch_fp8<2, 2>(p, ks, st);
+    return launch_fp8<4, 2>(p, ks, st);
 }
 
 } // namespace oxq
