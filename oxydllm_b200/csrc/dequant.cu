@@ -193,33 +193,205 @@ awq_slab_bf16_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__res
     }
 }
 
-// FP8: 16 bytes in, 32 bytes out per thread; one scale lookup per 16 elements
-// (requires the scale block along k to be a multiple of 16).
-__global__ void __launch_bounds__(256)
-fp8_slab_bf16_kernel(const uint8_t *__restrict__ weight, const float *__restrict__ scale_inv, int s_in, int block_out,
-                     int block_in, __nv_bfloat16 *__restrict__ out, int n_cnt, int k, int row_off)
+// ---- fast slab producers (same bits as the kernels above, a fraction of the instructions) -------
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi)
 {
-    const size_t total16 = (size_t)n_cnt * k / 16;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total16;
-         idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t e = idx * 16;
-        const int r = (int)(e / k), c = (int)(e % k);
-        const uint4 w = __ldcs(reinterpret_cast<const uint4 *>(weight) + idx);
-        const float s = scale_inv ? scale_inv[(size_t)((row_off + r) / block_out) * s_in + c / block_in] : 1.0f;
-        const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// AWQ: a CTA of 256 threads owns 128 input rows x 32 packed words (256 out columns). The words are
+// staged with coalesced 16-byte loads; then thread (word jj = lane, k block kb = warp) turns its 16
+// words into, for each of the word's eight out columns, 16 consecutive k of that column's dense row;
+// the rows are stored 256 contiguous bytes at a time. q - z is formed exactly in f32 by the 2^23 trick
+// ((2^23 + q) - (2^23 + z)), multiplied by the scale in f32 and rounded to bf16 once, as the
+// element-wise kernel does. Needs group_size % 16 == 0 and k % 16 == 0.
+__global__ void __launch_bounds__(256)
+awq_slab16_bf16_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict__ qzeros,
+                       const void *__restrict__ scales, int scales_dtype, __nv_bfloat16 *__restrict__ out, int k,
+                       int n_cnt, int group_size, int n_full, int n_off, int vec_ok)
+{
+    __shared__ __align__(16) uint32_t raw[128][32];
+    __shared__ __align__(16) unsigned char stage[2][32 * 272];
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int packed_full = n_full >> 3;
+    const int jw0 = (n_off >> 3) + blockIdx.x * 32; // first packed word of the tile (absolute)
+    const int jw_end = (n_off + n_cnt) >> 3;
+    const int k0 = blockIdx.y * 128;
+    {
+        const int r_in = t >> 3, w4 = (t & 7) * 4;
+#pragma unroll
+        for (int it = 0; it < 4; it++) {
+            const int r = r_in + 32 * it;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (k0 + r < k) {
+                const uint32_t *src = qweight + (size_t)(k0 + r) * packed_full + jw0 + w4;
+                if (vec_ok && jw0 + w4 + 4 <= jw_end) v = __ldcs(reinterpret_cast<const uint4 *>(src));
+                else {
+                    if (jw0 + w4 + 0 < jw_end) v.x = __ldcs(src + 0);
+                    if (jw0 + w4 + 1 < jw_end) v.y = __ldcs(src + 1);
+                    if (jw0 + w4 + 2 < jw_end) v.z = __ldcs(src + 2);
+                    if (jw0 + w4 + 3 < jw_end) v.w = __ldcs(src + 3);
+                }
+            }
+            *reinterpret_cast<uint4 *>(&raw[r][w4]) = v;
+        }
+    }
+    __syncthreads();
+    const int j = jw0 + lane, kb = k0 + 16 * warp;
+    const bool active = j < jw_end && kb < k;
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) w[i] = raw[16 * warp + i][lane];
+    uint32_t zw = 0u;
+    float sc[8]; // scales of out columns 8j .. 8j+7
+#pragma unroll
+    for (int c = 0; c < 8; c++) sc[c] = 0.0f;
+    if (active) {
+        const int g = kb / group_size;
+        zw = __ldg(qzeros + (size_t)g * packed_full + j);
+        const size_t s0 = (size_t)g * n_full + (size_t)j * 8;
+#pragma unroll
+        for (int c = 0; c < 8; c++) sc[c] = load_as_f32(scales, scales_dtype, s0 + c);
+    }
+    // The 16 k of one out column go through shared memory so that a warp stores whole rows: for
+    // nibble p the tile's 32 rows x 128 k (256 bytes each, padded to 272) are written by their
+    // producers, then warp w stores rows 4w .. 4w+3, eight lanes x 32 bytes per row.
+    const int row_l = 4 * warp + (lane >> 3), piece = lane & 7; // the row and 32-byte piece this lane stores
+    const int j_st = jw0 + row_l;
+    const bool st_ok = j_st < jw_end && k0 + 16 * piece < k;
+    __nv_bfloat16 *st0 = out + (size_t)(8 * (j_st - (n_off >> 3))) * k + k0 + 16 * piece;
+#pragma unroll
+    for (int p = 0; p < 8; p++) {
+        const int c = p < 4 ? 2 * p : 2 * (p - 4) + 1; // nibble p holds out column c of the word
+        unsigned char *buf = stage[p & 1];
+        if (active) {
+            const float zf = __uint_as_float(0x4B000000u | ((zw >> (4 * p)) & 0xFu));
+            const float s = sc[c];
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float a = __uint_as_float(0x4B000000u | ((w[2 * i] >> (4 * p)) & 0xFu)) - zf;
+                const float b = __uint_as_float(0x4B000000u | ((w[2 * i + 1] >> (4 * p)) & 0xFu)) - zf;
+                o[i] = pack_bf16x2_rn(__fmul_rn(a, s), __fmul_rn(b, s));
+            }
+            uint4 *d = reinterpret_cast<uint4 *>(buf + lane * 272 + warp * 32);
+            d[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+        __syncthreads(); // buffer p & 1 complete; its previous readers (nibble p - 2) passed the sync of p - 1
+        if (st_ok) {
+            const uint4 *sv = reinterpret_cast<const uint4 *>(buf + row_l * 272 + piece * 32);
+            uint4 *dst = reinterpret_cast<uint4 *>(st0 + (size_t)c * k);
+            dst[0] = sv[0];
+            dst[1] = sv[1];
+        }
+    }
+}
+
+// FP8: a thread converts 16 consecutive bytes of a row: the hardware widens E4M3 pairs to f16 pairs
+// (exact), f16 -> f32 is exact, one f32 multiply by the block's scale, one rounding to bf16. Words
+// holding a NaN byte take the element-wise route so that the NaN bits stay the same.
+// A CTA covers 256 * 16 columns of FP8_SLAB_ROWS rows.
+constexpr int FP8_SLAB_ROWS = 4;
+__global__ void __launch_bounds__(256)
+fp8_slab16_bf16_kernel(const uint8_t *__restrict__ weight, const float *__restrict__ scale_inv, int s_in, int block_out,
+                       int block_in, __nv_bfloat16 *__restrict__ out, int n_cnt, int k, int row_off)
+{
+    const int c16 = blockIdx.x * 256 + threadIdx.x;
+    if (c16 * 16 >= k) return;
+    const int kb = scale_inv ? (c16 * 16) / block_in : 0;
+#pragma unroll
+    for (int r = 0; r < FP8_SLAB_ROWS; r++) {
+        const int row = blockIdx.y * FP8_SLAB_ROWS + r;
+        if (row >= n_cnt) break;
+        const uint4 wv = __ldcs(reinterpret_cast<const uint4 *>(weight + (size_t)row * k) + c16);
+        const float s = scale_inv ? __ldg(scale_inv + (size_t)((row_off + row) / block_out) * s_in + kb) : 1.0f;
+        const uint32_t v[4] = {wv.x, wv.y, wv.z, wv.w};
         uint32_t o[8];
 #pragma unroll
-        for (int q = 0; q < 4; q++)
+        for (int q = 0; q < 4; q++) {
+            if ((((v[q] & 0x7F7F7F7Fu) + 0x01010101u) & 0x80808080u) == 0u) {
+                uint32_t h01, h23;
+                asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+                    "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+                    : "=r"(h01), "=r"(h23)
+                    : "r"(v[q]));
+                const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&h01));
+                const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&h23));
+                if (scale_inv) {
+                    o[2 * q] = pack_bf16x2_rn(__fmul_rn(s, f01.x), __fmul_rn(s, f01.y));
+                    o[2 * q + 1] = pack_bf16x2_rn(__fmul_rn(s, f23.x), __fmul_rn(s, f23.y));
+                } else {
+                    o[2 * q] = pack_bf16x2_rn(f01.x, f01.y);
+                    o[2 * q + 1] = pack_bf16x2_rn(f23.x, f23.y);
+                }
+            } else {
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                float a = e4m3_to_f32((wv[q] >> (16 * h)) & 0xFFu), b = e4m3_to_f32((wv[q] >> (16 * h + 8)) & 0xFFu);
-                if (scale_inv) { a = __fmul_rn(s, a); b = __fmul_rn(s, b); }
-                __nv_bfloat162 hh = __floats2bfloat162_rn(a, b);
-                o[2 * q + h] = *reinterpret_cast<uint32_t *>(&hh);
+                for (int h = 0; h < 2; h++) {
+                    float a = e4m3_to_f32((v[q] >> (16 * h)) & 0xFFu), b = e4m3_to_f32((v[q] >> (16 * h + 8)) & 0xFFu);
+                    if (scale_inv) { a = __fmul_rn(s, a); b = __fmul_rn(s, b); }
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(a, b);
+                    o[2 * q + h] = *reinterpret_cast<uint32_t *>(&hh);
+                }
             }
-        uint4 *dst = reinterpret_cast<uint4 *>(out + e);
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t)row * k) + 2 * c16;
         dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
         dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
+// MXFP4: a thread converts one 16-byte block (32 weights, one E8M0 scale). A 256-entry table in
+// shared memory maps a byte to its two E2M1 values as a bf16 pair; scaling by 2^(s-127) is an exact
+// bf16 multiply while the result stays normal (4 <= s <= 250); other scales, NaN and the
+// subnormal 2^-127 among them, take the element-wise route.
+__global__ void __launch_bounds__(256)
+mxfp4_slab16_bf16_kernel(const uint8_t *__restrict__ blocks, const uint8_t *__restrict__ scales,
+                         __nv_bfloat16 *__restrict__ out, size_t total_blocks)
+{
+    __shared__ uint32_t lut[256];
+    {
+        const uint32_t b = threadIdx.x;
+        __nv_bfloat162 hh = __floats2bfloat162_rn(e2m1_to_f32(b & 0xFu), e2m1_to_f32(b >> 4));
+        lut[b] = *reinterpret_cast<uint32_t *>(&hh);
+    }
+    __syncthreads();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_blocks;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const uint4 bv = __ldcs(reinterpret_cast<const uint4 *>(blocks) + idx);
+        const uint32_t sb = scales[idx];
+        const uint32_t v[4] = {bv.x, bv.y, bv.z, bv.w};
+        uint32_t o[16];
+        if (sb >= 4u && sb <= 250u) {
+            const uint32_t s2 = (sb << 7) | (sb << 23); // 2^(s-127) as a bf16 pair
+            const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162 *>(&s2);
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+#pragma unroll
+                for (int h = 0; h < 4; h++) {
+                    const uint32_t e = lut[(v[q] >> (8 * h)) & 0xFFu];
+                    const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&e), sc);
+                    o[4 * q + h] = *reinterpret_cast<const uint32_t *>(&r);
+                }
+        } else {
+            const float s = e8m0_to_f32(sb);
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+#pragma unroll
+                for (int h = 0; h < 4; h++) {
+                    const uint32_t b = (v[q] >> (8 * h)) & 0xFFu;
+                    __nv_bfloat162 hh = __halves2bfloat162(narrow<__nv_bfloat16>(__fmul_rn(e2m1_to_f32(b & 0xFu), s)),
+                                                           narrow<__nv_bfloat16>(__fmul_rn(e2m1_to_f32(b >> 4), s)));
+                    o[4 * q + h] = *reinterpret_cast<uint32_t *>(&hh);
+                }
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(out) + 4 * idx;
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        dst[2] = make_uint4(o[8], o[9], o[10], o[11]);
+        dst[3] = make_uint4(o[12], o[13], o[14], o[15]);
     }
 }
 
@@ -235,6 +407,14 @@ static int grid_for(size_t work_items, int block = 256)
 int awq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
                           __nv_bfloat16 *out, int k, int n_full, int group_size, int n_off, int n_cnt, cudaStream_t st)
 {
+    if (group_size % 16 == 0 && k % 16 == 0 && n_off % 8 == 0 && n_cnt % 8 == 0 && aligned(out, 16)) {
+        const int vec_ok = aligned(qweight, 16) && (n_full >> 3) % 4 == 0 && (n_off >> 3) % 4 == 0;
+        dim3 grid(ceil_div(n_cnt, 256), ceil_div(k, 128));
+        awq_slab16_bf16_kernel<<<grid, 256, 0, st>>>(qweight, qzeros, scales, scales_dtype, out, k, n_cnt, group_size,
+                                                     n_full, n_off, vec_ok);
+        OXQ_LAUNCH_CHECK("awq_slab16_bf16_kernel");
+        return OXQ_OK;
+    }
     dim3 grid(ceil_div(n_cnt, 256), ceil_div(k, 64));
     awq_slab_bf16_kernel<<<grid, 256, 0, st>>>(qweight, qzeros, scales, scales_dtype, out, k, n_cnt, group_size,
                                                n_full, n_off);
@@ -273,10 +453,11 @@ int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *
 int fp8_dequant_rows_bf16(const uint8_t *weight, const float *scale_inv, int s_in, int block_out, int block_in,
                           __nv_bfloat16 *out, int k, int n_off, int n_cnt, cudaStream_t st)
 {
-    if (k % 16 == 0 && block_in % 16 == 0 && aligned(weight, 16)) {
-        fp8_slab_bf16_kernel<<<grid_for((size_t)n_cnt * k / 16), 256, 0, st>>>(
-            weight + (size_t)n_off * k, scale_inv, s_in, block_out, block_in, out, n_cnt, k, n_off);
-        OXQ_LAUNCH_CHECK("fp8_slab_bf16_kernel");
+    if (k % 16 == 0 && block_in % 16 == 0 && aligned(weight, 16) && aligned(out, 16)) {
+        dim3 grid(ceil_div(k / 16, 256), ceil_div(n_cnt, FP8_SLAB_ROWS));
+        fp8_slab16_bf16_kernel<<<grid, 256, 0, st>>>(weight + (size_t)n_off * k, scale_inv, s_in, block_out, block_in,
+                                                     out, n_cnt, k, n_off);
+        OXQ_LAUNCH_CHECK("fp8_slab16_bf16_kernel");
         return OXQ_OK;
     }
     fp8_dequant_kernel<__nv_bfloat16><<<grid_for((size_t)n_cnt * k / 4), 256, 0, st>>>(
@@ -291,6 +472,13 @@ int mxfp4_dequant_rows_bf16(const uint8_t *blocks, const uint8_t *scales, __nv_b
                             int n_cnt, cudaStream_t st)
 {
     const size_t total_bytes = (size_t)n_cnt * k / 2;
+    if (k % 32 == 0 && aligned(blocks + (size_t)n_off * (k / 2), 16) && aligned(out, 16)) {
+        const size_t total_blocks = total_bytes / 16;
+        mxfp4_slab16_bf16_kernel<<<grid_for(total_blocks), 256, 0, st>>>(
+            blocks + (size_t)n_off * (k / 2), scales + (size_t)n_off * (k / 32), out, total_blocks);
+        OXQ_LAUNCH_CHECK("mxfp4_slab16_bf16_kernel");
+        return OXQ_OK;
+    }
     mxfp4_dequant_kernel<__nv_bfloat16><<<grid_for(total_bytes), 256, 0, st>>>(
         blocks + (size_t)n_off * (k / 2), scales + (size_t)n_off * (k / 32), out, total_bytes);
     OXQ_LAUNCH_CHECK("mxfp4_dequant_kernel");
@@ -319,6 +507,9 @@ OXQ_EXPORT int oxq_awq_dequant(const uint32_t *qweight, const uint32_t *qzeros, 
     OXQ_REQUIRE(n % 8 == 0, OXQ_ERR_BAD_SHAPE, "AWQ out_features (%d) not divisible by pack factor 8", n);
     OXQ_REQUIRE(k % group_size == 0, OXQ_ERR_BAD_SHAPE,
                 "quant in_features (%d) not divisible by group size (%d)", k, group_size);
+    if (out_dtype == OXQ_BF16) // same bits, the fast producer of the tensor-core path
+        return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, (__nv_bfloat16 *)w_out, k, n, group_size, 0, n,
+                                     (cudaStream_t)stream);
     dim3 grid(ceil_div(n / 8, 8), ceil_div(k, AWQ_TK));
     DISPATCH_OUT(out_dtype, awq_dequant_kernel<OutT><<<grid, 256, 0, (cudaStream_t)stream>>>(
                                 qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size, n, 0));
@@ -396,6 +587,9 @@ OXQ_EXPORT int oxq_fp8_dequant(const uint8_t *weight, const float *scale_inv, in
         bo = n / s_out;
         bi = k / s_in;
     }
+    if (out_dtype == OXQ_BF16) // same bits, the fast producer of the tensor-core path
+        return fp8_dequant_rows_bf16(weight, scale_inv, scale_inv ? s_in : 1, bo, bi, (__nv_bfloat16 *)w_out, k, 0, n,
+                                     (cudaStream_t)stream);
     DISPATCH_OUT(out_dtype, fp8_dequant_kernel<OutT><<<grid_for((size_t)n * k / 4), 256, 0, (cudaStream_t)stream>>>(
                                 weight, scale_inv, s_in, bo, bi, (OutT *)w_out, n, k, 0));
     OXQ_LAUNCH_CHECK("fp8_dequant_kernel");
@@ -409,6 +603,8 @@ OXQ_EXPORT int oxq_mxfp4_dequant(const uint8_t *blocks, const uint8_t *scales, v
     OXQ_REQUIRE(blocks && scales && w_out, OXQ_ERR_NULL, "oxq_mxfp4_dequant: null pointer");
     OXQ_REQUIRE(valid_dtype(out_dtype), OXQ_ERR_UNSUPPORTED, "oxq_mxfp4_dequant: unsupported out dtype");
     OXQ_REQUIRE(n > 0 && k > 0 && k % 32 == 0, OXQ_ERR_BAD_SHAPE, "MXFP4: cols %d must be a multiple of 32", k);
+    if (out_dtype == OXQ_BF16) // same bits, the fast producer of the tensor-core path
+        return mxfp4_dequant_rows_bf16(blocks, scales, (__nv_bfloat16 *)w_out, k, 0, n, (cudaStream_t)stream);
     const size_t total_bytes = (size_t)n * k / 2;
     DISPATCH_OUT(out_dtype, mxfp4_dequant_kernel<OutT><<<grid_for(total_bytes), 256, 0, (cudaStream_t)stream>>>(
                                 blocks, scales, (OutT *)w_out, total_bytes));

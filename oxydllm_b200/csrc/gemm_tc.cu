@@ -323,7 +323,7 @@ struct GroupedParams {
     const void *bias;
     void *out;
     int *flag;
-    int group, e_first, nw, k, tiles_n, bn, bias_dtype, ldo, epi;
+    int group, e_first, nw, k, tiles_n, bn, bias_dtype, ldo, epi, vec_ok;
     float limit;
 };
 
@@ -437,32 +437,71 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int col0 = n0 + cb * 32;
                 if (r_in < en.y && col0 < p.nw) {
                     const size_t bcol = (size_t)en.z * p.nw + col0;
-                    if (p.epi == 0) {
+                    const bool full = p.vec_ok && col0 + 32 <= p.nw;
+                    float bv[32]; // bias of the 32 columns (the same for every lane: broadcast loads)
+                    if (p.bias && full && p.bias_dtype == OXQ_BF16 && (bcol & 7) == 0) {
+                        const uint4 *bp = reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(p.bias) + bcol);
 #pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            if (col0 + j < p.nw) { // nw is even
-                                float v0 = __uint_as_float(r[j]), v1 = __uint_as_float(r[j + 1]);
-                                if (p.bias) {
-                                    v0 += load_as_f32(p.bias, p.bias_dtype, bcol + j);
-                                    v1 += load_as_f32(p.bias, p.bias_dtype, bcol + j + 1);
-                                }
-                                *reinterpret_cast<__nv_bfloat162 *>(outp + row * p.ldo + col0 + j) = __floats2bfloat162_rn(v0, v1);
+                        for (int q = 0; q < 4; q++) {
+                            const uint4 t = __ldg(bp + q);
+                            const uint32_t tw[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                bv[8 * q + 2 * u] = __uint_as_float(tw[u] << 16);
+                                bv[8 * q + 2 * u + 1] = __uint_as_float(tw[u] & 0xFFFF0000u);
                             }
                         }
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            if (col0 + j < p.nw) {
-                                float gate = __uint_as_float(r[j]), up = __uint_as_float(r[j + 1]);
-                                if (p.bias) {
-                                    gate += load_as_f32(p.bias, p.bias_dtype, bcol + j);
-                                    up += load_as_f32(p.bias, p.bias_dtype, bcol + j + 1);
-                                }
-                                gate = fminf(gate, p.limit);
-                                up = fminf(fmaxf(up, -p.limit), p.limit);
-                                const float sig = 1.0f / (expf(-1.702f * gate) + 1.0f);
-                                outp[row * p.ldo + ((col0 + j) >> 1)] = __float2bfloat16_rn((up + 1.0f) * (gate * sig));
+                        for (int j = 0; j < 32; j++)
+                            bv[j] = (p.bias && col0 + j < p.nw) ? load_as_f32(p.bias, p.bias_dtype, bcol + j) : 0.0f;
+                    }
+                    if (p.epi == 0) {
+                        if (full) { // 32 columns = 64 bytes of this lane's row
+                            uint32_t packed[16];
+#pragma unroll
+                            for (int j = 0; j < 16; j++) {
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) + bv[2 * j],
+                                                                          __uint_as_float(r[2 * j + 1]) + bv[2 * j + 1]);
+                                packed[j] = *reinterpret_cast<uint32_t *>(&h2);
                             }
+                            uint4 *dst = reinterpret_cast<uint4 *>(outp + row * p.ldo + col0);
+#pragma unroll
+                            for (int q = 0; q < 4; q++)
+                                dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) {
+                                if (col0 + j < p.nw) { // nw is even
+                                    *reinterpret_cast<__nv_bfloat162 *>(outp + row * p.ldo + col0 + j) =
+                                        __floats2bfloat162_rn(__uint_as_float(r[j]) + bv[j], __uint_as_float(r[j + 1]) + bv[j + 1]);
+                                }
+                            }
+                        }
+                    } else {
+                        float act[16];
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            float gate = __uint_as_float(r[2 * j]) + bv[2 * j], up = __uint_as_float(r[2 * j + 1]) + bv[2 * j + 1];
+                            gate = fminf(gate, p.limit);
+                            up = fminf(fmaxf(up, -p.limit), p.limit);
+                            const float sig = __fdividef(1.0f, __expf(-1.702f * gate) + 1.0f);
+                            act[j] = (up + 1.0f) * (gate * sig);
+                        }
+                        if (full) { // 16 outputs = 32 bytes of this lane's row
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(act[2 * j], act[2 * j + 1]);
+                                packed[j] = *reinterpret_cast<uint32_t *>(&h2);
+                            }
+                            uint4 *dst = reinterpret_cast<uint4 *>(outp + row * p.ldo + (col0 >> 1));
+                            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (col0 + 2 * j < p.nw) outp[row * p.ldo + ((col0 >> 1) + j)] = __float2bfloat16_rn(act[j]);
                         }
                     }
                 }
@@ -603,6 +642,7 @@ int gemm_grouped(const void *a, int a_rows, const void *w, int slab_experts, int
     p.entries = entries; p.grp_beg = grp_beg; p.bias = bias; p.out = out; p.flag = flag;
     p.group = group; p.e_first = e_first; p.nw = nw; p.k = k; p.tiles_n = ceil_div(nw, bn); p.bn = bn;
     p.bias_dtype = bias_dtype; p.ldo = ldo; p.epi = epi; p.limit = limit;
+    p.vec_ok = (ldo % 8 == 0 && aligned(out, 16)) ? 1 : 0;
     gemm_grouped_kernel<<<sm_count(), 192, TC_SMEM_BYTES, stream>>>(map_a, map_b, p);
     OXQ_LAUNCH_CHECK("gemm_grouped_kernel");
     return OXQ_OK;

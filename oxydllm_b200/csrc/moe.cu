@@ -212,9 +212,11 @@ static MoeLayout moe_layout(int tokens, int top_k, int n_exp, int hidden, int in
 {
     MoeLayout L;
     const size_t pairs = (size_t)tokens * top_k;
-    // Experts dequantized at once: as many as fit 144 MiB of bf16 gate_up weights, at least one.
+    // Experts dequantized at once: as many as fit 1152 MiB of bf16 gate_up weights (all 32 experts of
+    // a GPT-OSS-20B layer), at least one. One grouped GEMM over many experts fills whole rounds of
+    // the persistent grid; small groups left a third of the SM-rounds idle and paid a launch each.
     const size_t per_expert = (size_t)2 * inter * hidden * 2;
-    int ge = (int)((144u << 20) / per_expert);
+    int ge = (int)(((size_t)1152 << 20) / per_expert);
     if (ge < 1) ge = 1;
     if (ge > n_exp) ge = n_exp;
     L.group_experts = ge;
