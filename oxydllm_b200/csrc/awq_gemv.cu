@@ -44,6 +44,7 @@ struct AwqGemvParams {
     int m, k, n, group_size;
     int packed_out;
     int steps_per_cta; // 16-row steps handled by one CTA of the cluster
+    int token_split;   // main variant: neighbouring CTAs that share an n tile and take 8*MT tokens each (>= 1)
 };
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2])
@@ -330,7 +331,11 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, c = lane & 3;
     const int rank = blockIdx.y, nranks = gridDim.y;
-    const int jtile = blockIdx.x * 8 * V;
+    // Token tiles of one n tile sit in neighbouring CTAs: they stream the same weights at the same
+    // time, so all but the first reader hit in L2.
+    const int zt = blockIdx.x % p.token_split;
+    const int m0 = zt * 8 * MT, m_loc = min(8 * MT, p.m - m0); // this CTA's tokens [m0, m0 + m_loc)
+    const int jtile = (blockIdx.x / p.token_split) * 8 * V;
     const int jbase = jtile + g * V;
     const bool j_ok = jbase < p.packed_out;
     const int steps = p.steps_per_cta; // 16-row steps per warp slice, identical for all slices; a multiple of D
@@ -357,7 +362,7 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
     // token does not exist read a block of zeros instead (stride 0).
     const int xrow = kr + 16; // elements
     __half *xs = reinterpret_cast<__half *>(smem);
-    uint32_t *zeros = reinterpret_cast<uint32_t *>(smem + (size_t)p.m * xrow * sizeof(__half));
+    uint32_t *zeros = reinterpret_cast<uint32_t *>(smem + (size_t)m_loc * xrow * sizeof(__half));
     if (tid < 4) zeros[tid] = 0u;
     // Running totals live in shared memory, one 16-byte slot per (warp, MMA tile, lane), private to the
     // lane until the final reduction reads them: registers are kept for weights in flight instead.
@@ -365,8 +370,8 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
     float4 *mine = red + (size_t)warp * (NACC / 4) * 32 + lane;
 #pragma unroll
     for (int i = 0; i < NACC / 4; i++) mine[i * 32] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int row = 0; row < p.m; row++) {
-        const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)row * p.k + k_cta);
+    for (int row = 0; row < m_loc; row++) {
+        const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)(m0 + row) * p.k + k_cta);
         uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
         for (int q4 = tid; q4 < (kr >> 2); q4 += KW * 32) {
             const uint2 raw = __ldg(src + q4);
@@ -456,7 +461,7 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
     int xstep[MT];
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
-        const bool real = 8 * mt + g < p.m;
+        const bool real = 8 * mt + g < m_loc;
         xw[mt] = real ? xs + (size_t)(8 * mt + g) * xrow + warp * steps * 16 + 4 * c : reinterpret_cast<const __half *>(zeros);
         xstep[mt] = real ? 16 : 0;
     }
@@ -525,7 +530,7 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
         const int og = ol >> 2, oc = ol & 3;
         const int word = jtile + og * V + v;
         const int row = 8 * mt + 2 * oc;
-        if (word < p.packed_out && row < p.m) {
+        if (word < p.packed_out && row < m_loc) {
             float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             for (int q = 0; q < nranks; q++) {
                 const float4 *src = nranks > 1 ? cluster.map_shared_rank(red, q) : red;
@@ -538,11 +543,11 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
             const size_t col = (size_t)word * 8 + 2 * t;
             float b0 = 0.0f, b1 = 0.0f;
             if (p.bias) { b0 = load_as_f32(p.bias, p.bias_dtype, col); b1 = load_as_f32(p.bias, p.bias_dtype, col + 1); }
-            store_as(p.y, p.y_dtype, (size_t)row * p.n + col, sum.x + b0);
-            store_as(p.y, p.y_dtype, (size_t)row * p.n + col + 1, sum.z + b1);
-            if (row + 1 < p.m) {
-                store_as(p.y, p.y_dtype, (size_t)(row + 1) * p.n + col, sum.y + b0);
-                store_as(p.y, p.y_dtype, (size_t)(row + 1) * p.n + col + 1, sum.w + b1);
+            store_as(p.y, p.y_dtype, (size_t)(m0 + row) * p.n + col, sum.x + b0);
+            store_as(p.y, p.y_dtype, (size_t)(m0 + row) * p.n + col + 1, sum.z + b1);
+            if (row + 1 < m_loc) {
+                store_as(p.y, p.y_dtype, (size_t)(m0 + row + 1) * p.n + col, sum.y + b0);
+                store_as(p.y, p.y_dtype, (size_t)(m0 + row + 1) * p.n + col + 1, sum.w + b1);
             }
         }
     }
@@ -553,7 +558,8 @@ template <int MT, int V, int D, int MINB>
 static int launch_awq_gemv_group(const AwqGemvParams &p, int nranks, cudaStream_t stream)
 {
     constexpr int NACC = V * 4 * MT * 4;
-    const size_t xbytes = (size_t)p.m * (GK_KW * p.steps_per_cta * 16 + 16) * sizeof(__half) + 16;
+    const int m_cta = p.m < 8 * MT ? p.m : 8 * MT;
+    const size_t xbytes = (size_t)m_cta * (GK_KW * p.steps_per_cta * 16 + 16) * sizeof(__half) + 16;
     const size_t red = (size_t)GK_KW * NACC * 32 * sizeof(float);
     const size_t smem = xbytes + red;
     auto kern = awq_gemv_group_kernel<MT, V, D, MINB>;
@@ -565,7 +571,7 @@ static int launch_awq_gemv_group(const AwqGemvParams &p, int nranks, cudaStream_
         if (device < 64) configured[device] = smem;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ceil_div(p.packed_out, 8 * V), nranks, 1);
+    cfg.gridDim = dim3(ceil_div(p.packed_out, 8 * V) * p.token_split, nranks, 1);
     cfg.blockDim = dim3(GK_KW * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -656,43 +662,49 @@ OXQ_EXPORT int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight,
     cudaStream_t st = (cudaStream_t)stream;
 
     // Main path: contiguous k slices, 4 warps x R CTAs, each slice a whole number of groups or a
-    // divisor of one group; R is chosen for about 2000 warps in flight (13 per SM).
+    // divisor of one group. A CTA takes 8 * mtc tokens; more tokens go to neighbouring CTAs of the
+    // same n tile (token split).
+    p.token_split = 1;
     {
-        const int fv_default = mt <= 2 ? 2 : 1;
-        int fv = fv_default;
-        while (fv > 1 && p.packed_out % fv != 0) fv /= 2;
-        int r_force = 0, depth = 2, minb = 4;
+        // Measured on K = 4096, N = 14336: up to 8 tokens one CTA column with k split in 4; 9..16 tokens
+        // 16 tokens per CTA, k split in 2; more tokens 8 per CTA on neighbouring CTAs, k split in 2.
+        int fv = 2, mtc = (m > 8 && m <= 16) ? 2 : 1, r_force = 0, depth = 2, minb = 4;
         bool ok = aligned(scales, 16);
-        if (const char *env = getenv("OXQ_AWQ_GEMV_FAST")) { // bench-harness knob: "0" disables, else "V[,R[,D]]"
-            int ev = 0, er = 0, ed = 0, eb = 0;
-            const int got = sscanf(env, "%d,%d,%d,%d", &ev, &er, &ed, &eb);
-            if (got >= 4 && eb == 6) minb = 6;
+        if (const char *env = getenv("OXQ_AWQ_GEMV_FAST")) { // bench-harness knob: "0" disables, else "V[,R[,D[,B[,MT]]]]"
+            int ev = 0, er = 0, ed = 0, eb = 0, em = 0;
+            const int got = sscanf(env, "%d,%d,%d,%d,%d", &ev, &er, &ed, &eb, &em);
             if (got >= 1 && ev == 0) ok = false;
-            if (got >= 1 && (ev == 1 || ev == 2 || ev == 4) && p.packed_out % ev == 0 && 16 * ev * mt <= 64) fv = ev;
+            if (got >= 1 && (ev == 1 || ev == 2 || ev == 4)) fv = ev;
             if (got >= 2 && (er == 1 || er == 2 || er == 4 || er == 8)) r_force = er;
             if (got >= 3 && (ed == 2 || ed == 4)) depth = ed;
+            if (got >= 4 && eb == 6) minb = 6;
+            if (got >= 5 && (em == 1 || em == 2 || em == 4)) mtc = em;
         }
+        while (fv > 1 && p.packed_out % fv != 0) fv /= 2;
+        const int split = ceil_div(m, 8 * mtc);
+        const int m_cta = m < 8 * mtc ? m : 8 * mtc;
         const int gsteps = group_size / 16;
-        const int n_tiles = ceil_div(p.packed_out, 8 * fv);
+        const int n_tiles = ceil_div(p.packed_out, 8 * fv) * split;
         int r = 0;
         for (int cand : {8, 4, 2, 1}) {
             if (total_steps % (GK_KW * cand) != 0) continue;
             const int sl = total_steps / (GK_KW * cand);
             if (!(sl % gsteps == 0 || gsteps % sl == 0) || sl % depth != 0) continue;
-            if ((size_t)m * (GK_KW * sl * 16 + 16) * 2 > 160 * 1024) continue;
-            if (r_force ? cand == r_force : (r == 0 || n_tiles * GK_KW * cand >= (mt == 1 ? 1700 : 850))) r = cand;
+            if ((size_t)m_cta * (GK_KW * sl * 16 + 16) * 2 > 160 * 1024) continue;
+            if (r_force ? cand == r_force : (r == 0 || (m > 8 ? cand >= 2 : n_tiles * GK_KW * cand >= 1700))) r = cand;
         }
-        if (ok && r != 0 && (mt <= 2 || getenv("OXQ_AWQ_GEMV_FAST"))) { // measured: the ring kernel below is faster for m > 16
+        if (ok && r != 0) {
             p.steps_per_cta = total_steps / (GK_KW * r);
-            if (mt == 1 && fv == 4) return launch_awq_gemv_group<1, 4, 2, 2>(p, r, st);
-            if (mt == 1 && fv == 2 && depth == 2 && minb == 6) return launch_awq_gemv_group<1, 2, 2, 6>(p, r, st);
-            if (mt == 1 && fv == 2 && depth == 4 && minb == 6) return launch_awq_gemv_group<1, 2, 4, 6>(p, r, st);
-            if (mt == 1 && fv == 2 && depth == 2) return launch_awq_gemv_group<1, 2, 2, 4>(p, r, st);
-            if (mt == 1 && fv == 2) return launch_awq_gemv_group<1, 2, 4, 4>(p, r, st);
-            if (mt == 1 && fv == 1) return launch_awq_gemv_group<1, 1, 4, 4>(p, r, st);
-            if (mt == 2 && fv == 2) return launch_awq_gemv_group<2, 2, 2, 2>(p, r, st);
-            if (mt == 2 && fv == 1) return launch_awq_gemv_group<2, 1, 2, 4>(p, r, st);
-            if (mt == 4 && fv == 1) return launch_awq_gemv_group<4, 1, 2, 2>(p, r, st);
+            p.token_split = split;
+            if (mtc == 1 && fv == 4) return launch_awq_gemv_group<1, 4, 2, 2>(p, r, st);
+            if (mtc == 1 && fv == 2 && depth == 2 && minb == 6) return launch_awq_gemv_group<1, 2, 2, 6>(p, r, st);
+            if (mtc == 1 && fv == 2 && depth == 2) return launch_awq_gemv_group<1, 2, 2, 4>(p, r, st);
+            if (mtc == 1 && fv == 2) return launch_awq_gemv_group<1, 2, 4, 4>(p, r, st);
+            if (mtc == 1 && fv == 1) return launch_awq_gemv_group<1, 1, 4, 4>(p, r, st);
+            if (mtc == 2 && fv == 2) return launch_awq_gemv_group<2, 2, 2, 2>(p, r, st);
+            if (mtc == 2 && fv == 1) return launch_awq_gemv_group<2, 1, 2, 4>(p, r, st);
+            if (mtc == 4 && fv == 1) return launch_awq_gemv_group<4, 1, 2, 2>(p, r, st);
+            p.token_split = 1;
         }
     }
 

@@ -307,3 +307,56 @@ def test_full_size_config1_linearity(cuda):
     cols = slice(4096, 4096 + 512)
     ref = oracle.linear(x1, oracle.awq_dequant(qw[:, 512:576], qz[:, 512:576], sc[:, cols]))
     assert_matmul_close(y1[:, cols], ref, "C1 column slice")
+
+
+# ------------------------------------------------- edge cases of the tuned kernels
+@pytest.mark.parametrize("k,n,g", [(192, 264, 32), (384, 40, 64), (128, 1032, 128), (1040, 96, 16)])
+def test_awq_slab_producer_ragged_shapes_bit_exact(cuda, k, n, g):
+    # bf16 output takes the tensor-core path's producer: k not a multiple of its 128-row tile, a word
+    # count that is not a multiple of 4 (no 16-byte loads) or of the 32-word tile
+    qw, qz, sc = synth.awq_layer(k, n, g, seed=k + n)
+    raw = L.QuantWeight.new_awq(4, words(qw), words(qz), dev(sc))
+    ref = oracle.awq_dequant(qw, qz, sc)
+    assert np.array_equal(bits(L.dequantize_awq(raw, torch.bfloat16)), oracle.to_bf16_bits(ref))
+
+
+def test_mxfp4_slab_producer_extreme_scales_bit_exact(cuda):
+    rng = np.random.default_rng(5)
+    sc_list = [0, 1, 2, 3, 4, 5, 127, 249, 250, 251, 252, 253, 254]
+    blocks = rng.integers(0, 256, size=(len(sc_list), 2, 16), dtype=np.uint8)
+    scales = np.repeat(np.array(sc_list, np.uint8)[:, None], 2, axis=1)
+    lin = L.Mxfp4Linear(dev(blocks), dev(scales), None, 64, len(sc_list))
+    ref = oracle.mxfp4_dequant(blocks, scales, len(sc_list), 64)
+    assert np.array_equal(bits(lin.dequantize(torch.bfloat16)), oracle.to_bf16_bits(ref))
+
+
+def test_fp8_slab_producer_nan_bytes(cuda):
+    allb = np.tile(np.arange(256, dtype=np.uint8), 4).reshape(4, 256)
+    scale = np.array([[0.75, 2.0]], np.float32)
+    got = L.Fp8Linear(dev(allb), dev(scale)).dequantize(torch.bfloat16)
+    ref = oracle.fp8_dequant(allb, scale)
+    ok = ~np.isnan(ref)
+    g = got.float().cpu().numpy()
+    assert np.array_equal(np.isnan(g), ~ok)
+    assert np.array_equal(bits(got)[ok], oracle.to_bf16_bits(ref)[ok])
+
+
+@pytest.mark.parametrize("m", [9, 17, 24, 32])
+def test_fp8_gemv_tuned_kernel_many_tokens(cuda, m):
+    n, k = 200, 1024  # a ragged last row tile
+    q, s = synth.fp8_layer(256, k, seed=m)
+    q = np.ascontiguousarray(q[:n])
+    srow = np.ascontiguousarray(np.repeat(s, 128, axis=0)[:n])  # one scale per (row, 128-wide k block)
+    x = synth.activations(m, k, seed=3)
+    bias = synth.bf16_round(np.linspace(-0.5, 0.5, n).astype(np.float32))
+    y = L.Fp8Linear(dev(q), dev(srow), dev(bias, torch.bfloat16)).forward(dev(x, torch.bfloat16))
+    assert_matmul_close(y, oracle.linear(x, oracle.fp8_dequant(q, srow), bias), f"fp8 tuned m={m}")
+
+
+@pytest.mark.parametrize("n,k,m", [(72, 512, 11), (40, 768, 3), (16, 256, 16)])
+def test_q4k_gemv_tuned_kernel_ragged(cuda, n, k, m):
+    data = synth.gguf_layer(F.GGML_Q4_K, n, k, seed=n + m)
+    x = synth.activations(m, k, seed=9)
+    ref = oracle.linear(x, oracle.gguf_dequant(F.GGML_Q4_K, data, n, k))
+    y = L.QLinear(F.GGML_Q4_K, dev(data), n, k).forward(dev(x, torch.bfloat16))
+    assert_matmul_close(y, ref, f"q4k n={n} k={k} m={m}")
