@@ -284,6 +284,10 @@ def _timed_ms(torch, dist, world, fn, iters):
     return ms
 
 
+class _NotSelected(Exception):
+    pass
+
+
 def run_extras(args, world, rank, c1_layer):
     """Configs 0, 2, 3, 4 of BASELINE.json (single-GPU legs on every rank's own GPU; TP/EP legs when world > 1)."""
     import torch
@@ -313,8 +317,12 @@ def run_extras(args, world, rank, c1_layer):
             g.replay()
         return _timed_ms(torch, dist, world, g.replay, reps) * 1e3 / launches
 
+    want = {c.strip() for c in args.configs.split(",")}
+
     # ---- C0: GGUF Q4_K GEMV, N = K = 4096, M = 1 (16 distinct copies: 151 MB > L2)
     try:
+        if "c0" not in want:
+            raise _NotSelected()
         n = k = 4096
         copies = [L.QLinear(F.GGML_Q4_K, dev(synth.gguf_layer(F.GGML_Q4_K, n, k, seed=100 * rank + i)), n, k) for i in range(2)]
         base = copies[0].blocks
@@ -325,11 +333,15 @@ def run_extras(args, world, rank, c1_layer):
         out["c0_q4k_gemv_m1"] = {"us_per_launch": round(us, 2), "gbs": round(b / us / 1e3, 1),
                                   "frac_of_hbm_peak": round(b / us / 1e3 / hbm, 4), "algorithmic_bytes": b}
         del lins, copies
+    except _NotSelected:
+        pass
     except Exception as e:  # keep the headline line alive
         out["c0_q4k_gemv_m1"] = {"error": str(e)[:200]}
 
     # ---- C2: AWQ prefill GEMM M = 2048, K = 4096, N in {4096, 14336}
     try:
+        if "c2" not in want:
+            raise _NotSelected()
         m = 2048
         x = dev(synth.activations(m, K, seed=2), torch.bfloat16)
         res = {}
@@ -356,11 +368,15 @@ def run_extras(args, world, rank, c1_layer):
             tf = 2.0 * m * n * K / ms / 1e9
             res[f"n{n}_tp{world}_allgather"] = {"ms": round(ms, 4), "tflops_whole_job": round(tf, 1)}
         out["c2_awq_gemm_m2048"] = res
+    except _NotSelected:
+        pass
     except Exception as e:
         out["c2_awq_gemm_m2048"] = {"error": str(e)[:200]}
 
     # ---- C3: FP8 E4M3 128x128-block GEMV (M = 1, 32) and GEMM (M = 2048), N = 14336, K = 4096
     try:
+        if "c3" not in want:
+            raise _NotSelected()
         n = 14336
         q, s_ = synth.fp8_layer(n, K, seed=3 + rank)
         base = dev(q)
@@ -380,11 +396,15 @@ def run_extras(args, world, rank, c1_layer):
         res["gemm_m2048"] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_bf16_burst_peak": round(tf / tf_burst, 4)}
         out["c3_fp8_block"] = res
         del lins, base
+    except _NotSelected:
+        pass
     except Exception as e:
         out["c3_fp8_block"] = {"error": str(e)[:200]}
 
     # ---- C4: GPT-OSS-20B-shaped MXFP4 MoE layer, 32 experts, top-4, 4096 tokens
     try:
+        if "c4" not in want:
+            raise _NotSelected()
         e, hidden, inter, tokens = 32, 2880, 2880, 4096
         d = synth.gptoss_moe(4, hidden, inter, tokens, seed=4)  # 4 distinct experts, tiled 8x (throughput is data-independent)
         rep = lambda a: np.concatenate([a] * (e // 4), axis=0)
@@ -412,6 +432,8 @@ def run_extras(args, world, rank, c1_layer):
             res[f"ep{world}_all_to_all"] = {"ms": round(ms, 3), "tflops_whole_job": round(fl / ms / 1e9, 1),
                                             "tokens_per_s_whole_job": round(tokens / ms * 1e3, 0)}
         out["c4_mxfp4_moe"] = res
+    except _NotSelected:
+        pass
     except Exception as e:
         out["c4_mxfp4_moe"] = {"error": str(e)[:200]}
     return out
@@ -485,6 +507,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip configurations 0, 2, 3, 4 (headline C1 line only)")
+    ap.add_argument("--configs", default="c0,c2,c3,c4",
+                    help="which of the other configurations to run, e.g. 'c3' (used to keep profiler captures small)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
