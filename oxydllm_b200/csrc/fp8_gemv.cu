@@ -33,6 +33,7 @@ struct Fp8GemvParams {
     int m, k, n;
     int s_in, block_out, block_in;
     int row_tiles, k_warps; // warps of a CTA = row_tiles x k_warps
+    int token_split;        // neighbouring CTAs that share their rows and take 8*MT tokens each (>= 1)
 };
 
 namespace cg = cooperative_groups;
@@ -62,12 +63,16 @@ __global__ void __launch_bounds__(256, MT == 1 ? 4 : MT == 2 ? 3 : 2) fp8_gemv_k
     const int nrt = p.row_tiles, ks = (int)gridDim.y, rank = (int)blockIdx.y; // cluster = the y extent of the grid
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     const int rt = warp % nrt, kw = warp / nrt;
-    const int n0 = (blockIdx.x * nrt + rt) * 16;
+    // Token tiles of one row group sit in neighbouring CTAs: they stream the same weights at the same
+    // time, so all but the first reader hit in L2.
+    const int zt = blockIdx.x % p.token_split, bx = blockIdx.x / p.token_split;
+    const int m0 = zt * 8 * MT, m_loc = min(8 * MT, p.m - m0); // this CTA's tokens [m0, m0 + m_loc)
+    const int n0 = (bx * nrt + rt) * 16;
     const int kl = p.k / ks, k_cta = rank * kl; // this CTA's k slice
     const int wl = kl / p.k_warps, k_off = kw * wl, k_beg = k_cta + k_off; // this warp's part of it
     const int xrow = kl + 8; // halves; 16 bytes of padding: the 16-byte reads of a quarter warp hit distinct banks
     __half *xs = reinterpret_cast<__half *>(smem);
-    float *red = reinterpret_cast<float *>(smem + (size_t)p.m * xrow * 2); // [warp][MT*4][lane]
+    float *red = reinterpret_cast<float *>(smem + (size_t)m_loc * xrow * 2); // [warp][MT*4][lane]
 
     float *zeros = red + blockDim.x * MT * 4; // 32 bytes of zeros: what lanes without a token read as x
 
@@ -92,8 +97,8 @@ __global__ void __launch_bounds__(256, MT == 1 ? 4 : MT == 2 ? 3 : 2) fp8_gemv_k
     }
 
     if (tid < 8) zeros[tid] = 0.0f;
-    for (int row = 0; row < p.m; row++) {
-        const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)row * p.k + k_cta);
+    for (int row = 0; row < m_loc; row++) {
+        const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)(m0 + row) * p.k + k_cta);
         uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
         for (int q4 = tid; q4 < (kl >> 2); q4 += blockDim.x) {
             const uint2 raw = __ldg(src + q4);
@@ -108,7 +113,7 @@ __global__ void __launch_bounds__(256, MT == 1 ? 4 : MT == 2 ? 3 : 2) fp8_gemv_k
     int xstep[MT];
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
-        const bool real = 8 * mt + g < p.m;
+        const bool real = 8 * mt + g < m_loc;
         xp[mt] = real ? reinterpret_cast<const uint4 *>(xs + (size_t)(8 * mt + g) * xrow + k_off + 16 * c)
                       : reinterpret_cast<const uint4 *>(zeros);
         xstep[mt] = real ? 8 : 0; // 64 halves per chunk
@@ -202,15 +207,15 @@ __global__ void __launch_bounds__(256, MT == 1 ? 4 : MT == 2 ? 3 : 2) fp8_gemv_k
     const int slots = nrt * MT * 4 * 32;
     for (int o = rank * blockDim.x + tid; o < slots; o += ks * blockDim.x) {
         const int ln = o & 31, e = (o >> 5) & 3, mt = (o >> 7) % MT, wt = (o >> 7) / MT;
-        const int nn = (blockIdx.x * nrt + wt) * 16 + (ln >> 2) + 8 * (e >> 1), row = 8 * mt + 2 * (ln & 3) + (e & 1);
-        if (nn < p.n && row < p.m) {
+        const int nn = (bx * nrt + wt) * 16 + (ln >> 2) + 8 * (e >> 1), row = 8 * mt + 2 * (ln & 3) + (e & 1);
+        if (nn < p.n && row < m_loc) {
             float sum = 0.0f;
             for (int q = 0; q < ks; q++) {
                 const float *src = ks > 1 ? cluster.map_shared_rank(red, q) : red;
                 for (int w = 0; w < p.k_warps; w++) sum += src[((w * nrt + wt) * MT * 4 + mt * 4 + e) * 32 + ln];
             }
             if (p.bias) sum += load_as_f32(p.bias, p.bias_dtype, nn);
-            store_as(p.y, p.y_dtype, (size_t)row * p.n + nn, sum);
+            store_as(p.y, p.y_dtype, (size_t)(m0 + row) * p.n + nn, sum);
         }
     }
     if (ks > 1) cluster.sync(); // nobody leaves while a peer may still read its shared memory
@@ -219,7 +224,8 @@ __global__ void __launch_bounds__(256, MT == 1 ? 4 : MT == 2 ? 3 : 2) fp8_gemv_k
 template <int MT, int D> static int launch_fp8(const Fp8GemvParams &p, int ks, cudaStream_t st)
 {
     const int nw = p.row_tiles * p.k_warps;
-    const size_t smem = (size_t)p.m * (p.k / ks + 8) * 2 + (size_t)nw * MT * 4 * 32 * 4 + 32;
+    const int m_cta = p.m < 8 * MT ? p.m : 8 * MT;
+    const size_t smem = (size_t)m_cta * (p.k / ks + 8) * 2 + (size_t)nw * MT * 4 * 32 * 4 + 32;
     auto kern = fp8_gemv_kernel<MT, D>;
     static size_t configured[64] = {};
     int device = 0;
@@ -229,7 +235,7 @@ template <int MT, int D> static int launch_fp8(const Fp8GemvParams &p, int ks, c
         if (device < 64) configured[device] = smem;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ceil_div(p.n, 16 * p.row_tiles), ks, 1);
+    cfg.gridDim = dim3(ceil_div(p.n, 16 * p.row_tiles) * p.token_split, ks, 1);
     cfg.blockDim = dim3(nw * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -261,20 +267,25 @@ int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale_inv, int s
     // Warps of a CTA = row tiles x k parts, cluster = further k slices (measured on a 14336 x 4096 layer).
     // Few tokens: small row groups, so that every CTA of the grid is resident at once. More tokens:
     // more row tiles per CTA, which share the staged x.
-    int nrt = 2, kw = 4, ks = 1, d = 2;
+    // mtc = 8-token tiles per CTA; more tokens than 8 * mtc go to neighbouring CTAs of the same rows.
+    // Measured: 9..16 tokens run faster as two 8-token CTAs side by side than as one 16-token CTA.
+    int nrt = 2, kw = 4, ks = 1, d = 2, mtc = m <= 16 ? 1 : 4;
     if (m > 16) { nrt = 8; kw = 1; ks = 4; }
     else if (m > 8) { nrt = 8; kw = 1; ks = 2; }
     else if (m > 2) { nrt = 4; kw = 2; ks = 2; }
-    if (const char *env = getenv("OXQ_FP8_GEMV_TUNE")) { // bench-harness knob: "row_tiles,k_warps,cluster,depth"
-        int a = 0, b = 0, cc = 0, dd = 0;
-        if (sscanf(env, "%d,%d,%d,%d", &a, &b, &cc, &dd) == 4 && a >= 1 && b >= 1 && a * b <= 8 && cc >= 1 && cc <= 8 &&
-            (cc & (cc - 1)) == 0 && (dd == 1 || dd == 2 || dd == 4) && k % (b * cc * 64 * dd) == 0) {
+    if (const char *env = getenv("OXQ_FP8_GEMV_TUNE")) { // bench-harness knob: "row_tiles,k_warps,cluster,depth[,token tiles per CTA]"
+        int a = 0, b = 0, cc = 0, dd = 0, mm = 0;
+        const int got = sscanf(env, "%d,%d,%d,%d,%d", &a, &b, &cc, &dd, &mm);
+        if (got >= 4 && a >= 1 && b >= 1 && a * b <= 8 && cc >= 1 && cc <= 8 && (cc & (cc - 1)) == 0 &&
+            (dd == 1 || dd == 2 || dd == 4) && k % (b * cc * 64 * dd) == 0) {
             nrt = a; kw = b; ks = cc; d = dd;
+            if (got >= 5 && (mm == 1 || mm == 2 || mm == 4)) mtc = mm;
         }
     }
     p.row_tiles = nrt; p.k_warps = kw;
-    if (m <= 8) return d == 1 ? launch_fp8<1, 1>(p, ks, st) : d == 2 ? launch_fp8<1, 2>(p, ks, st) : launch_fp8<1, 4>(p, ks, st);
-    if (m <= 16) return d == 1 ? launch_fp8<2, 1>(p, ks, st) : launch_fp8<2, 2>(p, ks, st);
+    p.token_split = ceil_div(m, 8 * mtc);
+    if (mtc == 1) return d == 1 ? launch_fp8<1, 1>(p, ks, st) : d == 2 ? launch_fp8<1, 2>(p, ks, st) : launch_fp8<1, 4>(p, ks, st);
+    if (mtc == 2) return d == 1 ? launch_fp8<2, 1>(p, ks, st) : launch_fp8<2, 2>(p, ks, st);
     return launch_fp8<4, 2>(p, ks, st);
 }
 
