@@ -421,6 +421,13 @@ def run_extras(args, world, rank, c1_layer):
         res = {"ms": round(ms, 3), "tflops": round(fl / ms / 1e9, 1), "tokens_per_s": round(tokens / ms * 1e3, 0),
                "frac_of_bf16_burst_peak": round(fl / ms / 1e9 / tf_burst, 4),
                "note": "4 distinct experts tiled to 32; router logits N(0,1) given, router GEMM not timed"}
+        # decode-sized batches: only the selected experts' packed weights are streamed (batched GEMVs)
+        per_pair_bytes = (2 * inter * hidden + hidden * inter) // 2 + (2 * inter * hidden + hidden * inter) // 32
+        for t_dec in (1, 8):
+            xd, ld = x[:t_dec].contiguous(), lg[:t_dec].contiguous()
+            us = graph_us(lambda: layer.forward_with_logits(xd, ld), 1)
+            res[f"decode_tokens{t_dec}"] = {"us": round(us, 2), "gbs_upper_bound_distinct_experts": round(
+                t_dec * 4 * per_pair_bytes / us / 1e3, 1), "note": "bytes counted as if every (token, slot) pair hit a distinct expert"}
         if world > 1:  # expert parallel: tokens data-parallel, all-to-all dispatch and combine
             t_local = tokens // world
             sl = slice(rank * t_local, (rank + 1) * t_local)

@@ -395,6 +395,62 @@ mxfp4_slab16_bf16_kernel(const uint8_t *__restrict__ blocks, const uint8_t *__re
     }
 }
 
+// Q4_K: a thread converts one 32-byte nibble group of a super-block: sub-block 2*iq from the low
+// nibbles and 2*iq+1 from the high ones, 64 weights = 128 contiguous output bytes. The arithmetic
+// is the element-wise kernel's, operation for operation: (d*sc)*q - (dmin*mn), three roundings.
+__global__ void __launch_bounds__(256)
+q4k_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restrict__ out, size_t total_groups)
+{
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_groups;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t sb = idx >> 2;
+        const int iq = (int)(idx & 3);
+        const uint8_t *blk = blocks + sb * 144;
+        const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+        const uint4 qa = __ldcs(reinterpret_cast<const uint4 *>(blk + 16 + 32 * iq));
+        const uint4 qb = __ldcs(reinterpret_cast<const uint4 *>(blk + 32 + 32 * iq));
+        const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+        const uint32_t sw[3] = {hdr.y, hdr.z, hdr.w}; // the 12 scale bytes
+        auto byte_at = [&](int j) -> uint32_t { return (sw[j >> 2] >> (8 * (j & 3))) & 0xFFu; };
+        float sc_v[2], m_v[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int j = 2 * iq + h;
+            uint32_t sc, mn;
+            if (j < 4) {
+                sc = byte_at(j) & 63u;
+                mn = byte_at(j + 4) & 63u;
+            } else {
+                sc = (byte_at(j + 4) & 0x0Fu) | ((byte_at(j - 4) >> 6) << 4);
+                mn = (byte_at(j + 4) >> 4) | ((byte_at(j) >> 6) << 4);
+            }
+            sc_v[h] = __fmul_rn(d, (float)sc);
+            m_v[h] = __fmul_rn(dmin, (float)mn);
+        }
+        const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w}; // byte t = element t of both sub-blocks
+        uint4 *dst = reinterpret_cast<uint4 *>(out + sb * 256 + 64 * iq);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            uint32_t o[16];
+#pragma unroll
+            for (int wd = 0; wd < 8; wd++) {
+                const uint32_t v = h ? (q[wd] >> 4) : q[wd];
+                float f[4];
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    const float nib = __uint_as_float(0x4B000000u | ((v >> (8 * b)) & 0x0Fu)) - 8388608.0f;
+                    f[b] = __fsub_rn(__fmul_rn(sc_v[h], nib), m_v[h]);
+                }
+                o[2 * wd] = pack_bf16x2_rn(f[0], f[1]);
+                o[2 * wd + 1] = pack_bf16x2_rn(f[2], f[3]);
+            }
+#pragma unroll
+            for (int t = 0; t < 4; t++) dst[4 * h + t] = make_uint4(o[4 * t], o[4 * t + 1], o[4 * t + 2], o[4 * t + 3]);
+        }
+    }
+}
+
 static int grid_for(size_t work_items, int block = 256)
 {
     size_t blocks = (work_items + block - 1) / block;
@@ -439,6 +495,12 @@ int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *
     gguf_block_layout(ggml_type, bel, bby);
     const uint8_t *b = blocks + (size_t)n_off * (k / bel) * bby;
     const size_t total = (size_t)n_cnt * k;
+    if (ggml_type == OXQ_GGML_Q4_K && aligned(b, 16) && aligned(out, 16)) {
+        const size_t groups = total / 64;
+        q4k_slab_bf16_kernel<<<grid_for(groups), 256, 0, st>>>(b, out, groups);
+        OXQ_LAUNCH_CHECK("q4k_slab_bf16_kernel");
+        return OXQ_OK;
+    }
     const int grid = grid_for(total);
     switch (ggml_type) {
     case OXQ_GGML_Q4_0: gguf_dequant_kernel<OXQ_GGML_Q4_0, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
@@ -552,6 +614,8 @@ OXQ_EXPORT int oxq_gguf_dequant(int ggml_type, const void *blocks, void *w_out, 
     const size_t total = (size_t)n * k;
     const uint8_t *b = (const uint8_t *)blocks;
     cudaStream_t st = (cudaStream_t)stream;
+    if (out_dtype == OXQ_BF16) // same bits; Q4_K takes the fast producer of the tensor-core path
+        return gguf_dequant_rows_bf16(ggml_type, b, (__nv_bfloat16 *)w_out, k, 0, n, st);
     const int grid = grid_for(total);
     switch (ggml_type) {
     case OXQ_GGML_Q4_0:

@@ -14,8 +14,16 @@ int gemm_grouped(const void *a, int a_rows, const void *w, int slab_experts, int
                  const int4 *entries, const int *grp_beg, int group, const void *bias, int bias_dtype, void *out,
                  int ldo, int epi, float limit, int *flag, cudaStream_t stream);
 
+bool mxfp4_gemv_batched_supported(int k, const void *blocks);
+int mxfp4_gemv_batched(const void *x, int x_div, const uint8_t *blocks, const uint8_t *scales, const void *bias,
+                       int bias_dtype, const int *pair_expert, int pairs, int e_lo, int e_hi, void *y, int y_dtype, int k,
+                       int n, cudaStream_t st);
+
 constexpr int MOE_MAX_EXPERTS = 256;
 constexpr int MOE_MAX_TOPK = 8;
+// Up to this many (token, slot) pairs the layer runs as batched single-token GEMVs on the packed
+// weights of the selected experts only (decode); above, it dequantizes expert groups for the grouped GEMM.
+constexpr int MOE_DECODE_MAX_PAIRS = 64;
 
 // One warp per token: f32 softmax over all experts, k rounds of arg-max (ties: lower index),
 // optional renormalisation by the sum of the selected probabilities (moe.rs:472-487).
@@ -201,12 +209,35 @@ moe_combine_kernel(const __nv_bfloat16 *__restrict__ yp, const int *__restrict__
     }
 }
 
+// Decode path: h[pair, j] = clamped SwiGLU of the interleaved (gate, up) columns 2j, 2j+1 of gu[pair, :]
+// (moe.rs:152-173; the same arithmetic as the grouped GEMM's epilogue), and inv[pair] = pair.
+__global__ void __launch_bounds__(256)
+moe_swiglu_kernel(const float *__restrict__ gu, int pairs, int inter, float limit, __nv_bfloat16 *__restrict__ h,
+                  int *__restrict__ inv)
+{
+    const size_t total = (size_t)pairs * inter;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const float2 v = reinterpret_cast<const float2 *>(gu)[idx];
+        const float gate = fminf(v.x, limit), up = fminf(fmaxf(v.y, -limit), limit);
+        const float sig = __fdividef(1.0f, __expf(-1.702f * gate) + 1.0f);
+        h[idx] = __float2bfloat16_rn((up + 1.0f) * (gate * sig));
+        if (idx < (size_t)pairs) inv[idx] = (int)idx;
+    }
+}
+
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct MoeLayout {
     size_t top_idx, top_w, counts, offsets, grp_beg, entries, perm, inv, xs, h, slab, total;
     int group_experts, n_groups, max_mt;
+    bool decode; // few pairs: no dequantized slab, the slab region holds the f32 gate_up outputs
 };
+
+static bool moe_decode_shape(size_t pairs, int hidden, int inter)
+{
+    return pairs <= (size_t)MOE_DECODE_MAX_PAIRS && hidden % 32 == 0 && inter % 32 == 0 &&
+           mxfp4_gemv_batched_supported(hidden, nullptr) && mxfp4_gemv_batched_supported(inter, nullptr);
+}
 
 static MoeLayout moe_layout(int tokens, int top_k, int n_exp, int hidden, int inter)
 {
@@ -233,7 +264,8 @@ static MoeLayout moe_layout(int tokens, int top_k, int n_exp, int hidden, int in
     L.inv = off; off = align_up(off + pairs * 4, 256);
     L.xs = off; off = align_up(off + (pairs + 128) * hidden * 2, 256); // also the down-projection output
     L.h = off; off = align_up(off + (pairs + 128) * inter * 2, 256);
-    L.slab = off; off = align_up(off + (size_t)ge * per_expert, 256);
+    L.decode = moe_decode_shape(pairs, hidden, inter);
+    L.slab = off; off = align_up(off + (L.decode ? pairs * 2 * inter * sizeof(float) : (size_t)ge * per_expert), 256);
     L.total = off;
     return L;
 }
@@ -292,6 +324,26 @@ OXQ_EXPORT int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *r
     OXQ_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), st));
     moe_route_kernel<<<ceil_div(tokens * 32, 256), 256, 0, st>>>(router_logits, tokens, num_experts, top_k, norm_topk,
                                                                  top_idx, top_w);
+    if (L.decode) {
+        OXQ_REQUIRE(aligned(gu_blocks, 16) && aligned(dn_blocks, 16), OXQ_ERR_BAD_ALIGN,
+                    "oxq_gptoss_moe_forward: expert blocks must be 16-byte aligned");
+        // Decode: only the selected experts' packed weights are read. gate_up (f32 out, bias folded) ->
+        // SwiGLU -> down (into the xs buffer, bf16) -> combine with inv = identity.
+        OXQ_LAUNCH_CHECK("moe_route_kernel");
+        float *gu = reinterpret_cast<float *>(slab);
+        int rc = mxfp4_gemv_batched(x, top_k, gu_blocks, gu_scales, gu_bias, bias_dtype, top_idx, pairs, expert_lo, expert_hi,
+                                    gu, OXQ_F32, hidden, 2 * inter, st);
+        if (rc) return rc;
+        moe_swiglu_kernel<<<ceil_div(pairs * inter, 256), 256, 0, st>>>(gu, pairs, inter, limit, h, inv);
+        OXQ_LAUNCH_CHECK("moe_swiglu_kernel");
+        rc = mxfp4_gemv_batched(h, 1, dn_blocks, dn_scales, dn_bias, bias_dtype, top_idx, pairs, expert_lo, expert_hi, xs,
+                                OXQ_BF16, inter, hidden, st);
+        if (rc) return rc;
+        moe_combine_kernel<<<ceil_div(tokens * (hidden / 8), 256), 256, 0, st>>>(xs, top_idx, top_w, inv, tokens, top_k,
+                                                                                 hidden, expert_lo, expert_hi, out, out_dtype);
+        OXQ_LAUNCH_CHECK("moe_combine_kernel");
+        return OXQ_OK;
+    }
     moe_count_kernel<<<n_exp, 256, 0, st>>>(top_idx, pairs, expert_lo, counts);
     moe_plan_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, L.group_experts, offsets, entries, grp_beg);
     moe_scatter_kernel<<<n_exp, 1024, 0, st>>>(top_idx, pairs, expert_lo, offsets, perm, inv);

@@ -111,6 +111,10 @@ bool fp8_gemv_fast_supported(int m, int k, int block_in, const void *w);
 int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale_inv, int s_in, int block_out, int block_in,
                   const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, cudaStream_t st);
 
+bool mxfp4_gemv_fast_supported(int m, int k, const void *blocks, const void *scales);
+int mxfp4_gemv_fast(const void *x, const uint8_t *blocks, const uint8_t *scales, const void *bias, int bias_dtype, void *y,
+                    int y_dtype, int m, int k, int n, cudaStream_t st);
+
 constexpr int ROW_NW = 4;
 
 template <int FMT, int MT>
@@ -268,5 +272,10 @@ OXQ_EXPORT int oxq_mxfp4_gemv(const void *x, int x_dtype, const uint8_t *blocks,
     p.x = (const __nv_bfloat16 *)x; p.data = blocks; p.aux = scales; p.bias = bias; p.y = y;
     p.bias_dtype = bias_dtype; p.y_dtype = y_dtype; p.m = m; p.k = k; p.n = n;
     p.row_bytes = (size_t)k / 2;
+    if (mxfp4_gemv_fast_supported(m, k, blocks, scales)) {
+        const char *env = getenv("OXQ_MXFP4_FAST"); // bench-harness knob: "0" selects the generic kernel
+        if (!(env && env[0] == '0'))
+            return mxfp4_gemv_fast(x, blocks, scales, bias, bias_dtype, y, y_dtype, m, k, n, (cudaStream_t)stream);
+    }
     return launch_rowfmt<RF_MXFP4>(p, (cudaStream_t)stream);
 }

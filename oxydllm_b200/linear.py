@@ -36,7 +36,8 @@ def _p(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # raw handle of torch's current stream on the current device, without building a Stream object
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 def _require_cuda(*tensors):
@@ -59,6 +60,8 @@ def _as_u32_words(t: torch.Tensor) -> torch.Tensor:
 def _flatten_x(x: torch.Tensor, in_features: int, who: str):
     if x.shape[-1] != in_features:
         raise ValueError(f"{who}: input last dim {x.shape[-1]} != in_features {in_features}")
+    if x.dim() == 2 and x.is_contiguous():  # the common case: nothing to reshape
+        return x, x.shape[:1], x.shape[0]
     lead = x.shape[:-1]
     m = 1
     for d in lead:
@@ -215,10 +218,16 @@ class PackedQuantLinear:
         self.scales = raw.scales.contiguous()
         self.bias = None if bias is None else bias.contiguous()
         self.dtype = dtype
+        self._resident = all(t is None or t.is_cuda for t in (self.qweight, self.qzeros, self.scales, self.bias))
+        # constant arguments of the GEMV call, converted once
+        b = self.bias
+        self._const = (_p(self.qweight), _p(self.qzeros), _p(self.scales), _dt(self.scales.dtype), _p(b),
+                       _dt(b.dtype) if b is not None else 0)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x2, lead, m = _flatten_x(x, self.in_features, "PackedQuantLinear")
-        _require_cuda(x2, self.qweight, self.qzeros, self.scales, self.bias)
+        if not (self._resident and x2.is_cuda):
+            _require_cuda(x2, self.qweight, self.qzeros, self.scales, self.bias)
         y = torch.empty((m, self.out_features), dtype=x2.dtype, device=x2.device)
         if m == 0:
             return y.reshape(*lead, self.out_features)
@@ -230,9 +239,8 @@ class PackedQuantLinear:
         return y.reshape(*lead, self.out_features)
 
     def _gemv(self, x2, y, m):
-        b = self.bias
-        _lib.call("oxq_awq_gemv", _p(x2), _dt(x2.dtype), _p(self.qweight), _p(self.qzeros), _p(self.scales),
-                  _dt(self.scales.dtype), _p(b), _dt(b.dtype) if b is not None else 0, _p(y), _dt(y.dtype), m,
+        qw, qz, sc, sc_dt, b, b_dt = self._const
+        _lib.call("oxq_awq_gemv", _p(x2), _dt(x2.dtype), qw, qz, sc, sc_dt, b, b_dt, _p(y), _dt(y.dtype), m,
                   self.in_features, self.out_features, self.group_size, _stream())
 
 

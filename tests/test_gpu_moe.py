@@ -87,3 +87,23 @@ def test_moe_gpt_oss_shape_slice(cuda):
                             d["dn_bias"], 2880, 2880, 7.0)
     got = y.float().cpu().numpy()
     assert (np.abs(got - ref) <= 2e-2 * np.abs(ref).max(axis=1, keepdims=True) + 1e-5).all()
+
+
+@pytest.mark.parametrize("tokens", [1, 4, 16])
+def test_moe_decode_path_gpt_oss_shape(cuda, tokens):
+    """Few (token, slot) pairs: batched single-token GEMVs on the selected experts' packed weights (no dequantized slab)."""
+    d = synth.gptoss_moe(8, 2880, 2880, tokens, seed=20 + tokens)
+    layer = build(d)
+    x, lg = dev(d["x"], torch.bfloat16), dev(d["logits"])
+    y = layer.forward_with_logits(x, lg)
+    idx, w = oracle.moe_route(d["logits"], 4, True)
+    args = (d["gu_blocks"], d["gu_scales"], d["gu_bias"], d["dn_blocks"], d["dn_scales"], d["dn_bias"], 2880, 2880, 7.0)
+    ref = oracle.gptoss_moe(d["x"], idx, w, *args)
+    got = y.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert (np.abs(got - ref) <= 2e-2 * np.abs(ref).max(axis=1, keepdims=True) + 1e-5).all(), np.abs(got - ref).max()
+    assert torch.equal(y, layer.forward_with_logits(x, lg))  # run-to-run identical
+    # a rank's expert range: the other experts' pairs contribute nothing
+    got_hi = layer.forward_with_logits(x, lg, (4, 8)).float().cpu().numpy()
+    ref_hi = oracle.gptoss_moe(d["x"], idx, w, *args, expert_range=(4, 8))
+    assert (np.abs(got_hi - ref_hi) <= 2e-2 * np.abs(ref).max(axis=1, keepdims=True) + 1e-5).all()
