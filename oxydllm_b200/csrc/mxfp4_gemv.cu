@@ -264,7 +264,7 @@ int mxfp4_gemv_fast(const void *x, const uint8_t *blocks, const uint8_t *scales,
     p.row_tiles = nrt; p.k_warps = kw;
     p.token_split = ceil_div(m, 8); // 8 tokens per CTA; more on neighbouring CTAs
     p.pair_expert = nullptr; p.x_div = 1; p.e_lo = p.e_hi = 0;
-    return launch_mx4<1, 2>(p, ks, st);
+    return launch_mx4<1, 4>(p, ks, st);
 }
 
 // One single-token GEMV per (token, slot) pair against the pair's expert, all pairs in one launch:
@@ -289,7 +289,7 @@ int mxfp4_gemv_batched(const void *x, int x_div, const uint8_t *blocks, const ui
     mx4_pick(1, k, nrt, kw, ks);
     p.row_tiles = nrt; p.k_warps = kw; p.token_split = 1;
     p.pair_expert = pair_expert; p.x_div = x_div; p.e_lo = e_lo; p.e_hi = e_hi;
-    return launch_mx4<1, 2>(p, ks, st, pairs);
+    return launch_mx4<1, 4>(p, ks, st, pairs);
 }
 
 } // namespace oxq

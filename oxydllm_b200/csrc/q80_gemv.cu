@@ -202,7 +202,7 @@ static int launch_q80(const Q80GemvParams &p, int ks, cudaStream_t st)
 {
     const int nw = p.row_tiles * p.k_warps;
     const size_t smem = q80_smem(p.m < 8 ? p.m : 8, p.k / ks, nw);
-    auto kern = q80_gemv_kernel<2>;
+    auto kern = q80_gemv_kernel<4>;
     static size_t configured[64] = {};
     int device = 0;
     OXQ_CUDA(cudaGetDevice(&device));
@@ -230,7 +230,7 @@ static int launch_q80(const Q80GemvParams &p, int ks, cudaStream_t st)
 static bool q80_pick(int m, int k, int &nrt, int &kw, int &ks)
 {
     const int nb = k / 32;
-    static const int few[][3] = {{2, 4, 1}, {1, 8, 1}, {1, 6, 1}, {1, 5, 1}, {2, 3, 1}, {2, 2, 1}, {1, 7, 1}, {2, 1, 1}, {1, 1, 1}};
+    static const int few[][3] = {{1, 8, 1}, {2, 4, 1}, {1, 6, 1}, {1, 5, 1}, {2, 3, 1}, {2, 2, 1}, {1, 7, 1}, {2, 1, 1}, {1, 1, 1}};
     static const int many[][3] = {{8, 1, 2}, {4, 2, 2}, {4, 2, 1}, {2, 3, 1}, {8, 1, 1}};
     const int(*cand)[3] = m <= 8 ? few : many;
     const int count = m <= 8 ? 9 : 5;

@@ -111,6 +111,12 @@ bool fp8_gemv_fast_supported(int m, int k, int block_in, const void *w);
 int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale_inv, int s_in, int block_out, int block_in,
                   const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, cudaStream_t st);
 
+bool q40_gemv_supported(int m, int k, const void *blocks);
+int q40_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+             cudaStream_t st);
+bool q6k_gemv_supported(int m, int k, const void *blocks);
+int q6k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+             cudaStream_t st);
 bool q80_gemv_supported(int m, int k, const void *blocks);
 int q80_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
              cudaStream_t st);
@@ -222,6 +228,14 @@ OXQ_EXPORT int oxq_gguf_gemv(int ggml_type, const void *x, int x_dtype, const vo
     if (ggml_type == OXQ_GGML_Q4_K && q4k_gemv_supported(m, k)) {
         const char *env = getenv("OXQ_Q4K_FAST"); // bench-harness knob: "0" selects the generic kernel
         if (!(env && env[0] == '0')) return q4k_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
+    }
+    if (ggml_type == OXQ_GGML_Q4_0 && q40_gemv_supported(m, k, blocks)) {
+        const char *env = getenv("OXQ_Q40_FAST"); // bench-harness knob: "0" selects the generic kernel
+        if (!(env && env[0] == '0')) return q40_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
+    }
+    if (ggml_type == OXQ_GGML_Q6_K && q6k_gemv_supported(m, k, blocks)) {
+        const char *env = getenv("OXQ_Q6K_FAST"); // bench-harness knob: "0" selects the generic kernel
+        if (!(env && env[0] == '0')) return q6k_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
     }
     if (ggml_type == OXQ_GGML_Q8_0 && q80_gemv_supported(m, k, blocks)) {
         const char *env = getenv("OXQ_Q80_FAST"); // bench-harness knob: "0" selects the generic kernel

@@ -224,11 +224,19 @@ class PackedQuantLinear:
         self._const = (_p(self.qweight), _p(self.qzeros), _p(self.scales), _dt(self.scales.dtype), _p(b),
                        _dt(b.dtype) if b is not None else 0)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``out``: optional preallocated contiguous ``[m, out_features]`` result tensor of x's dtype and device."""
         x2, lead, m = _flatten_x(x, self.in_features, "PackedQuantLinear")
         if not (self._resident and x2.is_cuda):
             _require_cuda(x2, self.qweight, self.qzeros, self.scales, self.bias)
-        y = torch.empty((m, self.out_features), dtype=x2.dtype, device=x2.device)
+        if out is None:
+            y = torch.empty((m, self.out_features), dtype=x2.dtype, device=x2.device)
+        else:
+            if (out.shape != (m, self.out_features) or out.dtype != x2.dtype or out.device != x2.device
+                    or not out.is_contiguous()):
+                raise ValueError(f"PackedQuantLinear: out must be a contiguous [{m}, {self.out_features}] {x2.dtype} tensor "
+                                 f"on {x2.device}")
+            y = out
         if m == 0:
             return y.reshape(*lead, self.out_features)
         if m <= GEMV_MAX_M:

@@ -99,7 +99,9 @@ class ColumnParallelLinear:
 
     ``local`` is any callable ``x[m, k] -> y[m, b - a]`` (an operator of :mod:`linear` built on the
     sliced tensors). ``chunks`` > 1 cuts the batch into row chunks and overlaps the all-gather of one
-    chunk with the matmul of the next.
+    chunk with the matmul of the next; it pays when ``local`` costs the same per row whatever the batch
+    (a dense or GEMV-sized operator), not for the dequantize-then-GEMM operators, which would
+    dequantize the shard once per chunk.
     """
 
     def __init__(self, local: Callable[[torch.Tensor], torch.Tensor], out_features: int, group=None, chunks: int = 1,
@@ -128,10 +130,14 @@ class ColumnParallelLinear:
             flat = y.new_empty((self.world * (r1 - r0), self.width))  # rank-major concatenation
             work = dist.all_gather_into_tensor(flat, y.contiguous(), group=self.group, async_op=True)
             pending.append((work, flat.view(self.world, r1 - r0, self.width), r0, r1))
+        even = all(b - a == self.width for a, b in self.bounds)
         for work, gathered, r0, r1 in pending:
             work.wait()
-            for r, (a, b) in enumerate(self.bounds):
-                out[r0:r1, a:b] = gathered[r, :, :b - a]
+            if even:  # one strided copy: [world, rows, width] -> [rows, world * width]
+                out[r0:r1].view(r1 - r0, self.world, self.width).copy_(gathered.permute(1, 0, 2))
+            else:
+                for r, (a, b) in enumerate(self.bounds):
+                    out[r0:r1, a:b] = gathered[r, :, :b - a]
         return out
 
 
