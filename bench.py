@@ -369,6 +369,19 @@ def run_extras(args, world, rank, c1_layer):
             ms = _timed_ms(torch, dist, world, lambda: gemm.awq_matmul(lin, x, y), 10)
             tf = 2.0 * m * n * K / ms / 1e9
             res[f"n{n}"] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_bf16_burst_peak": round(tf / tf_burst, 4)}
+        # gated FFN projection on the fused [gate | up] weight (intermediate 14336): activation in the GEMM epilogue
+        inter = 14336
+        from oxydllm_b200 import formats as F2
+        fused = F2.concat_awq_along_out([(c1_layer.qweight.cpu().numpy().view(np.uint32), c1_layer.qzeros.cpu().numpy().view(np.uint32),
+                                          c1_layer.scales.cpu().numpy())] * 2)
+        glin = L.PackedQuantLinear(L.QuantWeight.new_awq(4, dev(fused[0].view(np.int32)), dev(fused[1].view(np.int32)), dev(fused[2])))
+        ffn = L.GatedFfnProjection(glin, "silu")
+        for _ in range(3):
+            ffn.forward(x)
+        ms = _timed_ms(torch, dist, world, lambda: ffn.forward(x), 10)
+        tf = 2.0 * m * 2 * inter * K / ms / 1e9
+        res["ffn_gate_up_silu_i14336"] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_bf16_burst_peak": round(tf / tf_burst, 4)}
+        del glin, ffn, fused
         gemm.check(gemm.workspace(1, 8, "cuda"))
         if world > 1:  # tensor-parallel column split of N = 14336 + all-gather
             n = 14336

@@ -63,6 +63,17 @@ int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight, const uint
                  int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
                  int group_size, void *stream);
 
+/* Gated FFN projection on a fused AWQ [gate | up] weight (concat_awq_along_out of gate_proj and
+ * up_proj, ffn.rs:235-254): y[m, inter] = act(x . W_gate^T) * (x . W_up^T), act = 1 SiLU, 2 GeLU-tanh
+ * (FeedForward::forward, ffn.rs:385-470; gated_silu_fused / gated_gelu_tanh_fused, metal_ops.rs:1243-1277).
+ * x, y bf16. qweight u32 [k, 2*inter/8], qzeros u32 [k/g, 2*inter/8], scales [k/g, 2*inter].
+ * m <= 32 runs the GEMV and a small activation kernel; larger m dequantizes the weight with gate row j
+ * and up row j side by side and applies the activation in the tensor-core GEMM's epilogue (no
+ * [m, 2*inter] round trip). Workspace as for oxq_awq_gemm with n = 2*inter; oxq_gemm_check applies. */
+int oxq_awq_ffn_gate_up(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
+                        int scales_dtype, int activation, void *y, int m, int k, int inter, int group_size,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------------------------ GPTQ
  * qweight u32 [k/pf, n] sequential LSB-first along k, qzeros u32 [k/g, n/pf]
  * storing zero-1 (NULL or sym != 0: zero = 2^(bits-1) - 1), pf = 32/bits. */

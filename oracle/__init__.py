@@ -219,6 +219,23 @@ def linear(x, w, bias=None) -> np.ndarray:
     return y
 
 
+def gated_ffn(x, w_gate_up, activation: str = "silu") -> np.ndarray:
+    """``act(gate) * up`` of the fused gate+up projection (ffn.rs:385-470, the non-Metal branch):
+    ``out = x @ w_gate_up.T`` in f32, ``gate = out[:, :I]``, ``up = out[:, I:]``, ``act`` = SiLU
+    ``g / (1 + exp(-g))`` or tanh-GeLU ``0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))``, all in f32
+    (the reference rounds ``out`` to the activation dtype first; parity is checked with a tolerance)."""
+    out = linear(x, w_gate_up).astype(np.float64)
+    inter = out.shape[1] // 2
+    g, u = out[:, :inter], out[:, inter:]
+    if activation == "silu":
+        a = g / (1.0 + np.exp(-g))
+    elif activation == "gelu_tanh":
+        a = 0.5 * g * (1.0 + np.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    else:
+        raise ValueError(f"unknown activation {activation!r}")
+    return (a * u).astype(np.float32)
+
+
 # ----------------------------------------------------------------------- MoE
 def moe_route(logits, top_k: int, norm_topk: bool = True):
     """softmax -> top-k -> renormalise (moe.rs:472-487)."""

@@ -21,6 +21,7 @@ SIGNATURES = {
     "oxq_version": [],
     "oxq_awq_dequant": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "oxq_awq_gemv": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
+    "oxq_awq_ffn_gate_up": [_vp, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp, ctypes.c_size_t, _vp],
     "oxq_gptq_dequant": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "oxq_gguf_dequant": [_i, _vp, _vp, _i, _i, _i, _vp],
     "oxq_gguf_gemv": [_i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],

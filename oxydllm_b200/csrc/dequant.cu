@@ -210,7 +210,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi)
 __global__ void __launch_bounds__(256)
 awq_slab16_bf16_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict__ qzeros,
                        const void *__restrict__ scales, int scales_dtype, __nv_bfloat16 *__restrict__ out, int k,
-                       int n_cnt, int group_size, int n_full, int n_off, int vec_ok)
+                       int n_cnt, int group_size, int n_full, int n_off, int vec_ok, int row_mul, int row_add)
 {
     __shared__ __align__(16) uint32_t raw[128][32];
     __shared__ __align__(16) unsigned char stage[2][32 * 272];
@@ -261,7 +261,11 @@ awq_slab16_bf16_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__r
     const int row_l = 4 * warp + (lane >> 3), piece = lane & 7; // the row and 32-byte piece this lane stores
     const int j_st = jw0 + row_l;
     const bool st_ok = j_st < jw_end && k0 + 16 * piece < k;
-    __nv_bfloat16 *st0 = out + (size_t)(8 * (j_st - (n_off >> 3))) * k + k0 + 16 * piece;
+    // Output row of the slab's column n (counted from n_off): row_mul * n + row_add. (1, 0) is the plain
+    // dense weight; (2, 0) and (2, 1) on the gate and the up columns of a fused [gate | up] weight make
+    // gate j and up j neighbouring rows.
+    const int n_st = 8 * (j_st - (n_off >> 3));
+    __nv_bfloat16 *st0 = out + k0 + 16 * piece;
 #pragma unroll
     for (int p = 0; p < 8; p++) {
         const int c = p < 4 ? 2 * p : 2 * (p - 4) + 1; // nibble p holds out column c of the word
@@ -283,7 +287,8 @@ awq_slab16_bf16_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__r
         __syncthreads(); // buffer p & 1 complete; its previous readers (nibble p - 2) passed the sync of p - 1
         if (st_ok) {
             const uint4 *sv = reinterpret_cast<const uint4 *>(buf + row_l * 272 + piece * 32);
-            uint4 *dst = reinterpret_cast<uint4 *>(st0 + (size_t)c * k);
+            const int n_row = row_mul * (n_st + c) + row_add;
+            uint4 *dst = reinterpret_cast<uint4 *>(st0 + (size_t)n_row * k);
             dst[0] = sv[0];
             dst[1] = sv[1];
         }
@@ -461,13 +466,18 @@ static int grid_for(size_t work_items, int block = 256)
 // ---- row-range (slab) dequantization to bf16 for the tensor-core GEMM -----------------------
 // Rows [n_off, n_off + n_cnt) of the dense [n, k] weight into a contiguous [n_cnt, k] bf16 buffer.
 int awq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
-                          __nv_bfloat16 *out, int k, int n_full, int group_size, int n_off, int n_cnt, cudaStream_t st)
+                          __nv_bfloat16 *out, int k, int n_full, int group_size, int n_off, int n_cnt, cudaStream_t st,
+                          int row_mul, int row_add)
 {
+    OXQ_REQUIRE((row_mul == 1 && row_add == 0) ||
+                    (group_size % 16 == 0 && k % 16 == 0 && n_off % 8 == 0 && n_cnt % 8 == 0 && aligned(out, 16)),
+                OXQ_ERR_UNSUPPORTED, "strided-row dequantization needs group_size and in_features (%d, %d) multiples of 16 "
+                "and column ranges in multiples of 8", group_size, k);
     if (group_size % 16 == 0 && k % 16 == 0 && n_off % 8 == 0 && n_cnt % 8 == 0 && aligned(out, 16)) {
         const int vec_ok = aligned(qweight, 16) && (n_full >> 3) % 4 == 0 && (n_off >> 3) % 4 == 0;
         dim3 grid(ceil_div(n_cnt, 256), ceil_div(k, 128));
         awq_slab16_bf16_kernel<<<grid, 256, 0, st>>>(qweight, qzeros, scales, scales_dtype, out, k, n_cnt, group_size,
-                                                     n_full, n_off, vec_ok);
+                                                     n_full, n_off, vec_ok, row_mul, row_add);
         OXQ_LAUNCH_CHECK("awq_slab16_bf16_kernel");
         return OXQ_OK;
     }
@@ -571,7 +581,7 @@ OXQ_EXPORT int oxq_awq_dequant(const uint32_t *qweight, const uint32_t *qzeros, 
                 "quant in_features (%d) not divisible by group size (%d)", k, group_size);
     if (out_dtype == OXQ_BF16) // same bits, the fast producer of the tensor-core path
         return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, (__nv_bfloat16 *)w_out, k, n, group_size, 0, n,
-                                     (cudaStream_t)stream);
+                                     (cudaStream_t)stream, 1, 0);
     dim3 grid(ceil_div(n / 8, 8), ceil_div(k, AWQ_TK));
     DISPATCH_OUT(out_dtype, awq_dequant_kernel<OutT><<<grid, 256, 0, (cudaStream_t)stream>>>(
                                 qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size, n, 0));

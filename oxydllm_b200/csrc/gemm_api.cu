@@ -6,9 +6,10 @@
 
 namespace oxq {
 int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int n,
-                 int k, int n_off, int ldy, int *flag, cudaStream_t stream);
+                 int k, int n_off, int ldy, int *flag, cudaStream_t stream, int epi = 0);
 int awq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
-                          __nv_bfloat16 *out, int k, int n_full, int group_size, int n_off, int n_cnt, cudaStream_t st);
+                          __nv_bfloat16 *out, int k, int n_full, int group_size, int n_off, int n_cnt, cudaStream_t st,
+                          int row_mul = 1, int row_add = 0);
 int gptq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
                            __nv_bfloat16 *out, int k, int n_full, int group_size, int bits, int sym, int n_off,
                            int n_cnt, cudaStream_t st);
@@ -205,6 +206,22 @@ OXQ_EXPORT int oxq_mxfp4_gemm(const void *x, int x_dtype, const uint8_t *blocks,
     });
 }
 
+// ---- gated FFN projection: act(x . W_gate^T) * (x . W_up^T) on a fused AWQ [gate | up] weight ----
+// Decode-sized helper: y[r, j] = act(gu[r, j]) * gu[r, inter + j] for gu bf16 [m, 2 * inter] (gate half, then up half).
+__global__ void __launch_bounds__(256)
+gated_act_rows_kernel(const __nv_bfloat16 *__restrict__ gu, __nv_bfloat16 *__restrict__ y, int m, int inter, int act)
+{
+    const size_t total = (size_t)m * inter;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / inter, j = idx % inter;
+        const float gate = __bfloat162float(gu[r * 2 * inter + j]), up = __bfloat162float(gu[r * 2 * inter + inter + j]);
+        float v;
+        if (act == 1) v = gate * __fdividef(1.0f, 1.0f + __expf(-gate)) * up;
+        else v = 0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate))) * up;
+        y[idx] = __float2bfloat16_rn(v);
+    }
+}
+
 // ---- entry point that allocates nothing ----------------------------------------------------------
 // Scratch for oxq_awq_gemm_noalloc: a fixed device array that lives in the library image, so a
 // caller that must not (or cannot) call cudaMalloc still has somewhere to dequantize into.
@@ -214,6 +231,54 @@ constexpr size_t NOALLOC_SCRATCH_BYTES = WS_HEADER + NOALLOC_SLAB_BYTES;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
 // In host code the symbol above is only a handle; the device address is looked up once per device.
 static void *g_noalloc_scratch_addr[64] = {};
+
+extern "C" int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
+                            int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+                            int group_size, void *stream);
+
+OXQ_EXPORT int oxq_awq_ffn_gate_up(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros,
+                                   const void *scales, int scales_dtype, int activation, void *y, int m, int k, int inter,
+                                   int group_size, void *workspace, size_t workspace_bytes, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(qweight && qzeros && scales, OXQ_ERR_NULL, "oxq_awq_ffn_gate_up: null pointer");
+    OXQ_REQUIRE(valid_dtype(scales_dtype), OXQ_ERR_UNSUPPORTED, "oxq_awq_ffn_gate_up: unsupported scales dtype");
+    OXQ_REQUIRE(activation == 1 || activation == 2, OXQ_ERR_UNSUPPORTED,
+                "oxq_awq_ffn_gate_up: activation %d (1 = SiLU, 2 = GeLU-tanh)", activation);
+    OXQ_REQUIRE(inter > 0 && inter % 8 == 0 && group_size > 0 && k > 0 && k % group_size == 0, OXQ_ERR_BAD_SHAPE,
+                "oxq_awq_ffn_gate_up: intermediate size %d must be a multiple of 8 and in_features %d of the group size %d",
+                inter, k, group_size);
+    const int n = 2 * inter;
+    GemmCommon c;
+    int rc = prepare("oxq_awq_ffn_gate_up", c, x, x_dtype, nullptr, 0, y, OXQ_BF16, m, k, n, workspace, workspace_bytes, stream);
+    if (rc) return rc;
+    if (m <= 32) {
+        // Decode: the GEMV into a scratch row block [m, 2 * inter] (the workspace slab), then the activation.
+        rc = oxq_awq_gemv(x, x_dtype, qweight, qzeros, scales, scales_dtype, nullptr, 0, c.slab, OXQ_BF16, m, k, n, group_size,
+                          stream);
+        if (rc) return rc;
+        const int blocks = (int)(((size_t)m * inter + 255) / 256);
+        gated_act_rows_kernel<<<blocks < 2368 ? blocks : 2368, 256, 0, c.st>>>(c.slab, (__nv_bfloat16 *)y, m, inter, activation);
+        OXQ_LAUNCH_CHECK("gated_act_rows_kernel");
+        return OXQ_OK;
+    }
+    // Prefill: gate row j and up row j of the dequantized weight are written next to each other, so that
+    // every accumulator tile holds (gate, up) pairs and the activation runs in the GEMM's epilogue.
+    // A slab takes the same column range [a, b) of both halves: 2 (b - a) interleaved rows.
+    int pairs = slab_rows(n, k) / 2;
+    if (pairs < inter) pairs = pairs / 128 * 128; // whole 256-row tiles per slab
+    OXQ_REQUIRE(pairs >= 8, OXQ_ERR_WORKSPACE, "oxq_awq_ffn_gate_up: workspace slab too small for in_features %d", k);
+    for (int a = 0; a < inter; a += pairs) {
+        const int cnt = inter - a < pairs ? inter - a : pairs;
+        rc = awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, a, cnt, c.st, 2, 0);
+        if (rc) return rc;
+        rc = awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, inter + a, cnt, c.st, 2, 1);
+        if (rc) return rc;
+        rc = gemm_bf16_tn(c.x, c.slab, nullptr, 0, c.y, OXQ_BF16, c.m, 2 * cnt, c.k, 2 * a, inter, c.flag, c.st, activation);
+        if (rc) return rc;
+    }
+    return OXQ_OK;
+}
 
 OXQ_EXPORT size_t oxq_awq_gemm_noalloc_max_k(void) { return NOALLOC_SLAB_BYTES / (256 * 2); }
 

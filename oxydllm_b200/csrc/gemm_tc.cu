@@ -42,7 +42,16 @@ struct GemmParams {
     int m, n, k;      // n = rows of W in this call (a slab); y columns [n_off, n_off + n)
     int n_off, ldy;   // ldy = full out_features
     int tiles_m, tiles_n, bn; // tile grid of this call; bn = tile width (multiple of 32, <= 256)
+    int epi; // 0: y = acc (+ bias). 1 / 2: W rows interleave (gate j, up j); y[:, j] = SiLU / GeLU-tanh(gate) * up, bf16 [m, n/2]
 };
+
+// Gated FFN activations on f32 (ffn.rs:385-470: act(gate) * up).
+__device__ __forceinline__ float gated_act(float gate, float up, int epi)
+{
+    if (epi == 1) return gate * __fdividef(1.0f, 1.0f + __expf(-gate)) * up;
+    const float t = tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate));
+    return 0.5f * gate * (1.0f + t) * up;
+}
 
 // ---- PTX wrappers ---------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -266,7 +275,35 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * TC_BN + cb * 32, r);
                 tmem_ld_wait();
                 const int col0 = n0 + cb * 32; // column inside this slab
-                if (row < p.m && col0 < p.n) {
+                if (row < p.m && col0 < p.n && p.epi != 0) {
+                    // 32 accumulator columns = 16 (gate, up) pairs -> 16 outputs of this lane's row
+                    __nv_bfloat16 *yo = reinterpret_cast<__nv_bfloat16 *>(p.y) + (size_t)row * p.ldy + ((p.n_off + col0) >> 1);
+                    float act[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        float gate = __uint_as_float(r[2 * j]), up = __uint_as_float(r[2 * j + 1]);
+                        if (p.bias) {
+                            gate += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j);
+                            up += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j + 1);
+                        }
+                        act[j] = gated_act(gate, up, p.epi);
+                    }
+                    if (vec_ok && col0 + 32 <= p.n) {
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(act[2 * j], act[2 * j + 1]);
+                            packed[j] = *reinterpret_cast<uint32_t *>(&h2);
+                        }
+                        uint4 *dst = reinterpret_cast<uint4 *>(yo);
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (col0 + 2 * j < p.n) yo[j] = __float2bfloat16_rn(act[j]);
+                    }
+                } else if (row < p.m && col0 < p.n) {
                     const size_t out = (size_t)row * p.ldy + p.n_off + col0;
                     if (vec_ok && col0 + 32 <= p.n) {
                         uint32_t packed[16];
@@ -583,8 +620,10 @@ int gemm_pick_bn(int m, int n)
 
 // y[:, n_off : n_off + n] = x[m, k] . w[n, k]^T (+ bias) with x, w bf16 row-major.
 int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int n,
-                 int k, int n_off, int ldy, int *flag, cudaStream_t stream)
+                 int k, int n_off, int ldy, int *flag, cudaStream_t stream, int epi)
 {
+    OXQ_REQUIRE(epi == 0 || (y_dtype == OXQ_BF16 && n % 2 == 0 && n_off % 2 == 0), OXQ_ERR_UNSUPPORTED,
+                "gated epilogue needs bf16 output and an even number of interleaved columns");
     OXQ_REQUIRE(aligned(x, 16) && aligned(w, 16), OXQ_ERR_BAD_ALIGN, "tensor-core GEMM operands must be 16-byte aligned");
     OXQ_REQUIRE(k % 8 == 0, OXQ_ERR_UNSUPPORTED, "tensor-core GEMM needs in_features %% 8 == 0 (got %d)", k);
     const int bn = gemm_pick_bn(m, n);
@@ -602,7 +641,7 @@ int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype,
     }
     GemmParams p;
     p.bias = bias; p.y = y; p.flag = flag; p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
-    p.m = m; p.n = n; p.k = k; p.n_off = n_off; p.ldy = ldy;
+    p.m = m; p.n = n; p.k = k; p.n_off = n_off; p.ldy = ldy; p.epi = epi;
     p.tiles_m = ceil_div(m, TC_BM); p.tiles_n = ceil_div(n, bn); p.bn = bn;
     const int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
     gemm_bf16_tn_kernel<<<tiles < sms ? tiles : sms, 192, TC_SMEM_BYTES, stream>>>(map_a, map_b, p);

@@ -1,4 +1,4 @@
-// GGUF Q4_K decode GEMV (1 <= m <= 16), tuned variant.
+// GGUF Q4_K decode GEMV (1 <= m <= 32), tuned variant.
 //
 // Q4_K super-block (144 B / 256 weights): f16 d, f16 dmin, 12 bytes of 6-bit sub-block scales and
 // mins, 128 bytes of nibbles; byte t of 32-byte group iq holds element t of sub-block 2*iq (low
@@ -35,6 +35,7 @@ struct Q4kGemvParams {
     int bias_dtype, y_dtype;
     int m, k, n;
     int row_tiles, k_warps; // warps of a CTA = row_tiles x k_warps
+    int token_split;        // neighbouring CTAs that share their rows and take 8*MT tokens each (>= 1)
 };
 
 namespace cg = cooperative_groups;
@@ -98,7 +99,11 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
     const int nrt = p.row_tiles, kwn = p.k_warps, ks = (int)gridDim.y, rank = (int)blockIdx.y; // cluster = grid y extent
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     const int rt = warp % nrt, kw = warp / nrt;
-    const int n0 = (blockIdx.x * nrt + rt) * 16;
+    // Token tiles of one row group sit in neighbouring CTAs: they stream the same weights at the same
+    // time, so all but the first reader hit in L2.
+    const int zt = blockIdx.x % p.token_split, bx = blockIdx.x / p.token_split;
+    const int m0 = zt * 8 * MT, m_loc = min(8 * MT, p.m - m0); // this CTA's tokens [m0, m0 + m_loc)
+    const int n0 = (bx * nrt + rt) * 16;
     const int nsb = p.k >> 8;                 // super-blocks per row
     const int sl_sb = nsb / ks, sb_beg = rank * sl_sb, sb_end = sb_beg + sl_sb; // this CTA's slice
     const int kl = sl_sb << 8, k_cta = sb_beg << 8;
@@ -106,7 +111,7 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
     const int xrow = kl + 32;                 // halves per staged token row: 64 bytes of padding keep the
                                               // 16-byte fragment reads of a quarter warp on distinct banks
     __half *xs = reinterpret_cast<__half *>(smem);
-    float *sx = reinterpret_cast<float *>(smem + (size_t)p.m * xrow * sizeof(__half)); // [kl/32][8*MT]
+    float *sx = reinterpret_cast<float *>(smem + (size_t)m_loc * xrow * sizeof(__half)); // [kl/32][8*MT]
     float *red = sx + (size_t)(kl >> 5) * 8 * MT;                                       // [warp][MT*4][lane]
     float *zeros = red + blockDim.x * MT * 4; // 16 bytes of zeros: what lanes without a token read as x
 
@@ -126,8 +131,8 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
     if (tid < 4) zeros[tid] = 0.0f;
     for (int idx = tid; idx < 8 * MT * (kl >> 5); idx += blockDim.x) sx[idx] = 0.0f; // rows without a token
     __syncthreads();
-    for (int row = 0; row < p.m; row++) {
-        const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)row * p.k + k_cta);
+    for (int row = 0; row < m_loc; row++) {
+        const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)(m0 + row) * p.k + k_cta);
         uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
         for (int q4 = tid; q4 < (kl >> 2); q4 += blockDim.x) { // kl / 4 is a multiple of 64: whole warps
             const uint2 raw = __ldg(src + q4);
@@ -151,7 +156,7 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
     int xstep[MT];
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
-        const bool real = 8 * mt + g < p.m;
+        const bool real = 8 * mt + g < m_loc;
         xp[mt] = real ? xs + (size_t)(8 * mt + g) * xrow + 8 * c : reinterpret_cast<const __half *>(zeros);
         xstep[mt] = real ? 1 : 0;
     }
@@ -232,15 +237,15 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
     const int slots = nrt * MT * 4 * 32;
     for (int o = rank * blockDim.x + tid; o < slots; o += ks * blockDim.x) {
         const int ln = o & 31, e = (o >> 5) & 3, mt = (o >> 7) % MT, wt = (o >> 7) / MT;
-        const int nn = (blockIdx.x * nrt + wt) * 16 + (ln >> 2) + 8 * (e >> 1), row = 8 * mt + 2 * (ln & 3) + (e & 1);
-        if (nn < p.n && row < p.m) {
+        const int nn = (bx * nrt + wt) * 16 + (ln >> 2) + 8 * (e >> 1), row = 8 * mt + 2 * (ln & 3) + (e & 1);
+        if (nn < p.n && row < m_loc) {
             float sum = 0.0f;
             for (int q = 0; q < ks; q++) {
                 const float *src = ks > 1 ? cluster.map_shared_rank(red, q) : red;
                 for (int w = 0; w < kwn; w++) sum += src[((w * nrt + wt) * MT * 4 + mt * 4 + e) * 32 + ln];
             }
             if (p.bias) sum += load_as_f32(p.bias, p.bias_dtype, nn);
-            store_as(p.y, p.y_dtype, (size_t)row * p.n + nn, sum);
+            store_as(p.y, p.y_dtype, (size_t)(m0 + row) * p.n + nn, sum);
         }
     }
     if (ks > 1) cluster.sync(); // nobody leaves while a peer may still read its shared memory
@@ -254,7 +259,7 @@ static size_t q4k_smem(int mt, int m, int kl, int warps)
 template <int MT> static int launch_q4k(const Q4kGemvParams &p, int ks, cudaStream_t st)
 {
     const int nw = p.row_tiles * p.k_warps;
-    const size_t smem = q4k_smem(MT, p.m, p.k / ks, nw);
+    const size_t smem = q4k_smem(MT, p.m < 8 * MT ? p.m : 8 * MT, p.k / ks, nw);
     auto kern = q4k_gemv_kernel<MT>;
     static size_t configured[64] = {};
     int device = 0;
@@ -264,7 +269,7 @@ template <int MT> static int launch_q4k(const Q4kGemvParams &p, int ks, cudaStre
         if (device < 64) configured[device] = smem;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ceil_div(p.n, 16 * p.row_tiles), ks, 1);
+    cfg.gridDim = dim3(ceil_div(p.n, 16 * p.row_tiles) * p.token_split, ks, 1);
     cfg.blockDim = dim3(nw * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -282,7 +287,7 @@ template <int MT> static int launch_q4k(const Q4kGemvParams &p, int ks, cudaStre
 // True when the tuned kernel applies; otherwise the caller uses the generic row-format kernel.
 bool q4k_gemv_supported(int m, int k)
 {
-    return m <= 16 && k % 256 == 0 && q4k_smem(m <= 8 ? 1 : 2, m, k, 8) <= 200 * 1024;
+    return m <= 32 && k % 256 == 0 && q4k_smem(m <= 8 ? 1 : 2, m < 16 ? m : 16, k, 8) <= 200 * 1024;
 }
 
 int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k,
@@ -301,6 +306,7 @@ int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype
         }
     }
     p.row_tiles = nrt; p.k_warps = kw;
+    p.token_split = m <= 8 ? 1 : ceil_div(m, 16); // more than 16 tokens: 16 per CTA on neighbouring CTAs
     return m <= 8 ? launch_q4k<1>(p, ks, st) : launch_q4k<2>(p, ks, st);
 }
 

@@ -58,6 +58,15 @@ def awq_matmul(lin, x2, y):
               lin.group_size, _p(ws), ws.numel(), _st())
 
 
+def awq_ffn_gate_up(lin, x2, y, activation: int):
+    """``y[m, inter] = act(x . W_gate^T) * (x . W_up^T)`` on the fused ``[gate | up]`` AWQ linear ``lin``."""
+    from .linear import _dt
+    ws = workspace(lin.out_features, lin.in_features, x2.device)
+    _lib.call("oxq_awq_ffn_gate_up", _p(x2), _dt(x2.dtype), _p(lin.qweight), _p(lin.qzeros), _p(lin.scales),
+              _dt(lin.scales.dtype), activation, _p(y), x2.shape[0], lin.in_features, lin.out_features // 2,
+              lin.group_size, _p(ws), ws.numel(), _st())
+
+
 def fp8_matmul(lin, s, s_out, s_in, x2, y):
     from .linear import _dt
     ws = workspace(lin.out_features, lin.in_features, x2.device)

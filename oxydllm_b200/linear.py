@@ -252,6 +252,41 @@ class PackedQuantLinear:
                   self.in_features, self.out_features, self.group_size, _stream())
 
 
+ACTIVATIONS = {"silu": 1, "gelu_tanh": 2}
+
+
+class GatedFfnProjection:
+    """Fused gate+up projection and gated activation of ``FeedForward`` (ffn.rs:235-254, 385-470).
+
+    ``gate_up`` is the AWQ linear over ``concat_awq_along_out([gate_proj, up_proj])`` (out features
+    ``2 * intermediate``); ``forward`` returns ``act(gate) * up`` with ``act`` SiLU or tanh-GeLU, i.e.
+    what the reference's ``GateUpProjection::Fused`` branch feeds to ``down_proj``.
+    """
+
+    def __init__(self, gate_up: "PackedQuantLinear", activation: str = "silu"):
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"GatedFfnProjection: unknown activation {activation!r} (silu, gelu_tanh)")
+        if gate_up.out_features % 16:
+            raise ValueError(f"GatedFfnProjection: fused out_features {gate_up.out_features} must be 2 * intermediate, "
+                             "intermediate a multiple of 8")
+        if gate_up.bias is not None:
+            raise ValueError("GatedFfnProjection: the fused gate/up projection carries no bias")
+        self.gate_up, self.activation = gate_up, activation
+        self.intermediate = gate_up.out_features // 2
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        lin = self.gate_up
+        x2, lead, m = _flatten_x(x, lin.in_features, "GatedFfnProjection")
+        _require_cuda(x2, lin.qweight, lin.qzeros, lin.scales)
+        if x2.dtype != torch.bfloat16:
+            raise ValueError("GatedFfnProjection: activations must be bf16")
+        y = torch.empty((m, self.intermediate), dtype=x2.dtype, device=x2.device)
+        if m:
+            from . import gemm
+            gemm.awq_ffn_gate_up(lin, x2, y, ACTIVATIONS[self.activation])
+        return y.reshape(*lead, self.intermediate)
+
+
 class Fp8Linear:
     """``Fp8Linear`` (linear.rs:81-146): E4M3 weight ``[out, in]`` + optional f32 ``scale_inv``.
 

@@ -95,3 +95,26 @@ def test_workspace_too_small_is_rejected(cuda):
     one = ctypes.c_void_p(256)
     with pytest.raises(_lib.OxqError, match="workspace of"):
         _lib.call("oxq_awq_gemm", one, 2, one, one, one, 1, None, 0, one, 2, 64, 256, 256, 128, one, 16, None)
+
+
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+@pytest.mark.parametrize("m,k,inter,g", [(1, 256, 64, 64), (7, 512, 200, 128), (33, 256, 64, 32), (300, 1024, 1000, 128),
+                                         (2048, 512, 1024, 128), (64, 4096, 9216, 128)])  # the last needs two slabs
+def test_gated_ffn_gate_up_matches_oracle(cuda, activation, m, k, inter, g):
+    """act(gate) * up on the fused [gate | up] AWQ weight: GEMV route for m <= 32, fused GEMM epilogue above."""
+    from oxydllm_b200 import gemm
+    qw, qz, sc = synth.awq_layer(k, 2 * inter, g, seed=m + inter)
+    sc = (sc.astype(np.float32) * 8.0).astype(sc.dtype)  # larger pre-activations: both tails of the activations
+    lin = L.PackedQuantLinear(L.QuantWeight.new_awq(4, words(qw), words(qz), dev(sc)))
+    x = synth.activations(m, k, seed=3)
+    w = oracle.awq_dequant(qw, qz, sc)
+    if m > 32:
+        w = oracle.round_bf16(w)  # the tensor-core path multiplies the bf16-rounded dense weight
+    ref = oracle.gated_ffn(x, w, activation)
+    y = L.GatedFfnProjection(lin, activation).forward(dev(x, torch.bfloat16))
+    gemm.check(gemm.workspace(1, 8, "cuda"))
+    got = y.float().cpu().numpy()
+    assert got.shape == (m, inter) and np.isfinite(got).all()
+    # products of two projections: tolerance relative to the row's largest |gate| * |up| scale
+    row_inf = np.abs(ref).max(axis=1, keepdims=True)
+    assert (np.abs(got - ref) <= 3e-2 * row_inf + 1e-4).all(), float(np.abs(got - ref).max())

@@ -83,3 +83,21 @@ def test_pack_unpack_awq_roundtrip_and_order():
     # slot k of a word holds column AWQ_PACK_ORDER[k] (awq.rs:23, 391-400)
     for k, col in enumerate(F.AWQ_PACK_ORDER):
         assert ((w[0, 0] >> (4 * k)) & 0xF) == v[0, col]
+
+
+def test_oracle_gated_ffn_known_values():
+    """act(gate) * up on a hand-built fused weight: identity gate rows, constant up rows."""
+    import oracle
+    inter, k = 4, 4
+    w = np.zeros((2 * inter, k), np.float32)
+    w[:inter] = np.eye(inter, dtype=np.float32)      # gate = x
+    w[inter:] = 0.5 * np.eye(inter, dtype=np.float32)  # up = x / 2
+    x = np.array([[0.0, 1.0, -2.0, 3.0]], np.float32)
+    silu = oracle.gated_ffn(x, w, "silu")[0]
+    want = [g / (1.0 + np.exp(-g)) * (g / 2) for g in x[0]]
+    assert np.allclose(silu, want, rtol=1e-6, atol=1e-7)
+    gelu = oracle.gated_ffn(x, w, "gelu_tanh")[0]
+    want = [0.5 * g * (1.0 + np.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3))) * (g / 2) for g in x[0]]
+    assert np.allclose(gelu, want, rtol=1e-6, atol=1e-7)
+    with pytest.raises(ValueError):
+        oracle.gated_ffn(x, w, "relu")
