@@ -456,6 +456,87 @@ q4k_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restri
     }
 }
 
+// Q8_0 / Q4_0 / Q6_K producers: one thread per 32 (Q8_0, Q4_0) or 16 (Q6_K) weights, halfword loads
+// (the blocks are only 2-byte aligned), the element-wise kernels' arithmetic operation for operation,
+// 16-byte stores. Exact small integers come from the 2^23 trick instead of the conversion unit.
+__device__ __forceinline__ float small_int_f32(int v) // |v| < 2^22
+{
+    return __uint_as_float(0x4B400000u + (uint32_t)v) - 12582912.0f; // 1.5 * 2^23 + v, minus 1.5 * 2^23
+}
+
+__global__ void __launch_bounds__(256)
+q80_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restrict__ out, size_t total_blocks)
+{
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_blocks;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const unsigned short *h = reinterpret_cast<const unsigned short *>(blocks + idx * 34);
+        const float d = __half2float(__ushort_as_half(__ldg(h)));
+        uint32_t o[16];
+#pragma unroll
+        for (int t = 0; t < 16; t++) {
+            const uint32_t two = __ldg(h + 1 + t); // elements 2t, 2t+1
+            const float a = __fmul_rn(small_int_f32((int)(signed char)(two & 0xFFu)), d);
+            const float b = __fmul_rn(small_int_f32((int)(signed char)(two >> 8)), d);
+            o[t] = pack_bf16x2_rn(a, b);
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(out + idx * 32);
+#pragma unroll
+        for (int t = 0; t < 4; t++) dst[t] = make_uint4(o[4 * t], o[4 * t + 1], o[4 * t + 2], o[4 * t + 3]);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+q40_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restrict__ out, size_t total_blocks)
+{
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_blocks;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const unsigned short *h = reinterpret_cast<const unsigned short *>(blocks + idx * 18);
+        const float d = __half2float(__ushort_as_half(__ldg(h)));
+        uint32_t lo[8], hi[8]; // elements 0..15 (low nibbles) and 16..31 (high nibbles)
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+            const uint32_t two = __ldg(h + 1 + t); // bytes 2t, 2t+1
+            const int b0 = (int)(two & 0xFFu), b1 = (int)(two >> 8);
+            lo[t] = pack_bf16x2_rn(__fmul_rn(small_int_f32((b0 & 15) - 8), d), __fmul_rn(small_int_f32((b1 & 15) - 8), d));
+            hi[t] = pack_bf16x2_rn(__fmul_rn(small_int_f32((b0 >> 4) - 8), d), __fmul_rn(small_int_f32((b1 >> 4) - 8), d));
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(out + idx * 32);
+        dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        dst[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+        dst[2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        dst[3] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+    }
+}
+
+// Q6_K: a thread takes the 16 weights that share one scale: super-block sb, half h, quad q, sixteen s.
+__global__ void __launch_bounds__(256)
+q6k_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restrict__ out, size_t total_groups)
+{
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_groups;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t sb = idx >> 4;
+        const int grp = (int)(idx & 15), h = grp >> 3, q = (grp >> 1) & 3, s = grp & 1; // element 128h + 32q + 16s + i
+        const uint8_t *blk = blocks + sb * 210;
+        const unsigned short *ql = reinterpret_cast<const unsigned short *>(blk + 64 * h + 32 * (q & 1) + 16 * s);
+        const unsigned short *qh = reinterpret_cast<const unsigned short *>(blk + 128 + 32 * h + 16 * s);
+        const float d = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short *>(blk + 208))));
+        const int sc = (int)(signed char)blk[192 + 8 * h + 2 * q + s];
+        const float ds = __fmul_rn(d, small_int_f32(sc));
+        uint32_t o[8];
+#pragma unroll
+        for (int t = 0; t < 8; t++) {
+            const uint32_t l2 = __ldg(ql + t), h2 = __ldg(qh + t); // bytes for elements 2t, 2t+1
+            const int n0 = (int)((l2 >> (q < 2 ? 0 : 4)) & 0x0Fu), n1 = (int)((l2 >> (q < 2 ? 8 : 12)) & 0x0Fu);
+            const int b0 = (int)((h2 >> (2 * q)) & 3u), b1 = (int)((h2 >> (8 + 2 * q)) & 3u);
+            o[t] = pack_bf16x2_rn(__fmul_rn(ds, small_int_f32((n0 | (b0 << 4)) - 32)),
+                                  __fmul_rn(ds, small_int_f32((n1 | (b1 << 4)) - 32)));
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(out + sb * 256 + 128 * h + 32 * q + 16 * s);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
 static int grid_for(size_t work_items, int block = 256)
 {
     size_t blocks = (work_items + block - 1) / block;
@@ -509,6 +590,13 @@ int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *
         const size_t groups = total / 64;
         q4k_slab_bf16_kernel<<<grid_for(groups), 256, 0, st>>>(b, out, groups);
         OXQ_LAUNCH_CHECK("q4k_slab_bf16_kernel");
+        return OXQ_OK;
+    }
+    if (aligned(b, 2) && aligned(out, 16) && ggml_type != OXQ_GGML_Q4_K) {
+        if (ggml_type == OXQ_GGML_Q8_0) q80_slab_bf16_kernel<<<grid_for(total / 32), 256, 0, st>>>(b, out, total / 32);
+        else if (ggml_type == OXQ_GGML_Q4_0) q40_slab_bf16_kernel<<<grid_for(total / 32), 256, 0, st>>>(b, out, total / 32);
+        else q6k_slab_bf16_kernel<<<grid_for(total / 16), 256, 0, st>>>(b, out, total / 16);
+        OXQ_LAUNCH_CHECK("gguf slab kernel");
         return OXQ_OK;
     }
     const int grid = grid_for(total);
