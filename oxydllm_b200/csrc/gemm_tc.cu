@@ -12,11 +12,15 @@
 //   warps 2-5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, bias, narrowing, stores.
 // Every wait is bounded (wall-clock limit); on expiry the kernel records a code in the caller's
 // flag word, all roles fall through, TMEM is released and the kernel returns.
+// With more than one 128-row tile of x the dense GEMM runs as pairs of CTAs (tcgen05 cta_group::2):
+// a pair shares a 256 x BN tile and each CTA stages only half of the W tile (see the two-CTA kernel).
 //
 // The quantized entry points dequantize W in slabs of rows into the caller's workspace with the
 // bit-exact dequantization kernels and run this GEMM per slab: the B operand the tensor cores
 // see is exactly the dense weight the reference materialises (awq.rs:325-440, linear.rs:96-141).
 #include <cuda.h>
+
+#include <cstdlib>
 
 #include "oxq_common.cuh"
 
@@ -166,6 +170,68 @@ __host__ __device__ constexpr uint32_t tc_idesc(int m, int n)
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// One 32-column chunk of one accumulator row: bias, optional gated activation, narrowing, store.
+__device__ __forceinline__ void gemm_store_chunk(const GemmParams &p, const uint32_t (&r)[32], int row, int col0, bool vec_ok)
+{
+    if (row < p.m && col0 < p.n && p.epi != 0) {
+        // 32 accumulator columns = 16 (gate, up) pairs -> 16 outputs of this lane's row
+        __nv_bfloat16 *yo = reinterpret_cast<__nv_bfloat16 *>(p.y) + (size_t)row * p.ldy + ((p.n_off + col0) >> 1);
+        float act[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            float gate = __uint_as_float(r[2 * j]), up = __uint_as_float(r[2 * j + 1]);
+            if (p.bias) {
+                gate += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j);
+                up += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j + 1);
+            }
+            act[j] = gated_act(gate, up, p.epi);
+        }
+        if (vec_ok && col0 + 32 <= p.n) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(act[2 * j], act[2 * j + 1]);
+                packed[j] = *reinterpret_cast<uint32_t *>(&h2);
+            }
+            uint4 *dst = reinterpret_cast<uint4 *>(yo);
+            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (col0 + 2 * j < p.n) yo[j] = __float2bfloat16_rn(act[j]);
+        }
+    } else if (row < p.m && col0 < p.n) {
+        const size_t out = (size_t)row * p.ldy + p.n_off + col0;
+        if (vec_ok && col0 + 32 <= p.n) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
+                if (p.bias) {
+                    v0 += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j);
+                    v1 += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j + 1);
+                }
+                __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                packed[j] = *reinterpret_cast<uint32_t *>(&h);
+            }
+            uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.y) + out);
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+                dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                if (col0 + j < p.n) {
+                    float v = __uint_as_float(r[j]);
+                    if (p.bias) v += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + j);
+                    store_as(p.y, p.y_dtype, out + j, v);
+                }
+            }
+        }
+    }
+}
+
 // Persistent kernel: CTA c handles tiles c, c + gridDim.x, ... (m fastest, so CTAs running together
 // share W tiles through L2). Two TMEM accumulators (2 x 256 columns) let the epilogue of one tile
 // overlap the MMAs of the next. `bn` (a multiple of 32, <= 256) is the tile width chosen by the host.
@@ -274,64 +340,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * TC_BN + cb * 32, r);
                 tmem_ld_wait();
-                const int col0 = n0 + cb * 32; // column inside this slab
-                if (row < p.m && col0 < p.n && p.epi != 0) {
-                    // 32 accumulator columns = 16 (gate, up) pairs -> 16 outputs of this lane's row
-                    __nv_bfloat16 *yo = reinterpret_cast<__nv_bfloat16 *>(p.y) + (size_t)row * p.ldy + ((p.n_off + col0) >> 1);
-                    float act[16];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        float gate = __uint_as_float(r[2 * j]), up = __uint_as_float(r[2 * j + 1]);
-                        if (p.bias) {
-                            gate += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j);
-                            up += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j + 1);
-                        }
-                        act[j] = gated_act(gate, up, p.epi);
-                    }
-                    if (vec_ok && col0 + 32 <= p.n) {
-                        uint32_t packed[8];
-#pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(act[2 * j], act[2 * j + 1]);
-                            packed[j] = *reinterpret_cast<uint32_t *>(&h2);
-                        }
-                        uint4 *dst = reinterpret_cast<uint4 *>(yo);
-                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            if (col0 + 2 * j < p.n) yo[j] = __float2bfloat16_rn(act[j]);
-                    }
-                } else if (row < p.m && col0 < p.n) {
-                    const size_t out = (size_t)row * p.ldy + p.n_off + col0;
-                    if (vec_ok && col0 + 32 <= p.n) {
-                        uint32_t packed[16];
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            float v0 = __uint_as_float(r[2 * j]), v1 = __uint_as_float(r[2 * j + 1]);
-                            if (p.bias) {
-                                v0 += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j);
-                                v1 += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + 2 * j + 1);
-                            }
-                            __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-                            packed[j] = *reinterpret_cast<uint32_t *>(&h);
-                        }
-                        uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.y) + out);
-#pragma unroll
-                        for (int q = 0; q < 4; q++)
-                            dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            if (col0 + j < p.n) {
-                                float v = __uint_as_float(r[j]);
-                                if (p.bias) v += load_as_f32(p.bias, p.bias_dtype, p.n_off + col0 + j);
-                                store_as(p.y, p.y_dtype, out + j, v);
-                            }
-                        }
-                    }
-                }
+                gemm_store_chunk(p, r, row, n0 + cb * 32, vec_ok);
             }
             // This warp has drained its quarter of the accumulator: hand the buffer back.
             tc_fence_before();
@@ -344,6 +353,182 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 2 * TC_BN);
+    }
+}
+
+// ---- two-CTA variant (tcgen05 cta_group::2) -----------------------------------------------------
+// A cluster of two CTAs on neighbouring SMs computes one 256 x BN tile: CTA r of the pair owns rows
+// 128 r .. 128 r + 127 of it (its own x tile, its own 128 TMEM lanes) and loads only HALF of the W
+// tile (rows n0 + r BN/2 .. of W); the MMA, issued by the even CTA alone, reads both halves out of
+// the two CTAs' shared memory. Per k block an SM stages 16 KB of x and BN/2 x 128 B of W instead of
+// BN x 128 B, which is what the one-CTA kernel is short of (operand traffic per tensor-core cycle).
+// Protocol: both CTAs issue their TMA loads with cta_group::2 so that the bytes are counted on the
+// even CTA's full barrier; tcgen05.commit with a two-CTA multicast releases ring slots and
+// accumulators in both CTAs; the epilogue warps of both CTAs arrive on the even CTA's
+// accumulator-free barrier. All waits are bounded as in the one-CTA kernel.
+constexpr int TC2_STAGES = 6;
+constexpr uint32_t TC2_B_BYTES = (TC_BN / 2) * TC_BK * 2;
+constexpr uint32_t TC2_STAGE_BYTES = TC_A_BYTES + TC2_B_BYTES;
+constexpr size_t TC2_SMEM_BYTES = 1024 + (size_t)TC2_STAGES * TC2_STAGE_BYTES + 256;
+constexpr uint32_t TC_PEER_BIT_MASK = 0xFEFFFFFFu; // clears the CTA-rank bit of a shared::cluster address: the even CTA's copy
+
+__device__ __forceinline__ void tma_load_2d_2cta(uint32_t dst, const CUtensorMap *map, uint32_t bar_even, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_even), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_bf16_2cta(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    const uint32_t z = 0u;
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
+                 : "memory");
+}
+// Arrive on the barrier at the same offset in both CTAs once the MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_2cta(uint32_t bar)
+{
+    const unsigned short mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask)
+                 : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmParams p)
+{
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u; // swizzled tiles need 1024-byte alignment
+    unsigned char *base_ptr = smem_raw + (base - raw);
+    const uint32_t bars = base + TC2_STAGES * TC2_STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (TC2_STAGES + s); };
+    auto tmem_full_bar = [&](int b) { return bars + 8u * (2 * TC2_STAGES + b); };
+    auto tmem_empty_bar = [&](int b) { return bars + 8u * (2 * TC2_STAGES + 2 + b); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + TC2_STAGES * TC2_STAGE_BYTES + 8 * (2 * TC2_STAGES + 4));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank(); // 0: issues the MMAs, 1: its partner
+    const int k_iters = (p.k + TC_BK - 1) / TC_BK;
+    const int pair_m = (p.tiles_m + 1) / 2;             // 256-row tiles
+    const int num_tiles = pair_m * p.tiles_n;
+    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    const uint32_t half_b = (uint32_t)(p.bn / 2) * TC_BK * 2;
+    const uint32_t stage_tx = 2u * (TC_A_BYTES + half_b); // both CTAs' copies land on the even CTA's barrier
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC2_STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(tmem_full_bar(b), 1);
+            mbar_init(tmem_empty_bar(b), 8); // one arrival per epilogue warp of both CTAs (used in the even CTA only)
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) { // the allocating warp (the same warp index in both CTAs) also frees
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * TC_BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all(); // barriers of both CTAs exist before anything is signalled across the pair
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+                const int m0 = ((tile % pair_m) * 2 + (int)rank) * TC_BM;                  // this CTA's 128 rows
+                const int n0 = (tile / pair_m) * p.bn + (int)rank * (p.bn / 2);           // this CTA's half of the W rows
+                for (int kb = 0; kb < k_iters; kb++, it++) {
+                    const int s = it % TC2_STAGES;
+                    ok = mbar_wait(empty_bar(s), ((it / TC2_STAGES) & 1) ^ 1, p.flag, 1);
+                    if (!ok) break;
+                    if (rank == 0) mbar_arrive_expect_tx(full_bar(s), stage_tx);
+                    const uint32_t sa = base + s * TC2_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                    const uint32_t bar_even = full_bar(s) & TC_PEER_BIT_MASK;
+                    tma_load_2d_2cta(sa, &map_a, bar_even, kb * TC_BK, m0);
+                    tma_load_2d_2cta(sb, &map_b, bar_even, kb * TC_BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0 && elect_one()) {
+            const uint32_t idesc = tc_idesc(2 * TC_BM, p.bn);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, local++) {
+                const int buf = local & 1;
+                ok = mbar_wait(tmem_empty_bar(buf), ((local >> 1) & 1) ^ 1, p.flag, 4);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * TC_BN;
+                for (int kb = 0; kb < k_iters; kb++, it++) {
+                    const int s = it % TC2_STAGES;
+                    ok = mbar_wait(full_bar(s), (it / TC2_STAGES) & 1, p.flag, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = base + s * TC2_STAGE_BYTES, sb = sa + TC_A_BYTES;
+                    const uint64_t da = kmajor_sw128_desc(sa), db = kmajor_sw128_desc(sb);
+#pragma unroll
+                    for (int kk = 0; kk < TC_BK / TC_UMMA_K; kk++)
+                        umma_bf16_2cta(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
+                    umma_commit_2cta(empty_bar(s)); // slot reusable in both CTAs once these MMAs have read it
+                }
+                umma_commit_2cta(tmem_full_bar(buf)); // accumulator complete in both CTAs
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const bool vec_ok = p.y_dtype == OXQ_BF16 && (p.ldy % 8 == 0) && (p.n_off % 8 == 0) &&
+                            (reinterpret_cast<uintptr_t>(p.y) & 15) == 0;
+        uint32_t local = 0;
+        bool ok = true;
+        for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, local++) {
+            const int buf = local & 1;
+            const int m0 = ((tile % pair_m) * 2 + (int)rank) * TC_BM, n0 = (tile / pair_m) * p.bn;
+            const int row = m0 + quad * 32 + lane;
+            ok = mbar_wait(tmem_full_bar(buf), (local >> 1) & 1, p.flag, 3);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int cb = 0; cb < p.bn / 32; cb++) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + buf * TC_BN + cb * 32, r);
+                tmem_ld_wait();
+                gemm_store_chunk(p, r, row, n0 + cb * 32, vec_ok);
+            }
+            // This warp has drained its quarter of its CTA's accumulator: tell the MMA issuer (even CTA).
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(tmem_empty_bar(buf) & TC_PEER_BIT_MASK) : "memory");
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    cluster_sync_all(); // neither CTA frees tensor memory or leaves while its partner may still use the pair
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * TC_BN) : "memory");
     }
 }
 
@@ -618,6 +803,21 @@ int gemm_pick_bn(int m, int n)
     return best;
 }
 
+// The same for the two-CTA kernel: 256-row tiles, one cluster of two CTAs per tile, sm_count / 2 clusters.
+int gemm_pick_bn_2cta(int m, int n)
+{
+    const int clusters = sm_count() / 2, pair_m = (ceil_div(m, TC_BM) + 1) / 2;
+    long long best_cost = -1;
+    int best = TC_BN;
+    for (int bn : TC_BN_CHOICES) {
+        const long long tiles = (long long)pair_m * ceil_div(n, bn);
+        const long long rounds = (tiles + clusters - 1) / clusters;
+        const long long cost = rounds * (bn + 24);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
 // y[:, n_off : n_off + n] = x[m, k] . w[n, k]^T (+ bias) with x, w bf16 row-major.
 int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int n,
                  int k, int n_off, int ldy, int *flag, cudaStream_t stream, int epi)
@@ -626,7 +826,10 @@ int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype,
                 "gated epilogue needs bf16 output and an even number of interleaved columns");
     OXQ_REQUIRE(aligned(x, 16) && aligned(w, 16), OXQ_ERR_BAD_ALIGN, "tensor-core GEMM operands must be 16-byte aligned");
     OXQ_REQUIRE(k % 8 == 0, OXQ_ERR_UNSUPPORTED, "tensor-core GEMM needs in_features %% 8 == 0 (got %d)", k);
-    const int bn = gemm_pick_bn(m, n);
+    // More than one 128-row tile: pairs of CTAs share 256-row tiles (two-CTA kernel) unless switched off.
+    const char *env2 = getenv("OXQ_GEMM_2CTA"); // bench-harness knob: "0" keeps the one-CTA kernel
+    const bool two_cta = m > TC_BM && !(env2 && env2[0] == '0');
+    const int bn = two_cta ? gemm_pick_bn_2cta(m, n) : gemm_pick_bn(m, n);
     CUtensorMap map_a, map_b;
     int rc = make_map_bf16(&map_a, x, (uint64_t)m, (uint64_t)k, TC_BM);
     if (rc) return rc;
@@ -644,6 +847,32 @@ int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype,
     p.m = m; p.n = n; p.k = k; p.n_off = n_off; p.ldy = ldy; p.epi = epi;
     p.tiles_m = ceil_div(m, TC_BM); p.tiles_n = ceil_div(n, bn); p.bn = bn;
     const int tiles = p.tiles_m * p.tiles_n, sms = sm_count();
+    if (two_cta) {
+        // W box of half a tile per CTA; pairs of CTAs share a 256-row tile.
+        rc = make_map_bf16(&map_b, w, (uint64_t)n, (uint64_t)k, (uint32_t)(bn / 2));
+        if (rc) return rc;
+        static bool configured2[64] = {};
+        if (device >= 64 || !configured2[device]) {
+            OXQ_CUDA(cudaFuncSetAttribute(gemm_bf16_tn_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC2_SMEM_BYTES));
+            if (device < 64) configured2[device] = true;
+        }
+        const int pair_tiles = ((p.tiles_m + 1) / 2) * p.tiles_n;
+        int clusters = sms / 2 < pair_tiles ? sms / 2 : pair_tiles;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * clusters, 1, 1);
+        cfg.blockDim = dim3(192, 1, 1);
+        cfg.dynamicSmemBytes = TC2_SMEM_BYTES;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        OXQ_CUDA(cudaLaunchKernelEx(&cfg, gemm_bf16_tn_2cta_kernel, map_a, map_b, p));
+        return OXQ_OK;
+    }
     gemm_bf16_tn_kernel<<<tiles < sms ? tiles : sms, 192, TC_SMEM_BYTES, stream>>>(map_a, map_b, p);
     OXQ_LAUNCH_CHECK("gemm_bf16_tn_kernel");
     return OXQ_OK;
