@@ -537,6 +537,49 @@ q6k_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restri
     }
 }
 
+// GPTQ 4-bit: a word holds 8 consecutive k of one out column, so a thread turns one word into 16
+// contiguous output bytes. A CTA of 256 threads stages 32 word rows (256 k) x 32 out columns with
+// coalesced loads along the columns, then reads them transposed: a warp owns 4 columns, its lanes
+// walk the word rows, so every column is stored as 512 contiguous bytes. Arithmetic as in the
+// element-wise kernel: (q - (zero + 1)) * scale in f32, one rounding. Needs group_size % 8 == 0.
+__global__ void __launch_bounds__(256)
+gptq4_slab_bf16_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict__ qzeros,
+                       const void *__restrict__ scales, int scales_dtype, __nv_bfloat16 *__restrict__ out, int k,
+                       int n_cnt, int group_size, int sym, int n_full, int n_off)
+{
+    __shared__ uint32_t tile[32][33];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int c0 = blockIdx.x * 32, kp0 = blockIdx.y * 32, kwords = k >> 3;
+#pragma unroll
+    for (int it = 0; it < 4; it++) {
+        const int r = warp + 8 * it, kp = kp0 + r, col = c0 + lane;
+        tile[r][lane] = (kp < kwords && col < n_cnt) ? __ldcs(qweight + (size_t)kp * n_full + n_off + col) : 0u;
+    }
+    __syncthreads();
+    const int kp = kp0 + lane;
+    if (kp >= kwords) return;
+    const int g = (kp * 8) / group_size;
+#pragma unroll
+    for (int it = 0; it < 4; it++) {
+        const int cl = warp * 4 + it, col = c0 + cl;
+        if (col >= n_cnt) break;
+        const int o = n_off + col;
+        uint32_t zero = 7u;
+        if (!sym) zero = (__ldg(qzeros + (size_t)g * (n_full >> 3) + (o >> 3)) >> ((o & 7) * 4)) & 15u;
+        const float sc = load_as_f32(scales, scales_dtype, (size_t)g * n_full + o);
+        const float zf = __uint_as_float(0x4B000000u | (zero + 1u)); // 2^23 + zero + 1
+        const uint32_t w = tile[lane][cl];
+        uint32_t o4[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float a = __uint_as_float(0x4B000000u | ((w >> (8 * j)) & 15u)) - zf;
+            const float b = __uint_as_float(0x4B000000u | ((w >> (8 * j + 4)) & 15u)) - zf;
+            o4[j] = pack_bf16x2_rn(__fmul_rn(a, sc), __fmul_rn(b, sc));
+        }
+        *reinterpret_cast<uint4 *>(out + (size_t)col * k + (size_t)kp * 8) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+    }
+}
+
 static int grid_for(size_t work_items, int block = 256)
 {
     size_t blocks = (work_items + block - 1) / block;
@@ -573,6 +616,13 @@ int gptq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, cons
                            __nv_bfloat16 *out, int k, int n_full, int group_size, int bits, int sym, int n_off,
                            int n_cnt, cudaStream_t st)
 {
+    if (bits == 4 && group_size % 8 == 0 && k % 8 == 0 && aligned(out, 16)) {
+        dim3 grid(ceil_div(n_cnt, 32), ceil_div(k / 8, 32));
+        gptq4_slab_bf16_kernel<<<grid, 256, 0, st>>>(qweight, qzeros, scales, scales_dtype, out, k, n_cnt, group_size, sym,
+                                                     n_full, n_off);
+        OXQ_LAUNCH_CHECK("gptq4_slab_bf16_kernel");
+        return OXQ_OK;
+    }
     gptq_dequant_kernel<__nv_bfloat16><<<grid_for((size_t)n_cnt * k), 256, 0, st>>>(
         qweight, qzeros, scales, scales_dtype, out, k, n_cnt, group_size, bits, sym, n_full, n_off);
     OXQ_LAUNCH_CHECK("gptq_dequant_kernel");
@@ -692,6 +742,9 @@ OXQ_EXPORT int oxq_gptq_dequant(const uint32_t *qweight, const uint32_t *qzeros,
     OXQ_REQUIRE(k % pf == 0 && k % group_size == 0, OXQ_ERR_BAD_SHAPE,
                 "GPTQ in_features %d not divisible by pack_factor %d / group size %d", k, pf, group_size);
     const int use_sym = (sym != 0 || qzeros == nullptr) ? 1 : 0;
+    if (out_dtype == OXQ_BF16) // same bits; 4-bit takes the fast producer of the tensor-core path
+        return gptq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, (__nv_bfloat16 *)w_out, k, n, group_size, bits,
+                                      use_sym, 0, n, (cudaStream_t)stream);
     DISPATCH_OUT(out_dtype, gptq_dequant_kernel<OutT><<<grid_for((size_t)n * k), 256, 0, (cudaStream_t)stream>>>(
                                 qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size, bits, use_sym, n, 0));
     OXQ_LAUNCH_CHECK("gptq_dequant_kernel");

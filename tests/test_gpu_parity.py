@@ -360,3 +360,16 @@ def test_q4k_gemv_tuned_kernel_ragged(cuda, n, k, m):
     ref = oracle.linear(x, oracle.gguf_dequant(F.GGML_Q4_K, data, n, k))
     y = L.QLinear(F.GGML_Q4_K, dev(data), n, k).forward(dev(x, torch.bfloat16))
     assert_matmul_close(y, ref, f"q4k n={n} k={k} m={m}")
+
+
+@pytest.mark.parametrize("k,n,g,sym", [(320, 72, 40, False), (512, 200, 128, True), (2048, 96, 64, False)])
+def test_gptq4_slab_producer_ragged_shapes_bit_exact(cuda, k, n, g, sym):
+    # bf16 output takes the transposing 4-bit producer: word rows and columns that do not fill its 32 x 32 tile
+    rng = np.random.default_rng(k + n)
+    iw = rng.integers(0, 16, size=(k, n), dtype=np.uint32)
+    iz = rng.integers(0, 16, size=(k // g, n), dtype=np.uint32)
+    sc = (np.abs(rng.standard_normal((k // g, n))) * 0.01 + 1e-3).astype(np.float16)
+    qw, qz = F.pack_gptq_qweight(iw, 4), F.pack_gptq_qzeros(iz, 4)
+    ref = oracle.gptq_dequant(qw, None if sym else qz, sc, 4, sym)
+    raw = L.QuantWeight.new_gptq(4, sym, words(qw), None if sym else words(qz), dev(sc))
+    assert np.array_equal(bits(L.dequantize_gptq(raw, torch.bfloat16)), oracle.to_bf16_bits(ref))
