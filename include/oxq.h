@@ -38,7 +38,10 @@ typedef enum {
 typedef enum { OXQ_F32 = 0, OXQ_F16 = 1, OXQ_BF16 = 2 } oxq_dtype;
 
 /* GGML block types, numbered as in GGUF files (candle GgmlDType; linear.rs:199-211). */
-typedef enum { OXQ_GGML_Q4_0 = 2, OXQ_GGML_Q8_0 = 8, OXQ_GGML_Q4_K = 12, OXQ_GGML_Q6_K = 14 } oxq_ggml_type;
+typedef enum {
+    OXQ_GGML_Q4_0 = 2, OXQ_GGML_Q4_1 = 3, OXQ_GGML_Q5_0 = 6, OXQ_GGML_Q5_1 = 7, OXQ_GGML_Q8_0 = 8,
+    OXQ_GGML_Q4_K = 12, OXQ_GGML_Q5_K = 13, OXQ_GGML_Q6_K = 14
+} oxq_ggml_type;
 
 const char *oxq_status_string(int status);
 /* Message of the last failing call on this thread ("" if none). */
@@ -87,7 +90,8 @@ int oxq_gptq_dequant(const uint32_t *qweight, const uint32_t *qzeros, const void
  * (metal_ops.rs:5228-5241, linear.rs:220-236). */
 
 /* QTensor::dequantize as restated by the reference's per-element strips
- * (quant_kernels.metal:2342-2384,2438-2482,2518-2554), dense [n, k], bit-exact. */
+ * (quant_kernels.metal:2342-2384,2438-2482,2518-2554; Q5_0/Q4_1/Q5_1: 2315-2341,2386-2437; Q5_K: block
+ * layout 1438-1445), dense [n, k], bit-exact. Types: Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q4_K, Q5_K, Q6_K. */
 int oxq_gguf_dequant(int ggml_type, const void *blocks, void *w_out, int out_dtype, int n, int k, void *stream);
 
 /* QLinear::forward (linear.rs:324-393) / gguf_quant_matmul (metal_ops.rs:5819):

@@ -275,7 +275,7 @@ ORC_API int orc_mxfp4_dequant_f32(const uint8_t *blocks, const uint8_t *scales, 
 /* ------------------------------------------------------------------ GGUF */
 
 /* GGML type ids as stored in GGUF files. */
-enum { ORC_Q4_0 = 2, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q6_K = 14 };
+enum { ORC_Q4_0 = 2, ORC_Q4_1 = 3, ORC_Q5_0 = 6, ORC_Q5_1 = 7, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q5_K = 13, ORC_Q6_K = 14 };
 
 static inline uint16_t ld16(const uint8_t *p) { return (uint16_t)(p[0] | (p[1] << 8)); }
 
@@ -296,6 +296,7 @@ static inline void q4k_scale_min(int j, const uint8_t *q, uint32_t *d, uint32_t 
  * into one fused multiply-add. */
 static inline float mul_rn(float a, float b) { volatile float r = a * b; return r; }
 static inline float sub_rn(float a, float b) { volatile float r = a - b; return r; }
+static inline float add_rn(float a, float b) { volatile float r = a + b; return r; }
 
 /*
  * Per-element GGUF block dequantization to [rows, cols] f32. The block
@@ -314,6 +315,10 @@ ORC_API int orc_gguf_dequant_f32(int ggml_type, const uint8_t *data, int64_t row
     case ORC_Q8_0: bel = 32; bby = 34; break;
     case ORC_Q4_K: bel = 256; bby = 144; break;
     case ORC_Q6_K: bel = 256; bby = 210; break;
+    case ORC_Q4_1: bel = 32; bby = 20; break;
+    case ORC_Q5_0: bel = 32; bby = 22; break;
+    case ORC_Q5_1: bel = 32; bby = 24; break;
+    case ORC_Q5_K: bel = 256; bby = 176; break;
     default: return -3;
     }
     if (cols % bel != 0) return -1;
@@ -346,6 +351,43 @@ ORC_API int orc_gguf_dequant_f32(int ggml_type, const uint8_t *data, int64_t row
                     int iq = sub / 2, lo = sub % 2;
                     uint32_t nib = lo == 0 ? (qs[iq * 32 + el] & 0x0Fu) : (uint32_t)(qs[iq * 32 + el] >> 4);
                     o[j] = sub_rn(mul_rn(sc_v, (float)nib), m_v);
+                }
+            } else if (ggml_type == ORC_Q4_1) {
+                /* {f16 d; f16 m; u8 qs[16]}: q * d + m (quant_kernels.metal:2386-2408) */
+                float d = f16_to_f32(ld16(blk)), mn = f16_to_f32(ld16(blk + 2));
+                const uint8_t *qs = blk + 4;
+                for (int j = 0; j < 32; j++) {
+                    int hi = j / 16, jj = j % 16;
+                    uint32_t q = hi == 0 ? (qs[jj] & 0x0Fu) : (uint32_t)(qs[jj] >> 4);
+                    o[j] = add_rn(mul_rn((float)q, d), mn);
+                }
+            } else if (ggml_type == ORC_Q5_0 || ggml_type == ORC_Q5_1) {
+                /* {f16 d; [f16 m;] u8 qh[4]; u8 qs[16]}: fifth bit of element j is bit j of qh
+                 * (quant_kernels.metal:2315-2341, 2410-2437): (q - 16) * d, or q * d + m */
+                const int with_min = ggml_type == ORC_Q5_1;
+                float d = f16_to_f32(ld16(blk)), mn = with_min ? f16_to_f32(ld16(blk + 2)) : 0.0f;
+                const uint8_t *qhb = blk + (with_min ? 4 : 2), *qs = qhb + 4;
+                uint32_t qh = (uint32_t)qhb[0] | ((uint32_t)qhb[1] << 8) | ((uint32_t)qhb[2] << 16) | ((uint32_t)qhb[3] << 24);
+                for (int j = 0; j < 32; j++) {
+                    int hi = j / 16, jj = j % 16;
+                    uint32_t xh = ((qh >> (jj + hi * 16)) & 1u) << 4;
+                    uint32_t q = (hi == 0 ? (qs[jj] & 0x0Fu) : (uint32_t)(qs[jj] >> 4)) | xh;
+                    o[j] = with_min ? add_rn(mul_rn((float)q, d), mn) : mul_rn((float)((int)q - 16), d);
+                }
+            } else if (ggml_type == ORC_Q5_K) {
+                /* {f16 d, dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]} (block_q5_K, quant_kernels.metal:1438-1445):
+                 * Q4_K with a fifth bit: sub-block j takes bit j of qh[el]; (d*sc)*q - dmin*mn */
+                float d = f16_to_f32(ld16(blk)), dmin = f16_to_f32(ld16(blk + 2));
+                const uint8_t *sc = blk + 4, *qh = blk + 16, *qs = blk + 48;
+                for (int j = 0; j < 256; j++) {
+                    int sub = j / 32, el = j % 32;
+                    uint32_t scb, mb;
+                    q4k_scale_min(sub, sc, &scb, &mb);
+                    float sc_v = mul_rn(d, (float)scb), m_v = mul_rn(dmin, (float)mb);
+                    int iq = sub / 2, lo = sub % 2;
+                    uint32_t nib = lo == 0 ? (qs[iq * 32 + el] & 0x0Fu) : (uint32_t)(qs[iq * 32 + el] >> 4);
+                    uint32_t q = nib | (((uint32_t)(qh[el] >> sub) & 1u) << 4);
+                    o[j] = sub_rn(mul_rn(sc_v, (float)q), m_v);
                 }
             } else { /* Q6_K */
                 const uint8_t *ql = blk, *qh = blk + 128;

@@ -642,7 +642,8 @@ int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *
         OXQ_LAUNCH_CHECK("q4k_slab_bf16_kernel");
         return OXQ_OK;
     }
-    if (aligned(b, 2) && aligned(out, 16) && ggml_type != OXQ_GGML_Q4_K) {
+    if (aligned(b, 2) && aligned(out, 16) &&
+        (ggml_type == OXQ_GGML_Q8_0 || ggml_type == OXQ_GGML_Q4_0 || ggml_type == OXQ_GGML_Q6_K)) {
         if (ggml_type == OXQ_GGML_Q8_0) q80_slab_bf16_kernel<<<grid_for(total / 32), 256, 0, st>>>(b, out, total / 32);
         else if (ggml_type == OXQ_GGML_Q4_0) q40_slab_bf16_kernel<<<grid_for(total / 32), 256, 0, st>>>(b, out, total / 32);
         else q6k_slab_bf16_kernel<<<grid_for(total / 16), 256, 0, st>>>(b, out, total / 16);
@@ -650,12 +651,13 @@ int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *
         return OXQ_OK;
     }
     const int grid = grid_for(total);
+#define OXQ_GGUF_CASE(T) case T: gguf_dequant_kernel<T, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
     switch (ggml_type) {
-    case OXQ_GGML_Q4_0: gguf_dequant_kernel<OXQ_GGML_Q4_0, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
-    case OXQ_GGML_Q8_0: gguf_dequant_kernel<OXQ_GGML_Q8_0, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
-    case OXQ_GGML_Q4_K: gguf_dequant_kernel<OXQ_GGML_Q4_K, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
+    OXQ_GGUF_CASE(OXQ_GGML_Q4_0) OXQ_GGUF_CASE(OXQ_GGML_Q8_0) OXQ_GGUF_CASE(OXQ_GGML_Q4_K) OXQ_GGUF_CASE(OXQ_GGML_Q4_1)
+    OXQ_GGUF_CASE(OXQ_GGML_Q5_0) OXQ_GGUF_CASE(OXQ_GGML_Q5_1) OXQ_GGUF_CASE(OXQ_GGML_Q5_K)
     default: gguf_dequant_kernel<OXQ_GGML_Q6_K, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
     }
+#undef OXQ_GGUF_CASE
     OXQ_LAUNCH_CHECK("gguf_dequant_kernel");
     return OXQ_OK;
 }
@@ -768,20 +770,18 @@ OXQ_EXPORT int oxq_gguf_dequant(int ggml_type, const void *blocks, void *w_out, 
     if (out_dtype == OXQ_BF16) // same bits; Q4_K takes the fast producer of the tensor-core path
         return gguf_dequant_rows_bf16(ggml_type, b, (__nv_bfloat16 *)w_out, k, 0, n, st);
     const int grid = grid_for(total);
+#define OXQ_GGUF_CASE(T)                                                                                            \
+    case T:                                                                                                         \
+        DISPATCH_OUT(out_dtype, gguf_dequant_kernel<T, OutT><<<grid, 256, 0, st>>>(b, (OutT *)w_out, total));       \
+        break;
     switch (ggml_type) {
-    case OXQ_GGML_Q4_0:
-        DISPATCH_OUT(out_dtype, gguf_dequant_kernel<OXQ_GGML_Q4_0, OutT><<<grid, 256, 0, st>>>(b, (OutT *)w_out, total));
-        break;
-    case OXQ_GGML_Q8_0:
-        DISPATCH_OUT(out_dtype, gguf_dequant_kernel<OXQ_GGML_Q8_0, OutT><<<grid, 256, 0, st>>>(b, (OutT *)w_out, total));
-        break;
-    case OXQ_GGML_Q4_K:
-        DISPATCH_OUT(out_dtype, gguf_dequant_kernel<OXQ_GGML_Q4_K, OutT><<<grid, 256, 0, st>>>(b, (OutT *)w_out, total));
-        break;
+    OXQ_GGUF_CASE(OXQ_GGML_Q4_0) OXQ_GGUF_CASE(OXQ_GGML_Q8_0) OXQ_GGUF_CASE(OXQ_GGML_Q4_K) OXQ_GGUF_CASE(OXQ_GGML_Q4_1)
+    OXQ_GGUF_CASE(OXQ_GGML_Q5_0) OXQ_GGUF_CASE(OXQ_GGML_Q5_1) OXQ_GGUF_CASE(OXQ_GGML_Q5_K)
     default:
         DISPATCH_OUT(out_dtype, gguf_dequant_kernel<OXQ_GGML_Q6_K, OutT><<<grid, 256, 0, st>>>(b, (OutT *)w_out, total));
         break;
     }
+#undef OXQ_GGUF_CASE
     OXQ_LAUNCH_CHECK("gguf_dequant_kernel");
     return OXQ_OK;
 }

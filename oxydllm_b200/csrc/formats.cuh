@@ -15,6 +15,10 @@ __host__ __device__ inline bool gguf_block_layout(int ggml_type, int &block_elem
     case OXQ_GGML_Q8_0: block_elems = 32; block_bytes = 34; return true;
     case OXQ_GGML_Q4_K: block_elems = 256; block_bytes = 144; return true;
     case OXQ_GGML_Q6_K: block_elems = 256; block_bytes = 210; return true;
+    case OXQ_GGML_Q4_1: block_elems = 32; block_bytes = 20; return true;
+    case OXQ_GGML_Q5_0: block_elems = 32; block_bytes = 22; return true;
+    case OXQ_GGML_Q5_1: block_elems = 32; block_bytes = 24; return true;
+    case OXQ_GGML_Q5_K: block_elems = 256; block_bytes = 176; return true;
     default: return false;
     }
 }
@@ -43,6 +47,10 @@ __device__ __forceinline__ void q4k_scale_min(int j, const uint8_t *q, uint32_t 
 //   Q8_0 {f16 d; i8 qs[32]}: qs[j] * d.
 //   Q4_K {f16 d, dmin; u8 scales[12]; u8 qs[128]}: (d*sc)*nibble - (dmin*mn).
 //   Q6_K {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d}: (d*scale) * (6-bit - 32).
+//   Q4_1 {f16 d, m; u8 qs[16]}: nibble * d + m.
+//   Q5_0 {f16 d; u8 qh[4]; u8 qs[16]}: ((nibble | bit j of qh << 4) - 16) * d.
+//   Q5_1 {f16 d, m; u8 qh[4]; u8 qs[16]}: (nibble | bit j of qh << 4) * d + m.
+//   Q5_K {f16 d, dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]}: Q4_K with bit `sub` of qh[el] as fifth bit.
 template <int TYPE> __device__ __forceinline__ float gguf_decode_elem(const uint8_t *blk, int j)
 {
     if (TYPE == OXQ_GGML_Q4_0) {
@@ -54,6 +62,30 @@ template <int TYPE> __device__ __forceinline__ float gguf_decode_elem(const uint
         float d = half_bits_to_f32((uint16_t)ld_u16(blk));
         int q = (int)(int8_t)blk[2 + j];
         return __fmul_rn((float)q, d);
+    } else if (TYPE == OXQ_GGML_Q4_1) {
+        float d = half_bits_to_f32((uint16_t)ld_u16(blk)), mn = half_bits_to_f32((uint16_t)ld_u16(blk + 2));
+        uint32_t b = blk[4 + (j & 15)];
+        uint32_t q = j < 16 ? (b & 0x0Fu) : (b >> 4);
+        return __fadd_rn(__fmul_rn((float)q, d), mn);
+    } else if (TYPE == OXQ_GGML_Q5_0 || TYPE == OXQ_GGML_Q5_1) {
+        const bool with_min = TYPE == OXQ_GGML_Q5_1;
+        const uint8_t *qhb = blk + (with_min ? 4 : 2);
+        float d = half_bits_to_f32((uint16_t)ld_u16(blk));
+        uint32_t qh = ld_u16(qhb) | (ld_u16(qhb + 2) << 16);
+        uint32_t b = qhb[4 + (j & 15)];
+        uint32_t q = (j < 16 ? (b & 0x0Fu) : (b >> 4)) | (((qh >> j) & 1u) << 4);
+        if (with_min) return __fadd_rn(__fmul_rn((float)q, d), half_bits_to_f32((uint16_t)ld_u16(blk + 2)));
+        return __fmul_rn((float)((int)q - 16), d);
+    } else if (TYPE == OXQ_GGML_Q5_K) {
+        float d = half_bits_to_f32((uint16_t)ld_u16(blk));
+        float dmin = half_bits_to_f32((uint16_t)ld_u16(blk + 2));
+        int sub = j >> 5, el = j & 31;
+        uint32_t sc, mn;
+        q4k_scale_min(sub, blk + 4, sc, mn);
+        float sc_v = __fmul_rn(d, (float)sc), m_v = __fmul_rn(dmin, (float)mn);
+        uint32_t b = blk[48 + (sub >> 1) * 32 + el];
+        uint32_t q = ((sub & 1) ? (b >> 4) : (b & 0x0Fu)) | ((((uint32_t)blk[16 + el] >> sub) & 1u) << 4);
+        return __fsub_rn(__fmul_rn(sc_v, (float)q), m_v);
     } else if (TYPE == OXQ_GGML_Q4_K) {
         float d = half_bits_to_f32((uint16_t)ld_u16(blk));
         float dmin = half_bits_to_f32((uint16_t)ld_u16(blk + 2));

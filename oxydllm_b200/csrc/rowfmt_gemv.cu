@@ -13,7 +13,8 @@
 
 namespace oxq {
 
-enum RowFormat { RF_Q4_0 = 0, RF_Q8_0, RF_Q4_K, RF_Q6_K, RF_FP8, RF_MXFP4 };
+enum RowFormat { RF_Q4_0 = 0, RF_Q8_0, RF_Q4_K, RF_Q6_K, RF_FP8, RF_MXFP4,
+                 RF_GGUF_ELEM = 100 }; // RF_GGUF_ELEM + ggml type: any GGUF type through the per-element decoder
 
 struct RowGemvParams {
     const __nv_bfloat16 *x;
@@ -37,7 +38,14 @@ __device__ __forceinline__ uint32_t ld2x16(const uint8_t *p)
 template <int FMT> __device__ __forceinline__ void decode4(const RowGemvParams &p, int n, int k, float (&out)[4])
 {
     const uint8_t *row = p.data + (size_t)n * p.row_bytes;
-    if (FMT == RF_Q4_0) {
+    if (FMT >= RF_GGUF_ELEM) {
+        constexpr int TYPE = FMT - RF_GGUF_ELEM;
+        int bel = 32, bby = 0;
+        gguf_block_layout(TYPE, bel, bby);
+        const uint8_t *blk = row + (size_t)(k / bel) * bby;
+#pragma unroll
+        for (int u = 0; u < 4; u++) out[u] = gguf_decode_elem<TYPE>(blk, (k % bel) + u);
+    } else if (FMT == RF_Q4_0) {
         const uint8_t *blk = row + (k >> 5) * 18;
         const int j = k & 31;
         const float d = half_bits_to_f32((uint16_t)ld_u16(blk));
@@ -242,6 +250,10 @@ OXQ_EXPORT int oxq_gguf_gemv(int ggml_type, const void *x, int x_dtype, const vo
         if (!(env && env[0] == '0')) return q80_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
     }
     switch (ggml_type) {
+    case OXQ_GGML_Q4_1: return launch_rowfmt<RF_GGUF_ELEM + OXQ_GGML_Q4_1>(p, st);
+    case OXQ_GGML_Q5_0: return launch_rowfmt<RF_GGUF_ELEM + OXQ_GGML_Q5_0>(p, st);
+    case OXQ_GGML_Q5_1: return launch_rowfmt<RF_GGUF_ELEM + OXQ_GGML_Q5_1>(p, st);
+    case OXQ_GGML_Q5_K: return launch_rowfmt<RF_GGUF_ELEM + OXQ_GGML_Q5_K>(p, st);
     case OXQ_GGML_Q4_0: return launch_rowfmt<RF_Q4_0>(p, st);
     case OXQ_GGML_Q8_0: return launch_rowfmt<RF_Q8_0>(p, st);
     case OXQ_GGML_Q4_K: return launch_rowfmt<RF_Q4_K>(p, st);

@@ -28,9 +28,12 @@ AWQ_PACK_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)
 AWQ_PACK_FACTOR = 8
 
 GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 2, 8, 12, 14
+GGML_Q4_1, GGML_Q5_0, GGML_Q5_1, GGML_Q5_K = 3, 6, 7, 13
 #: ggml type id -> (elements per block, bytes per block)
-GGML_BLOCK = {GGML_Q4_0: (32, 18), GGML_Q8_0: (32, 34), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210)}
-GGML_NAME = {GGML_Q4_0: "Q4_0", GGML_Q8_0: "Q8_0", GGML_Q4_K: "Q4_K", GGML_Q6_K: "Q6_K"}
+GGML_BLOCK = {GGML_Q4_0: (32, 18), GGML_Q8_0: (32, 34), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210),
+              GGML_Q4_1: (32, 20), GGML_Q5_0: (32, 22), GGML_Q5_1: (32, 24), GGML_Q5_K: (256, 176)}
+GGML_NAME = {GGML_Q4_0: "Q4_0", GGML_Q8_0: "Q8_0", GGML_Q4_K: "Q4_K", GGML_Q6_K: "Q6_K",
+             GGML_Q4_1: "Q4_1", GGML_Q5_0: "Q5_0", GGML_Q5_1: "Q5_1", GGML_Q5_K: "Q5_K"}
 
 
 # ----------------------------------------------------------------------- AWQ
@@ -323,5 +326,105 @@ def quantize_q6_k(weight: np.ndarray) -> np.ndarray:
     return out.reshape(-1)
 
 
+def _pack5(q: np.ndarray):
+    """5-bit codes [rows, nb, 32] -> (qh u8 [rows, nb, 4], qs u8 [rows, nb, 16]): bit j of qh is the fifth bit of element j."""
+    hi = (q >> 4).astype(np.uint32)
+    qh = (hi << np.arange(32, dtype=np.uint32)).sum(axis=2, dtype=np.uint32)
+    qh4 = np.ascontiguousarray(qh).view(np.uint8).reshape(q.shape[0], q.shape[1], 4)
+    lo = (q & 0xF).astype(np.uint8)
+    return qh4, lo[:, :, :16] | (lo[:, :, 16:] << 4)
+
+
+def quantize_q4_1(weight: np.ndarray) -> np.ndarray:
+    """Q4_1 {f16 d; f16 m; u8 qs[16]}: affine 4-bit per 32 elements, w = q * d + m."""
+    w = np.ascontiguousarray(weight, np.float32)
+    rows, k = w.shape
+    b = w.reshape(rows, k // 32, 32)
+    mn, mx = b.min(axis=2), b.max(axis=2)
+    d, m = _f16((mx - mn) / 15.0), _f16(mn)
+    df, mf = d.astype(np.float32), m.astype(np.float32)
+    q = np.clip(np.round((b - mf[:, :, None]) / np.where(df > 0, df, 1.0)[:, :, None]), 0, 15).astype(np.uint8)
+    out = np.empty((rows, k // 32, 20), np.uint8)
+    out[:, :, 0:2] = d.view(np.uint8).reshape(rows, k // 32, 2)
+    out[:, :, 2:4] = m.view(np.uint8).reshape(rows, k // 32, 2)
+    out[:, :, 4:] = q[:, :, :16] | (q[:, :, 16:] << 4)
+    return out.reshape(-1)
+
+
+def quantize_q5_0(weight: np.ndarray) -> np.ndarray:
+    """Q5_0 {f16 d; u8 qh[4]; u8 qs[16]}: symmetric 5-bit per 32 elements, w = (q - 16) * d."""
+    w = np.ascontiguousarray(weight, np.float32)
+    rows, k = w.shape
+    b = w.reshape(rows, k // 32, 32)
+    idx = np.abs(b).argmax(axis=2)
+    mx = np.take_along_axis(b, idx[:, :, None], axis=2)[:, :, 0]
+    d = _f16(mx / -16.0)
+    df = d.astype(np.float32)
+    inv = np.where(df != 0, 1.0 / np.where(df != 0, df, 1.0), 0.0)
+    q = np.clip(np.floor(b * inv[:, :, None] + 16.5), 0, 31).astype(np.uint8)
+    qh4, qs = _pack5(q)
+    out = np.empty((rows, k // 32, 22), np.uint8)
+    out[:, :, 0:2] = d.view(np.uint8).reshape(rows, k // 32, 2)
+    out[:, :, 2:6] = qh4
+    out[:, :, 6:] = qs
+    return out.reshape(-1)
+
+
+def quantize_q5_1(weight: np.ndarray) -> np.ndarray:
+    """Q5_1 {f16 d; f16 m; u8 qh[4]; u8 qs[16]}: affine 5-bit per 32 elements, w = q * d + m."""
+    w = np.ascontiguousarray(weight, np.float32)
+    rows, k = w.shape
+    b = w.reshape(rows, k // 32, 32)
+    mn, mx = b.min(axis=2), b.max(axis=2)
+    d, m = _f16((mx - mn) / 31.0), _f16(mn)
+    df, mf = d.astype(np.float32), m.astype(np.float32)
+    q = np.clip(np.round((b - mf[:, :, None]) / np.where(df > 0, df, 1.0)[:, :, None]), 0, 31).astype(np.uint8)
+    qh4, qs = _pack5(q)
+    out = np.empty((rows, k // 32, 24), np.uint8)
+    out[:, :, 0:2] = d.view(np.uint8).reshape(rows, k // 32, 2)
+    out[:, :, 2:4] = m.view(np.uint8).reshape(rows, k // 32, 2)
+    out[:, :, 4:8] = qh4
+    out[:, :, 8:] = qs
+    return out.reshape(-1)
+
+
+def quantize_q5_k(weight: np.ndarray) -> np.ndarray:
+    """Own Q5_K encoder: Q4_K's layout with 5-bit codes; bit j of qh[el] is the fifth bit of sub-block j's element el."""
+    w = np.ascontiguousarray(weight, np.float32)
+    rows, k = w.shape
+    nb = k // 256
+    sb = w.reshape(rows, nb, 8, 32)
+    mn = np.minimum(sb.min(axis=3), 0.0)
+    mxv = np.maximum(sb.max(axis=3), 0.0)
+    sub_scale = (mxv - mn) / 31.0
+    sub_min = -mn
+    d = _f16(sub_scale.max(axis=2) / 63.0)
+    dmin = _f16(sub_min.max(axis=2) / 63.0)
+    df, dmf = d.astype(np.float32), dmin.astype(np.float32)
+    sc = np.clip(np.round(sub_scale / np.where(df > 0, df, 1.0)[:, :, None]), 0, 63).astype(np.uint8)
+    mq = np.clip(np.round(sub_min / np.where(dmf > 0, dmf, 1.0)[:, :, None]), 0, 63).astype(np.uint8)
+    eff_s = df[:, :, None] * sc.astype(np.float32)
+    eff_m = dmf[:, :, None] * mq.astype(np.float32)
+    q = np.clip(np.round((sb + eff_m[:, :, :, None]) / np.where(eff_s > 0, eff_s, 1.0)[:, :, :, None]), 0, 31)
+    q = q.astype(np.uint8)
+    out = np.empty((rows, nb, 176), np.uint8)
+    out[:, :, 0:2] = d.view(np.uint8).reshape(rows, nb, 2)
+    out[:, :, 2:4] = dmin.view(np.uint8).reshape(rows, nb, 2)
+    s12 = np.empty((rows, nb, 12), np.uint8)
+    for j in range(4):
+        s12[:, :, j] = sc[:, :, j] | ((sc[:, :, j + 4] >> 4) << 6)
+        s12[:, :, j + 4] = mq[:, :, j] | ((mq[:, :, j + 4] >> 4) << 6)
+        s12[:, :, j + 8] = (sc[:, :, j + 4] & 0xF) | ((mq[:, :, j + 4] & 0xF) << 4)
+    out[:, :, 4:16] = s12
+    qh = np.zeros((rows, nb, 32), np.uint8)
+    for j in range(8):
+        qh |= ((q[:, :, j, :] >> 4) << j).astype(np.uint8)
+    out[:, :, 16:48] = qh
+    lo = (q & 0xF).reshape(rows, nb, 4, 2, 32)
+    out[:, :, 48:] = (lo[:, :, :, 0, :] | (lo[:, :, :, 1, :] << 4)).reshape(rows, nb, 128)
+    return out.reshape(-1)
+
+
 GGML_QUANTIZE = {GGML_Q4_0: quantize_q4_0, GGML_Q8_0: quantize_q8_0, GGML_Q4_K: quantize_q4_k,
-                 GGML_Q6_K: quantize_q6_k}
+                 GGML_Q6_K: quantize_q6_k, GGML_Q4_1: quantize_q4_1, GGML_Q5_0: quantize_q5_0,
+                 GGML_Q5_1: quantize_q5_1, GGML_Q5_K: quantize_q5_k}
