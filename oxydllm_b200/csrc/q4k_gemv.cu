@@ -1,4 +1,4 @@
-// GGUF Q4_K decode GEMV (1 <= m <= 32), tuned variant.
+// GGUF Q4_K and Q5_K decode GEMV (1 <= m <= 32), tuned variant.
 //
 // Q4_K super-block (144 B / 256 weights): f16 d, f16 dmin, 12 bytes of 6-bit sub-block scales and
 // mins, 128 bytes of nibbles; byte t of 32-byte group iq holds element t of sub-block 2*iq (low
@@ -65,13 +65,25 @@ __device__ __forceinline__ float byte_to_f32(uint32_t v, int idx)
 struct Q4kRow {
     uint4 hdr;     // d | dmin << 16, scales[0..3], scales[4..7], scales[8..11]
     uint2 qs[4];   // bytes [8c, 8c+8) of each 32-byte nibble group
+    uint2 qh;      // Q5_K only: bytes [8c, 8c+8) of qh (bit j = fifth bit of sub-block j's element)
 };
 
-__device__ __forceinline__ void q4k_load_row(Q4kRow &r, const uint8_t *blk, int c)
+// FIVE: the Q5_K layout (176 bytes: 32 bytes of fifth bits between the header and the nibbles).
+template <bool FIVE> __device__ __forceinline__ void q4k_load_row(Q4kRow &r, const uint8_t *blk, int c)
 {
     r.hdr = __ldcs(reinterpret_cast<const uint4 *>(blk));
+    constexpr int QS = FIVE ? 48 : 16;
 #pragma unroll
-    for (int iq = 0; iq < 4; iq++) r.qs[iq] = __ldcs(reinterpret_cast<const uint2 *>(blk + 16 + 32 * iq + 8 * c));
+    for (int iq = 0; iq < 4; iq++) r.qs[iq] = __ldcs(reinterpret_cast<const uint2 *>(blk + QS + 32 * iq + 8 * c));
+    if (FIVE) r.qh = __ldcs(reinterpret_cast<const uint2 *>(blk + 16 + 8 * c));
+    else r.qh = make_uint2(0u, 0u);
+}
+
+// (word >> or << so that bit `bit` of bytes 0 and 2 lands on bit `to` of the two halves) & (1 << to in both halves), | base.
+template <int BIT, int TO> __device__ __forceinline__ uint32_t fifth_bit(uint32_t qhw, uint32_t base)
+{
+    const uint32_t sh = BIT >= TO ? (qhw >> (BIT - TO >= 0 ? BIT - TO : 0)) : (qhw << (TO - BIT >= 0 ? TO - BIT : 0));
+    return (sh & (0x00010001u << TO)) | base;
 }
 
 // (d*sc, dmin*mn) of the eight sub-blocks of one row's super-block.
@@ -91,7 +103,7 @@ __device__ __forceinline__ void q4k_scales(const uint4 &hdr, float (&dsc)[8], fl
     }
 }
 
-template <int MT>
+template <int MT, bool FIVE>
 __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4kGemvParams p)
 {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -107,7 +119,8 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
     const int nsb = p.k >> 8;                 // super-blocks per row
     const int sl_sb = nsb / ks, sb_beg = rank * sl_sb, sb_end = sb_beg + sl_sb; // this CTA's slice
     const int kl = sl_sb << 8, k_cta = sb_beg << 8;
-    const size_t row_bytes = (size_t)nsb * 144;
+    constexpr int BLK = FIVE ? 176 : 144;
+    const size_t row_bytes = (size_t)nsb * BLK;
     const int xrow = kl + 32;                 // halves per staged token row: 64 bytes of padding keep the
                                               // 16-byte fragment reads of a quarter warp on distinct banks
     __half *xs = reinterpret_cast<__half *>(smem);
@@ -121,8 +134,8 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
     Q4kRow cur0, cur1;
     int sb = sb_beg + kw;
     if (sb < sb_end) {
-        q4k_load_row(cur0, row0 + (size_t)sb * 144, c);
-        q4k_load_row(cur1, row1 + (size_t)sb * 144, c);
+        q4k_load_row<FIVE>(cur0, row0 + (size_t)sb * BLK, c);
+        q4k_load_row<FIVE>(cur1, row1 + (size_t)sb * BLK, c);
     }
 
     // Stage the slice of x as f16, elements of every group of four stored as [0, 2, 1, 3] (the order in
@@ -171,8 +184,8 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
     for (; sb < sb_end; sb += kwn) {
         Q4kRow nxt0 = cur0, nxt1 = cur1;
         if (sb + kwn < sb_end) { // next super-block on its way while this one is consumed
-            q4k_load_row(nxt0, row0 + (size_t)(sb + kwn) * 144, c);
-            q4k_load_row(nxt1, row1 + (size_t)(sb + kwn) * 144, c);
+            q4k_load_row<FIVE>(nxt0, row0 + (size_t)(sb + kwn) * BLK, c);
+            q4k_load_row<FIVE>(nxt1, row1 + (size_t)(sb + kwn) * BLK, c);
         }
         float dsc0[8], dmn0[8], dsc1[8], dmn1[8];
         q4k_scales(cur0.hdr, dsc0, dmn0);
@@ -194,10 +207,24 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
                     const uint32_t w0 = j ? cur0.qs[iq].y : cur0.qs[iq].x, w1 = j ? cur1.qs[iq].y : cur1.qs[iq].x;
-                    const uint32_t a_lo[4] = {lop3_and_or(w0, mask_lo, magic), lop3_and_or(w1, mask_lo, magic),
-                                              lop3_and_or(w0 >> 8, mask_lo, magic), lop3_and_or(w1 >> 8, mask_lo, magic)};
-                    const uint32_t a_hi[4] = {lop3_and_or(w0, mask_hi, magic), lop3_and_or(w1, mask_hi, magic),
-                                              lop3_and_or(w0 >> 8, mask_hi, magic), lop3_and_or(w1 >> 8, mask_hi, magic)};
+                    uint32_t a_lo[4] = {lop3_and_or(w0, mask_lo, magic), lop3_and_or(w1, mask_lo, magic),
+                                        lop3_and_or(w0 >> 8, mask_lo, magic), lop3_and_or(w1 >> 8, mask_lo, magic)};
+                    uint32_t a_hi[4] = {lop3_and_or(w0, mask_hi, magic), lop3_and_or(w1, mask_hi, magic),
+                                        lop3_and_or(w0 >> 8, mask_hi, magic), lop3_and_or(w1 >> 8, mask_hi, magic)};
+                    if (FIVE) {
+                        // fifth bits of the same four elements: bit 2 iq of qh for the low sub-block (worth 16 ->
+                        // bit 4 of 1024 + q), bit 2 iq + 1 for the high one (worth 16 * 16 -> bit 8 of 1024 + 16 q);
+                        // elements in bytes (0, 2) of the word, then bytes (1, 3)
+                        const uint32_t h0 = j ? cur0.qh.y : cur0.qh.x, h1 = j ? cur1.qh.y : cur1.qh.x;
+                        a_lo[0] = fifth_bit<2 * 0, 4>(h0 >> (2 * iq), a_lo[0]);
+                        a_lo[1] = fifth_bit<2 * 0, 4>(h1 >> (2 * iq), a_lo[1]);
+                        a_lo[2] = fifth_bit<8, 4>(h0 >> (2 * iq), a_lo[2]);
+                        a_lo[3] = fifth_bit<8, 4>(h1 >> (2 * iq), a_lo[3]);
+                        a_hi[0] = fifth_bit<1, 8>(h0 >> (2 * iq), a_hi[0]);
+                        a_hi[1] = fifth_bit<1, 8>(h1 >> (2 * iq), a_hi[1]);
+                        a_hi[2] = fifth_bit<9, 8>(h0 >> (2 * iq), a_hi[2]);
+                        a_hi[3] = fifth_bit<9, 8>(h1 >> (2 * iq), a_hi[3]);
+                    }
                     const uint32_t b_lo[2] = {j ? xl.z : xl.x, j ? xl.w : xl.y};
                     const uint32_t b_hi[2] = {j ? xh.z : xh.x, j ? xh.w : xh.y};
                     mma_f16_16816(acc_lo[mt], a_lo, b_lo);
@@ -256,11 +283,11 @@ static size_t q4k_smem(int mt, int m, int kl, int warps)
     return (size_t)m * (kl + 32) * 2 + (size_t)(kl / 32) * 8 * mt * 4 + (size_t)warps * mt * 4 * 32 * 4 + 16;
 }
 
-template <int MT> static int launch_q4k(const Q4kGemvParams &p, int ks, cudaStream_t st)
+template <int MT, bool FIVE> static int launch_q4k(const Q4kGemvParams &p, int ks, cudaStream_t st)
 {
     const int nw = p.row_tiles * p.k_warps;
     const size_t smem = q4k_smem(MT, p.m < 8 * MT ? p.m : 8 * MT, p.k / ks, nw);
-    auto kern = q4k_gemv_kernel<MT>;
+    auto kern = q4k_gemv_kernel<MT, FIVE>;
     static size_t configured[64] = {};
     int device = 0;
     OXQ_CUDA(cudaGetDevice(&device));
@@ -290,8 +317,9 @@ bool q4k_gemv_supported(int m, int k)
     return m <= 32 && k % 256 == 0 && q4k_smem(m <= 8 ? 1 : 2, m < 16 ? m : 16, k, 8) <= 200 * 1024;
 }
 
+// five_bit: the blocks are Q5_K (same kernel with the fifth bits merged into the f16 operands).
 int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k,
-             int n, cudaStream_t st)
+             int n, cudaStream_t st, bool five_bit)
 {
     Q4kGemvParams p;
     p.x = (const __nv_bfloat16 *)x; p.blocks = (const uint8_t *)blocks; p.bias = bias; p.y = y;
@@ -307,7 +335,8 @@ int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype
     }
     p.row_tiles = nrt; p.k_warps = kw;
     p.token_split = m <= 8 ? 1 : ceil_div(m, 16); // more than 16 tokens: 16 per CTA on neighbouring CTAs
-    return m <= 8 ? launch_q4k<1>(p, ks, st) : launch_q4k<2>(p, ks, st);
+    if (five_bit) return m <= 8 ? launch_q4k<1, true>(p, ks, st) : launch_q4k<2, true>(p, ks, st);
+    return m <= 8 ? launch_q4k<1, false>(p, ks, st) : launch_q4k<2, false>(p, ks, st);
 }
 
 } // namespace oxq

@@ -114,7 +114,7 @@ __device__ __forceinline__ void mma_bf16_row(float (&d)[4], const uint32_t (&a)[
 
 bool q4k_gemv_supported(int m, int k);
 int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k,
-             int n, cudaStream_t st);
+             int n, cudaStream_t st, bool five_bit);
 bool fp8_gemv_fast_supported(int m, int k, int block_in, const void *w);
 int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale_inv, int s_in, int block_out, int block_in,
                   const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, cudaStream_t st);
@@ -233,9 +233,10 @@ OXQ_EXPORT int oxq_gguf_gemv(int ggml_type, const void *x, int x_dtype, const vo
     p.bias_dtype = bias_dtype; p.y_dtype = y_dtype; p.m = m; p.k = k; p.n = n;
     p.row_bytes = (size_t)(k / bel) * bby;
     cudaStream_t st = (cudaStream_t)stream;
-    if (ggml_type == OXQ_GGML_Q4_K && q4k_gemv_supported(m, k)) {
+    if ((ggml_type == OXQ_GGML_Q4_K || ggml_type == OXQ_GGML_Q5_K) && q4k_gemv_supported(m, k)) {
         const char *env = getenv("OXQ_Q4K_FAST"); // bench-harness knob: "0" selects the generic kernel
-        if (!(env && env[0] == '0')) return q4k_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
+        if (!(env && env[0] == '0'))
+            return q4k_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st, ggml_type == OXQ_GGML_Q5_K);
     }
     if (ggml_type == OXQ_GGML_Q4_0 && q40_gemv_supported(m, k, blocks)) {
         const char *env = getenv("OXQ_Q40_FAST"); // bench-harness knob: "0" selects the generic kernel
