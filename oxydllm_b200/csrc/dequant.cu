@@ -403,6 +403,8 @@ mxfp4_slab16_bf16_kernel(const uint8_t *__restrict__ blocks, const uint8_t *__re
 // Q4_K: a thread converts one 32-byte nibble group of a super-block: sub-block 2*iq from the low
 // nibbles and 2*iq+1 from the high ones, 64 weights = 128 contiguous output bytes. The arithmetic
 // is the element-wise kernel's, operation for operation: (d*sc)*q - (dmin*mn), three roundings.
+// FIVE: the Q5_K layout (176 bytes, 32 bytes of fifth bits after the header: bit j of qh[el] belongs to sub-block j).
+template <bool FIVE>
 __global__ void __launch_bounds__(256)
 q4k_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restrict__ out, size_t total_groups)
 {
@@ -410,10 +412,16 @@ q4k_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restri
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t sb = idx >> 2;
         const int iq = (int)(idx & 3);
-        const uint8_t *blk = blocks + sb * 144;
+        const uint8_t *blk = blocks + sb * (FIVE ? 176 : 144);
         const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
-        const uint4 qa = __ldcs(reinterpret_cast<const uint4 *>(blk + 16 + 32 * iq));
-        const uint4 qb = __ldcs(reinterpret_cast<const uint4 *>(blk + 32 + 32 * iq));
+        const uint4 qa = __ldcs(reinterpret_cast<const uint4 *>(blk + (FIVE ? 48 : 16) + 32 * iq));
+        const uint4 qb = __ldcs(reinterpret_cast<const uint4 *>(blk + (FIVE ? 64 : 32) + 32 * iq));
+        uint4 ha = make_uint4(0u, 0u, 0u, 0u), hb = ha;
+        if (FIVE) {
+            ha = __ldg(reinterpret_cast<const uint4 *>(blk + 16));
+            hb = __ldg(reinterpret_cast<const uint4 *>(blk + 32));
+        }
+        const uint32_t qhw[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w}; // byte t = fifth bits of element t
         const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
         const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
         const uint32_t sw[3] = {hdr.y, hdr.z, hdr.w}; // the 12 scale bytes
@@ -441,10 +449,11 @@ q4k_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restri
 #pragma unroll
             for (int wd = 0; wd < 8; wd++) {
                 const uint32_t v = h ? (q[wd] >> 4) : q[wd];
+                const uint32_t hv = FIVE ? ((qhw[wd] >> (2 * iq + h)) & 0x01010101u) << 4 : 0u;
                 float f[4];
 #pragma unroll
                 for (int b = 0; b < 4; b++) {
-                    const float nib = __uint_as_float(0x4B000000u | ((v >> (8 * b)) & 0x0Fu)) - 8388608.0f;
+                    const float nib = __uint_as_float(0x4B000000u | (((v >> (8 * b)) & 0x0Fu) | ((hv >> (8 * b)) & 0x10u))) - 8388608.0f;
                     f[b] = __fsub_rn(__fmul_rn(sc_v[h], nib), m_v[h]);
                 }
                 o[2 * wd] = pack_bf16x2_rn(f[0], f[1]);
@@ -636,9 +645,10 @@ int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *
     gguf_block_layout(ggml_type, bel, bby);
     const uint8_t *b = blocks + (size_t)n_off * (k / bel) * bby;
     const size_t total = (size_t)n_cnt * k;
-    if (ggml_type == OXQ_GGML_Q4_K && aligned(b, 16) && aligned(out, 16)) {
+    if ((ggml_type == OXQ_GGML_Q4_K || ggml_type == OXQ_GGML_Q5_K) && aligned(b, 16) && aligned(out, 16)) {
         const size_t groups = total / 64;
-        q4k_slab_bf16_kernel<<<grid_for(groups), 256, 0, st>>>(b, out, groups);
+        if (ggml_type == OXQ_GGML_Q5_K) q4k_slab_bf16_kernel<true><<<grid_for(groups), 256, 0, st>>>(b, out, groups);
+        else q4k_slab_bf16_kernel<false><<<grid_for(groups), 256, 0, st>>>(b, out, groups);
         OXQ_LAUNCH_CHECK("q4k_slab_bf16_kernel");
         return OXQ_OK;
     }
