@@ -1,5 +1,7 @@
 // GGUF Q4_0 ({f16 d; u8 qs[16]}, 18 bytes per 32 weights: element j < 16 is the low nibble of qs[j],
-// element j >= 16 the high nibble of qs[j - 16]; w = (nibble - 8) * d) decode GEMV (1 <= m <= 32).
+// element j >= 16 the high nibble of qs[j - 16]; w = (nibble - 8) * d) decode GEMV (1 <= m <= 32), and
+// its three siblings: Q4_1 (+ f16 minimum, w = q * d + m), Q5_0 and Q5_1 (+ 32 fifth bits, bit j of qh
+// for element j, merged into the f16 operands; the minimum comes back through the sums of x).
 //
 // Same decomposition as the Q8_0 kernel: warps of a CTA = row tiles x k parts, a thread-block cluster
 // adds further k slices, partial sums meet in (distributed) shared memory and are added in a fixed
@@ -27,7 +29,7 @@ namespace cg = cooperative_groups;
 
 struct Q40GemvParams {
     const __nv_bfloat16 *x;
-    const uint8_t *blocks; // [n][k/32][18]
+    const uint8_t *blocks; // [n][k/32][block bytes]
     const void *bias;
     void *y;
     int bias_dtype, y_dtype;
@@ -51,26 +53,47 @@ __device__ __forceinline__ uint32_t q40_and_or(uint32_t p, uint32_t mask, uint32
     return r;
 }
 
-// One lane's share of one block: the two aligned words around its 4 bytes, and the block's scale.
-struct Q40Piece {
-    uint32_t w0, w1;
-    unsigned short d;
+// The four 32-weight formats this kernel serves: V = 0 Q4_0 {d; qs} 18 B, 1 Q4_1 {d; m; qs} 20 B,
+// 2 Q5_0 {d; qh; qs} 22 B, 3 Q5_1 {d; m; qh; qs} 24 B. w = (q - off) * d (+ m): off = 8, 0, 16, 0.
+template <int V> struct Q40Fmt {
+    static constexpr bool HAS_MIN = V == 1 || V == 3, FIVE = V >= 2;
+    static constexpr int BLK = 18 + 2 * V, QH = HAS_MIN ? 4 : 2, QS = 2 + (HAS_MIN ? 2 : 0) + (FIVE ? 4 : 0);
+    static constexpr float OFF = V == 0 ? 8.0f : V == 2 ? 16.0f : 0.0f;
 };
 
-__device__ __forceinline__ void q40_load(Q40Piece &q, const uint8_t *blk, int c)
+// One lane's share of one block: the two aligned words around its 4 bytes of nibbles, the block's
+// scale (and minimum), and for the 5-bit formats the 32 fifth bits.
+struct Q40Piece {
+    uint32_t w0, w1, qh;
+    unsigned short d, m;
+};
+
+template <int V> __device__ __forceinline__ void q40_load(Q40Piece &q, const uint8_t *blk, int c)
 {
-    const uint8_t *p8 = blk + 2 + 4 * c;
+    using Fm = Q40Fmt<V>;
+    const uint8_t *p8 = blk + Fm::QS + 4 * c;
     const uint32_t *al = reinterpret_cast<const uint32_t *>(reinterpret_cast<uintptr_t>(p8) & ~(uintptr_t)3);
     q.w0 = __ldg(al);
     // A piece that starts on a word boundary needs no second word (and the last block of the weight has
     // none after it); a shifted piece ends 2 bytes into the next word.
     q.w1 = (reinterpret_cast<uintptr_t>(p8) & 3) ? __ldg(al + 1) : 0u;
-    q.d = __ldg(reinterpret_cast<const unsigned short *>(blk));
+    const unsigned short *h = reinterpret_cast<const unsigned short *>(blk);
+    q.d = __ldg(h);
+    q.m = Fm::HAS_MIN ? __ldg(h + 1) : (unsigned short)0;
+    q.qh = Fm::FIVE ? ((uint32_t)__ldg(h + Fm::QH / 2) | ((uint32_t)__ldg(h + Fm::QH / 2 + 1) << 16)) : 0u;
 }
 
-template <int D>
+// Fifth bits of two elements (bits 0 and 2 of e) placed at bit TO of the low and of the high half:
+// (e & 5) * (2^TO + 2^(TO + 14)) puts bit 0 at TO and bit 2 at TO + 16 (the stray copies are masked off).
+template <int TO> __device__ __forceinline__ uint32_t q40_fifth(uint32_t e, uint32_t base)
+{
+    return (((e & 5u) * ((1u << TO) | (1u << (TO + 14)))) & (0x00010001u << TO)) | base;
+}
+
+template <int D, int V>
 __global__ void __launch_bounds__(256, 3) q40_gemv_kernel(const Q40GemvParams p)
 {
+    using Fm = Q40Fmt<V>;
     extern __shared__ __align__(16) unsigned char smem[];
     cg::cluster_group cluster = cg::this_cluster();
     const int nrt = p.row_tiles, ks = (int)gridDim.y, rank = (int)blockIdx.y; // cluster = the y extent of the grid
@@ -90,15 +113,15 @@ __global__ void __launch_bounds__(256, 3) q40_gemv_kernel(const Q40GemvParams p)
     float *zeros = red + blockDim.x * 4; // 16 bytes of zeros: what lanes without a token read as x
 
     const int r0 = min(n0 + g, p.n - 1), r1 = min(n0 + g + 8, p.n - 1); // past-the-end rows re-read the last row
-    const uint8_t *q0 = p.blocks + ((size_t)r0 * nb + b_cta + b_off) * 18;
-    const uint8_t *q1 = p.blocks + ((size_t)r1 * nb + b_cta + b_off) * 18;
+    const uint8_t *q0 = p.blocks + ((size_t)r0 * nb + b_cta + b_off) * Fm::BLK;
+    const uint8_t *q1 = p.blocks + ((size_t)r1 * nb + b_cta + b_off) * Fm::BLK;
 
     Q40Piece buf0[D], buf1[D];
 #pragma unroll
     for (int d = 0; d < D; d++)
         if (d < wb) {
-            q40_load(buf0[d], q0 + 18 * d, c);
-            q40_load(buf1[d], q1 + 18 * d, c);
+            q40_load<V>(buf0[d], q0 + Fm::BLK * d, c);
+            q40_load<V>(buf1[d], q1 + Fm::BLK * d, c);
         }
 
     // Stage the slice of x as f16, every group of four in the order [0, 2, 1, 3], with the sums of the
@@ -147,18 +170,32 @@ __global__ void __launch_bounds__(256, 3) q40_gemv_kernel(const Q40GemvParams p)
             if (b + d < wb) {
                 const Q40Piece p0 = buf0[d], p1 = buf1[d];
                 if (b + D + d < wb) {
-                    q40_load(buf0[d], q0 + 18 * (b + D + d), c);
-                    q40_load(buf1[d], q1 + 18 * (b + D + d), c);
+                    q40_load<V>(buf0[d], q0 + Fm::BLK * (b + D + d), c);
+                    q40_load<V>(buf1[d], q1 + Fm::BLK * (b + D + d), c);
                 }
-                // even blocks of a row start 2 bytes after a word boundary, odd blocks on one
-                const uint32_t sh0 = (uint32_t)(reinterpret_cast<uintptr_t>(q0 + 18 * (b + d) + 2) & 3) * 8;
-                const uint32_t sh1 = (uint32_t)(reinterpret_cast<uintptr_t>(q1 + 18 * (b + d) + 2) & 3) * 8;
+                // with 18- and 22-byte blocks every other block's nibbles start 2 bytes after a word boundary
+                const uint32_t sh0 = (uint32_t)(reinterpret_cast<uintptr_t>(q0 + Fm::BLK * (b + d) + Fm::QS) & 3) * 8;
+                const uint32_t sh1 = (uint32_t)(reinterpret_cast<uintptr_t>(q1 + Fm::BLK * (b + d) + Fm::QS) & 3) * 8;
                 const uint32_t w0 = __funnelshift_r(p0.w0, p0.w1, sh0), w1 = __funnelshift_r(p1.w0, p1.w1, sh1);
                 // byte t of the piece: low nibble = element 4c + t, high nibble = element 16 + 4c + t
-                const uint32_t a_lo[4] = {q40_and_or(w0, mask_lo, magic), q40_and_or(w1, mask_lo, magic),
-                                          q40_and_or(w0 >> 8, mask_lo, magic), q40_and_or(w1 >> 8, mask_lo, magic)};
-                const uint32_t a_hi[4] = {q40_and_or(w0, mask_hi, magic), q40_and_or(w1, mask_hi, magic),
-                                          q40_and_or(w0 >> 8, mask_hi, magic), q40_and_or(w1 >> 8, mask_hi, magic)};
+                uint32_t a_lo[4] = {q40_and_or(w0, mask_lo, magic), q40_and_or(w1, mask_lo, magic),
+                                    q40_and_or(w0 >> 8, mask_lo, magic), q40_and_or(w1 >> 8, mask_lo, magic)};
+                uint32_t a_hi[4] = {q40_and_or(w0, mask_hi, magic), q40_and_or(w1, mask_hi, magic),
+                                    q40_and_or(w0 >> 8, mask_hi, magic), q40_and_or(w1 >> 8, mask_hi, magic)};
+                if (Fm::FIVE) {
+                    // bit j of qh is the fifth bit of element j: this lane's low elements 4c .. 4c+3 and high
+                    // elements 16+4c .. 16+4c+3; worth 16 (bit 4 of 1024 + q) and 16 * 16 (bit 8 of 1024 + 16 q)
+                    const uint32_t l0 = p0.qh >> (4 * c), l1 = p1.qh >> (4 * c);
+                    const uint32_t h0 = p0.qh >> (16 + 4 * c), h1 = p1.qh >> (16 + 4 * c);
+                    a_lo[0] = q40_fifth<4>(l0, a_lo[0]);
+                    a_lo[1] = q40_fifth<4>(l1, a_lo[1]);
+                    a_lo[2] = q40_fifth<4>(l0 >> 1, a_lo[2]);
+                    a_lo[3] = q40_fifth<4>(l1 >> 1, a_lo[3]);
+                    a_hi[0] = q40_fifth<8>(h0, a_hi[0]);
+                    a_hi[1] = q40_fifth<8>(h1, a_hi[1]);
+                    a_hi[2] = q40_fifth<8>(h0 >> 1, a_hi[2]);
+                    a_hi[3] = q40_fifth<8>(h1 >> 1, a_hi[3]);
+                }
                 const uint2 xl = xp[0], xh = xp[xhalf];
                 xp += xstep;
                 const float2 s_lo = *reinterpret_cast<const float2 *>(sxp + (size_t)(b + d) * 16);
@@ -168,11 +205,13 @@ __global__ void __launch_bounds__(256, 3) q40_gemv_kernel(const Q40GemvParams p)
                 q40_mma_f16(acc_lo, a_lo, b_lo);
                 q40_mma_f16(acc_hi, a_hi, b_hi);
                 const float d0 = __half2float(__ushort_as_half(p0.d)), d1 = __half2float(__ushort_as_half(p1.d));
+                const float m0 = __half2float(__ushort_as_half(p0.m)), m1 = __half2float(__ushort_as_half(p1.m));
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const float sl = (e & 1) ? s_lo.y : s_lo.x, sh = (e & 1) ? s_hi.y : s_hi.x;
-                    const float v = fmaf(-1032.0f, sl, acc_lo[e]) + fmaf(0.0625f, acc_hi[e], -72.0f * sh);
+                    const float v = fmaf(-(1024.0f + Fm::OFF), sl, acc_lo[e]) + fmaf(0.0625f, acc_hi[e], -(64.0f + Fm::OFF) * sh);
                     tot[e] = fmaf((e >> 1) ? d1 : d0, v, tot[e]);
+                    if (Fm::HAS_MIN) tot[e] = fmaf((e >> 1) ? m1 : m0, sl + sh, tot[e]);
                 }
             }
         }
@@ -205,11 +244,11 @@ static size_t q40_smem(int m_cta, int kl, int warps)
     return (size_t)m_cta * (kl + 8) * 2 + (size_t)(kl / 32) * 16 * 4 + (size_t)warps * 4 * 32 * 4 + 16;
 }
 
-static int launch_q40(const Q40GemvParams &p, int ks, cudaStream_t st)
+template <int V> static int launch_q40(const Q40GemvParams &p, int ks, cudaStream_t st)
 {
     const int nw = p.row_tiles * p.k_warps;
     const size_t smem = q40_smem(p.m < 8 ? p.m : 8, p.k / ks, nw);
-    auto kern = q40_gemv_kernel<4>;
+    auto kern = q40_gemv_kernel<4, V>;
     static size_t configured[64] = {};
     int device = 0;
     OXQ_CUDA(cudaGetDevice(&device));
@@ -254,8 +293,9 @@ bool q40_gemv_supported(int m, int k, const void *blocks)
            q40_smem(m < 8 ? m : 8, k, 8) <= 160 * 1024;
 }
 
-int q40_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
-             cudaStream_t st)
+// variant: 0 Q4_0, 1 Q4_1, 2 Q5_0, 3 Q5_1.
+int q40_gemv(int variant, const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m,
+             int k, int n, cudaStream_t st)
 {
     Q40GemvParams p;
     p.x = (const __nv_bfloat16 *)x; p.blocks = (const uint8_t *)blocks; p.bias = bias; p.y = y;
@@ -271,7 +311,12 @@ int q40_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype
     }
     p.row_tiles = nrt; p.k_warps = kw;
     p.token_split = ceil_div(m, 8); // 8 tokens per CTA; more on neighbouring CTAs
-    return launch_q40(p, ks, st);
+    switch (variant) {
+    case 1: return launch_q40<1>(p, ks, st);
+    case 2: return launch_q40<2>(p, ks, st);
+    case 3: return launch_q40<3>(p, ks, st);
+    default: return launch_q40<0>(p, ks, st);
+    }
 }
 
 } // namespace oxq

@@ -120,8 +120,8 @@ int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale_inv, int s
                   const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, cudaStream_t st);
 
 bool q40_gemv_supported(int m, int k, const void *blocks);
-int q40_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
-             cudaStream_t st);
+int q40_gemv(int variant, const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m,
+             int k, int n, cudaStream_t st);
 bool q6k_gemv_supported(int m, int k, const void *blocks);
 int q6k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
              cudaStream_t st);
@@ -238,9 +238,11 @@ OXQ_EXPORT int oxq_gguf_gemv(int ggml_type, const void *x, int x_dtype, const vo
         if (!(env && env[0] == '0'))
             return q4k_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st, ggml_type == OXQ_GGML_Q5_K);
     }
-    if (ggml_type == OXQ_GGML_Q4_0 && q40_gemv_supported(m, k, blocks)) {
+    const int legacy = ggml_type == OXQ_GGML_Q4_0 ? 0 : ggml_type == OXQ_GGML_Q4_1 ? 1 : ggml_type == OXQ_GGML_Q5_0 ? 2
+                       : ggml_type == OXQ_GGML_Q5_1 ? 3 : -1;
+    if (legacy >= 0 && q40_gemv_supported(m, k, blocks)) {
         const char *env = getenv("OXQ_Q40_FAST"); // bench-harness knob: "0" selects the generic kernel
-        if (!(env && env[0] == '0')) return q40_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
+        if (!(env && env[0] == '0')) return q40_gemv(legacy, x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
     }
     if (ggml_type == OXQ_GGML_Q6_K && q6k_gemv_supported(m, k, blocks)) {
         const char *env = getenv("OXQ_Q6K_FAST"); // bench-harness knob: "0" selects the generic kernel
