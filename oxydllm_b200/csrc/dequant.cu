@@ -494,20 +494,33 @@ q80_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restri
     }
 }
 
+// V = 0 Q4_0 {d; qs} 18 B, 1 Q4_1 {d; m; qs} 20 B, 2 Q5_0 {d; qh; qs} 22 B, 3 Q5_1 {d; m; qh; qs} 24 B.
+template <int V>
 __global__ void __launch_bounds__(256)
 q40_slab_bf16_kernel(const uint8_t *__restrict__ blocks, __nv_bfloat16 *__restrict__ out, size_t total_blocks)
 {
+    constexpr bool HAS_MIN = V == 1 || V == 3, FIVE = V >= 2;
+    constexpr int BLK = 18 + 2 * V, QH = (HAS_MIN ? 4 : 2) / 2, QS = (2 + (HAS_MIN ? 2 : 0) + (FIVE ? 4 : 0)) / 2; // halfword offsets
+    constexpr int OFF = V == 0 ? 8 : V == 2 ? 16 : 0;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_blocks;
          idx += (size_t)gridDim.x * blockDim.x) {
-        const unsigned short *h = reinterpret_cast<const unsigned short *>(blocks + idx * 18);
+        const unsigned short *h = reinterpret_cast<const unsigned short *>(blocks + idx * BLK);
         const float d = __half2float(__ushort_as_half(__ldg(h)));
+        const float mn = HAS_MIN ? __half2float(__ushort_as_half(__ldg(h + 1))) : 0.0f;
+        const uint32_t qh = FIVE ? ((uint32_t)__ldg(h + QH) | ((uint32_t)__ldg(h + QH + 1) << 16)) : 0u;
+        auto value = [&](int q) -> float {
+            const float v = __fmul_rn(small_int_f32(q - OFF), d);
+            return HAS_MIN ? __fadd_rn(v, mn) : v;
+        };
         uint32_t lo[8], hi[8]; // elements 0..15 (low nibbles) and 16..31 (high nibbles)
 #pragma unroll
         for (int t = 0; t < 8; t++) {
-            const uint32_t two = __ldg(h + 1 + t); // bytes 2t, 2t+1
+            const uint32_t two = __ldg(h + QS + t); // bytes 2t, 2t+1
             const int b0 = (int)(two & 0xFFu), b1 = (int)(two >> 8);
-            lo[t] = pack_bf16x2_rn(__fmul_rn(small_int_f32((b0 & 15) - 8), d), __fmul_rn(small_int_f32((b1 & 15) - 8), d));
-            hi[t] = pack_bf16x2_rn(__fmul_rn(small_int_f32((b0 >> 4) - 8), d), __fmul_rn(small_int_f32((b1 >> 4) - 8), d));
+            const int f0 = (int)((qh >> (2 * t)) & 1u) << 4, f1 = (int)((qh >> (2 * t + 1)) & 1u) << 4;
+            const int g0 = (int)((qh >> (16 + 2 * t)) & 1u) << 4, g1 = (int)((qh >> (17 + 2 * t)) & 1u) << 4;
+            lo[t] = pack_bf16x2_rn(value((b0 & 15) | f0), value((b1 & 15) | f1));
+            hi[t] = pack_bf16x2_rn(value((b0 >> 4) | g0), value((b1 >> 4) | g1));
         }
         uint4 *dst = reinterpret_cast<uint4 *>(out + idx * 32);
         dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
@@ -652,10 +665,13 @@ int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *
         OXQ_LAUNCH_CHECK("q4k_slab_bf16_kernel");
         return OXQ_OK;
     }
-    if (aligned(b, 2) && aligned(out, 16) &&
-        (ggml_type == OXQ_GGML_Q8_0 || ggml_type == OXQ_GGML_Q4_0 || ggml_type == OXQ_GGML_Q6_K)) {
-        if (ggml_type == OXQ_GGML_Q8_0) q80_slab_bf16_kernel<<<grid_for(total / 32), 256, 0, st>>>(b, out, total / 32);
-        else if (ggml_type == OXQ_GGML_Q4_0) q40_slab_bf16_kernel<<<grid_for(total / 32), 256, 0, st>>>(b, out, total / 32);
+    if (aligned(b, 2) && aligned(out, 16) && ggml_type != OXQ_GGML_Q4_K && ggml_type != OXQ_GGML_Q5_K) {
+        const int g32 = grid_for(total / 32);
+        if (ggml_type == OXQ_GGML_Q8_0) q80_slab_bf16_kernel<<<g32, 256, 0, st>>>(b, out, total / 32);
+        else if (ggml_type == OXQ_GGML_Q4_0) q40_slab_bf16_kernel<0><<<g32, 256, 0, st>>>(b, out, total / 32);
+        else if (ggml_type == OXQ_GGML_Q4_1) q40_slab_bf16_kernel<1><<<g32, 256, 0, st>>>(b, out, total / 32);
+        else if (ggml_type == OXQ_GGML_Q5_0) q40_slab_bf16_kernel<2><<<g32, 256, 0, st>>>(b, out, total / 32);
+        else if (ggml_type == OXQ_GGML_Q5_1) q40_slab_bf16_kernel<3><<<g32, 256, 0, st>>>(b, out, total / 32);
         else q6k_slab_bf16_kernel<<<grid_for(total / 16), 256, 0, st>>>(b, out, total / 16);
         OXQ_LAUNCH_CHECK("gguf slab kernel");
         return OXQ_OK;
