@@ -257,7 +257,7 @@ def run_gpu(args):
                 "d2h_bytes_per_step": LAYERS * sum(m * N * 2 for m in M_SWEEP)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                     "kernel": "awq_gemv_group_kernel (m <= 16), awq_gemv_kernel (m = 32)",
+                     "kernel": "awq_gemv_group_kernel (every m of the sweep; m = 32 as four 8-token CTAs per n tile)",
                      "peak_kind": f"{peak_kind} copy bandwidth", "per_m": per_m},
         "clocks": clocks,
     }
