@@ -670,7 +670,7 @@ OXQ_EXPORT int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight,
         // 16 tokens per CTA, k split in 2; more tokens 8 per CTA on neighbouring CTAs, k split in 2.
         int fv = 2, mtc = (m > 8 && m <= 16) ? 2 : 1, r_force = 0, depth = 2, minb = 4;
         bool ok = aligned(scales, 16);
-        if (const char *env = getenv("OXQ_AWQ_GEMV_FAST")) { // bench-harness knob: "0" disables, else "V[,R[,D[,B[,MT]]]]"
+        if (const char *env = tuning_env("OXQ_AWQ_GEMV_FAST")) { // bench-harness knob: "0" disables, else "V[,R[,D[,B[,MT]]]]"
             int ev = 0, er = 0, ed = 0, eb = 0, em = 0;
             const int got = sscanf(env, "%d,%d,%d,%d,%d", &ev, &er, &ed, &eb, &em);
             if (got >= 1 && ev == 0) ok = false;
@@ -711,8 +711,8 @@ OXQ_EXPORT int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight,
     // Enough CTAs for about two per SM; the k split is the cluster size (portable maximum 8).
     const int n_tiles = ceil_div(p.packed_out, 8 * v * NW);
     int ksplit = 1;
-    while (ksplit < 8 && n_tiles * ksplit < 2 * 148 && total_steps / (ksplit * 2) >= 4) ksplit *= 2;
-    if (const char *env = getenv("OXQ_AWQ_GEMV_TUNE")) { // bench-harness knob: "V,KSPLIT"
+    while (ksplit < 8 && n_tiles * ksplit < 2 * sm_count() && total_steps / (ksplit * 2) >= 4) ksplit *= 2;
+    if (const char *env = tuning_env("OXQ_AWQ_GEMV_TUNE")) { // bench-harness knob: "V,KSPLIT"
         int ev = 0, ek = 0;
         if (sscanf(env, "%d,%d", &ev, &ek) == 2) {
             if ((ev == 1 || ev == 2 || ev == 4) && p.packed_out % ev == 0 && 16 * ev * mt <= 64) v = ev;

@@ -605,7 +605,7 @@ gptq4_slab_bf16_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__r
 static int grid_for(size_t work_items, int block = 256)
 {
     size_t blocks = (work_items + block - 1) / block;
-    const size_t cap = 148 * 32; // a few waves of resident CTAs on 148 SMs, then grid-stride
+    const size_t cap = (size_t)sm_count() * 32; // a few waves of resident CTAs, then grid-stride
     return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 

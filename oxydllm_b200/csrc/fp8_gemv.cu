@@ -273,7 +273,7 @@ int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale_inv, int s
     if (m > 16) { nrt = 8; kw = 1; ks = 4; }
     else if (m > 8) { nrt = 8; kw = 1; ks = 2; }
     else if (m > 2) { nrt = 4; kw = 2; ks = 2; }
-    if (const char *env = getenv("OXQ_FP8_GEMV_TUNE")) { // bench-harness knob: "row_tiles,k_warps,cluster,depth[,token tiles per CTA]"
+    if (const char *env = tuning_env("OXQ_FP8_GEMV_TUNE")) { // bench-harness knob: "row_tiles,k_warps,cluster,depth[,token tiles per CTA]"
         int a = 0, b = 0, cc = 0, dd = 0, mm = 0;
         const int got = sscanf(env, "%d,%d,%d,%d,%d", &a, &b, &cc, &dd, &mm);
         if (got >= 4 && a >= 1 && b >= 1 && a * b <= 8 && cc >= 1 && cc <= 8 && (cc & (cc - 1)) == 0 &&

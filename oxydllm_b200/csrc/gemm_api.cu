@@ -33,14 +33,15 @@ static int slab_rows(int n, int k)
 }
 
 // When the weight needs several slabs, make each one a whole number of persistent-grid rounds:
-// tiles_m x (rows / 256) tiles should be a multiple of the SM count (148 = 4 x 37 SMs).
+// tiles_m x (rows / 256) tiles should be a multiple of the SM count.
 static int slab_rows_for_m(int cap_rows, int n, int m)
 {
     if (cap_rows >= n) return n;
     const int tiles_m = (m + 127) / 128;
-    int g = tiles_m, b = 148;
-    while (b) { const int t = g % b; g = b; b = t; } // gcd(tiles_m, 148)
-    const int q = 148 / g * 256;                      // rows per balanced group of n tiles
+    const int sms = sm_count();
+    int g = tiles_m, b = sms;
+    while (b) { const int t = g % b; g = b; b = t; } // gcd(tiles_m, SM count)
+    const int q = sms / g * 256;                      // rows per balanced group of n tiles
     if (q <= cap_rows) return cap_rows / q * q;
     return cap_rows / 256 * 256;
 }
@@ -72,8 +73,7 @@ static int prepare(const char *who, GemmCommon &c, const void *x, int x_dtype, c
     c.slab = reinterpret_cast<__nv_bfloat16 *>(reinterpret_cast<unsigned char *>(workspace) + WS_HEADER);
     c.rows = slab_rows_for_m(slab_rows(n, k), n, m);
     c.st = (cudaStream_t)stream;
-    OXQ_CUDA(cudaMemsetAsync(c.flag, 0, sizeof(int), c.st));
-    return OXQ_OK;
+    return OXQ_OK; // the flag word is sticky: only oxq_gemm_check / oxq_gemm_workspace_init clear it
 }
 
 template <typename Dequant> static int run_slabs(const GemmCommon &c, Dequant dequant)
@@ -105,8 +105,21 @@ OXQ_EXPORT int oxq_gemm_check(const void *workspace, void *stream)
     int flag = 0;
     OXQ_CUDA(cudaMemcpyAsync(&flag, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     OXQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (flag != 0) { // report once, then the workspace is clean again
+        OXQ_CUDA(cudaMemsetAsync(const_cast<void *>(workspace), 0, sizeof(int), (cudaStream_t)stream));
+        OXQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    }
     OXQ_REQUIRE(flag == 0, OXQ_ERR_DEVICE_FLAG,
-                "tensor-core GEMM: bounded wait %d ran out (1 = ring slot, 2 = tile data, 3 = accumulator ready, 4 = accumulator free)", flag);
+                "tensor-core kernel: bounded wait %d ran out (1 = ring slot, 2 = tile data, 3 = accumulator ready, "
+                "4 = accumulator free, 5 = meeting of the fold warps) in a call since the last check", flag);
+    return OXQ_OK;
+}
+
+OXQ_EXPORT int oxq_gemm_workspace_init(void *workspace, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(workspace, OXQ_ERR_NULL, "oxq_gemm_workspace_init: null workspace");
+    OXQ_CUDA(cudaMemsetAsync(workspace, 0, WS_HEADER, (cudaStream_t)stream));
     return OXQ_OK;
 }
 
@@ -315,8 +328,7 @@ OXQ_EXPORT int oxq_awq_gemm_noalloc(const void *x, int x_dtype, const uint32_t *
     c.slab = reinterpret_cast<__nv_bfloat16 *>(scratch + WS_HEADER);
     long long rows = (long long)(NOALLOC_SLAB_BYTES / ((size_t)k * 2)) / 256 * 256;
     c.rows = rows >= n ? n : (int)rows;
-    c.st = (cudaStream_t)stream;
-    OXQ_CUDA(cudaMemsetAsync(c.flag, 0, sizeof(int), c.st)); // the array keeps the previous call's contents
+    c.st = (cudaStream_t)stream; // the slab keeps the previous call's contents and is overwritten; the flag word is sticky
     return run_slabs(c, [&](int n_off, int cnt) {
         return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, n_off, cnt, c.st);
     });

@@ -321,7 +321,6 @@ OXQ_EXPORT int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *r
     __nv_bfloat16 *slab = reinterpret_cast<__nv_bfloat16 *>(ws + L.slab);
     const int pairs = tokens * top_k;
 
-    OXQ_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), st));
     moe_route_kernel<<<ceil_div(tokens * 32, 256), 256, 0, st>>>(router_logits, tokens, num_experts, top_k, norm_topk,
                                                                  top_idx, top_w);
     if (L.decode) {
@@ -347,7 +346,7 @@ OXQ_EXPORT int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *r
     moe_count_kernel<<<n_exp, 256, 0, st>>>(top_idx, pairs, expert_lo, counts);
     moe_plan_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, L.group_experts, offsets, entries, grp_beg);
     moe_scatter_kernel<<<n_exp, 1024, 0, st>>>(top_idx, pairs, expert_lo, offsets, perm, inv);
-    moe_gather_kernel<<<148 * 8, 256, 0, st>>>((const __nv_bfloat16 *)x, perm, offsets + n_exp, top_k, hidden, xs);
+    moe_gather_kernel<<<sm_count() * 8, 256, 0, st>>>((const __nv_bfloat16 *)x, perm, offsets + n_exp, top_k, hidden, xs);
     OXQ_LAUNCH_CHECK("moe routing kernels");
 
     const int a_rows = pairs + 128;
@@ -372,7 +371,7 @@ OXQ_EXPORT int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *r
                           0, limit, flag, st);
         if (rc) return rc;
     }
-    moe_combine_kernel<<<148 * 8, 256, 0, st>>>(xs, top_idx, top_w, inv, tokens, top_k, hidden, expert_lo, expert_hi, out,
+    moe_combine_kernel<<<sm_count() * 8, 256, 0, st>>>(xs, top_idx, top_w, inv, tokens, top_k, hidden, expert_lo, expert_hi, out,
                                                 out_dtype);
     OXQ_LAUNCH_CHECK("moe_combine_kernel");
     return OXQ_OK;

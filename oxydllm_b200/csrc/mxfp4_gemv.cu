@@ -254,7 +254,7 @@ int mxfp4_gemv_fast(const void *x, const uint8_t *blocks, const uint8_t *scales,
     p.bias_dtype = bias_dtype; p.y_dtype = y_dtype; p.m = m; p.k = k; p.n = n;
     int nrt = 2, kw = 4, ks = 1;
     mx4_pick(m, k, nrt, kw, ks);
-    if (const char *env = getenv("OXQ_MXFP4_GEMV_TUNE")) { // bench-harness knob: "row_tiles,k_warps,cluster"
+    if (const char *env = tuning_env("OXQ_MXFP4_GEMV_TUNE")) { // bench-harness knob: "row_tiles,k_warps,cluster"
         int a = 0, b = 0, cc = 0;
         if (sscanf(env, "%d,%d,%d", &a, &b, &cc) == 3 && a >= 1 && b >= 1 && a * b <= 8 && cc >= 1 && cc <= 8 &&
             (cc & (cc - 1)) == 0 && (k / 32) % (b * cc) == 0) {

@@ -5,6 +5,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/oxq.h"
 
@@ -36,6 +37,28 @@ void clear_error();
         if (e__ != cudaSuccess)                                                                     \
             return ::oxq::fail(OXQ_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e__)); \
     } while (0)
+
+// Experiment knobs: environment variables are looked at only in builds made with -DOXQ_TUNING
+// (passed through OXQ_NVCC_FLAGS); the shipped library never reads the environment.
+#ifdef OXQ_TUNING
+inline const char *tuning_env(const char *name) { return getenv(name); }
+#else
+inline const char *tuning_env(const char *) { return nullptr; }
+#endif
+
+// Streaming multiprocessors of the current device (cached per device; 148 on B200).
+inline int sm_count()
+{
+    static int count[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+    if (count[device] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || v <= 0) v = 148;
+        count[device] = v;
+    }
+    return count[device];
+}
 
 inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 inline bool valid_dtype(int d) { return d == OXQ_F32 || d == OXQ_F16 || d == OXQ_BF16; }

@@ -326,7 +326,7 @@ int q4k_gemv(const void *x, const void *blocks, const void *bias, int bias_dtype
     p.bias_dtype = bias_dtype; p.y_dtype = y_dtype; p.m = m; p.k = k; p.n = n;
     // Measured on a 4096 x 4096 layer: one row tile per CTA up to 8 tokens, two (sharing the staged x) above.
     int nrt = m > 8 ? 2 : 1, kw = m > 8 ? 4 : 8, ks = 1;
-    if (const char *env = getenv("OXQ_Q4K_GEMV_TUNE")) { // bench-harness knob: "row_tiles,k_warps,cluster"
+    if (const char *env = tuning_env("OXQ_Q4K_GEMV_TUNE")) { // bench-harness knob: "row_tiles,k_warps,cluster"
         int a = 0, b = 0, cc = 0;
         if (sscanf(env, "%d,%d,%d", &a, &b, &cc) == 3 && a >= 1 && b >= 1 && a * b <= 8 && cc >= 1 && cc <= 8 &&
             (cc & (cc - 1)) == 0 && (k / 256) % cc == 0) {

@@ -234,22 +234,22 @@ OXQ_EXPORT int oxq_gguf_gemv(int ggml_type, const void *x, int x_dtype, const vo
     p.row_bytes = (size_t)(k / bel) * bby;
     cudaStream_t st = (cudaStream_t)stream;
     if ((ggml_type == OXQ_GGML_Q4_K || ggml_type == OXQ_GGML_Q5_K) && q4k_gemv_supported(m, k)) {
-        const char *env = getenv("OXQ_Q4K_FAST"); // bench-harness knob: "0" selects the generic kernel
+        const char *env = tuning_env("OXQ_Q4K_FAST"); // bench-harness knob: "0" selects the generic kernel
         if (!(env && env[0] == '0'))
             return q4k_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st, ggml_type == OXQ_GGML_Q5_K);
     }
     const int legacy = ggml_type == OXQ_GGML_Q4_0 ? 0 : ggml_type == OXQ_GGML_Q4_1 ? 1 : ggml_type == OXQ_GGML_Q5_0 ? 2
                        : ggml_type == OXQ_GGML_Q5_1 ? 3 : -1;
     if (legacy >= 0 && q40_gemv_supported(m, k, blocks)) {
-        const char *env = getenv("OXQ_Q40_FAST"); // bench-harness knob: "0" selects the generic kernel
+        const char *env = tuning_env("OXQ_Q40_FAST"); // bench-harness knob: "0" selects the generic kernel
         if (!(env && env[0] == '0')) return q40_gemv(legacy, x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
     }
     if (ggml_type == OXQ_GGML_Q6_K && q6k_gemv_supported(m, k, blocks)) {
-        const char *env = getenv("OXQ_Q6K_FAST"); // bench-harness knob: "0" selects the generic kernel
+        const char *env = tuning_env("OXQ_Q6K_FAST"); // bench-harness knob: "0" selects the generic kernel
         if (!(env && env[0] == '0')) return q6k_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
     }
     if (ggml_type == OXQ_GGML_Q8_0 && q80_gemv_supported(m, k, blocks)) {
-        const char *env = getenv("OXQ_Q80_FAST"); // bench-harness knob: "0" selects the generic kernel
+        const char *env = tuning_env("OXQ_Q80_FAST"); // bench-harness knob: "0" selects the generic kernel
         if (!(env && env[0] == '0')) return q80_gemv(x, blocks, bias, bias_dtype, y, y_dtype, m, k, n, st);
     }
     switch (ggml_type) {
@@ -286,7 +286,7 @@ OXQ_EXPORT int oxq_fp8_gemv(const void *x, int x_dtype, const uint8_t *weight, c
                     p.block_in);
     }
     if (fp8_gemv_fast_supported(m, k, p.block_in, weight)) {
-        const char *env = getenv("OXQ_FP8_FAST"); // bench-harness knob: "0" selects the generic kernel
+        const char *env = tuning_env("OXQ_FP8_FAST"); // bench-harness knob: "0" selects the generic kernel
         if (!(env && env[0] == '0'))
             return fp8_gemv_fast(x, weight, scale_inv, p.s_in, p.block_out, p.block_in, bias, bias_dtype, y, y_dtype, m, k,
                                  n, (cudaStream_t)stream);
@@ -309,7 +309,7 @@ OXQ_EXPORT int oxq_mxfp4_gemv(const void *x, int x_dtype, const uint8_t *blocks,
     p.bias_dtype = bias_dtype; p.y_dtype = y_dtype; p.m = m; p.k = k; p.n = n;
     p.row_bytes = (size_t)k / 2;
     if (mxfp4_gemv_fast_supported(m, k, blocks, scales)) {
-        const char *env = getenv("OXQ_MXFP4_FAST"); // bench-harness knob: "0" selects the generic kernel
+        const char *env = tuning_env("OXQ_MXFP4_FAST"); // bench-harness knob: "0" selects the generic kernel
         if (!(env && env[0] == '0'))
             return mxfp4_gemv_fast(x, blocks, scales, bias, bias_dtype, y, y_dtype, m, k, n, (cudaStream_t)stream);
     }

@@ -19,7 +19,8 @@ _workspaces: dict = {}
 
 
 def _workspace(nbytes: int, device) -> torch.Tensor:
-    key = torch.device(device).index or 0
+    idx = torch.device(device).index
+    key = torch.cuda.current_device() if idx is None else idx
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
