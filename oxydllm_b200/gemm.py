@@ -22,12 +22,41 @@ def workspace_bytes(n: int, k: int) -> int:
 def workspace(n: int, k: int, device) -> torch.Tensor:
     """A device buffer large enough for ``oxq_*_gemm`` on an ``[n, k]`` weight (grown on demand, reused)."""
     need = workspace_bytes(n, k)
-    key = torch.device(device).index or 0
+    key = _dev_index(device)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < need:
         buf = torch.zeros(need, dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
+
+
+_decode_ws: dict = {}
+
+
+def _dev_index(device) -> int:
+    idx = torch.device(device).index
+    return torch.cuda.current_device() if idx is None else idx
+
+
+def decode_workspace(m: int, k: int, n: int, device) -> torch.Tensor:
+    """Workspace of ``oxq_awq_decode_matmul`` for this device (grown on demand, zero-filled, reused)."""
+    need = int(_lib.load().oxq_decode_workspace_bytes(m, k, n))
+    key = _dev_index(device)
+    buf = _decode_ws.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.zeros(need, dtype=torch.uint8, device=torch.device("cuda", key))
+        _decode_ws[key] = buf
+    return buf
+
+
+def awq_decode_matmul(lin, x2, y):
+    """``y = x2 . deq(W)`` for decode-sized batches on the tensor cores (``oxq_awq_decode_matmul``)."""
+    from .linear import _dt
+    ws = decode_workspace(x2.shape[0], lin.in_features, lin.out_features, x2.device)
+    bp, bd = _bias(lin.bias)
+    _lib.call("oxq_awq_decode_matmul", _p(x2), _dt(x2.dtype), _p(lin.qweight), _p(lin.qzeros), _p(lin.scales),
+              _dt(lin.scales.dtype), bp, bd, _p(y), _dt(y.dtype), x2.shape[0], lin.in_features, lin.out_features,
+              lin.group_size, _p(ws), ws.numel(), _st())
 
 
 def check(ws: torch.Tensor) -> None:
@@ -56,6 +85,19 @@ def awq_matmul(lin, x2, y):
     _lib.call("oxq_awq_gemm", _p(x2), _dt(x2.dtype), _p(lin.qweight), _p(lin.qzeros), _p(lin.scales),
               _dt(lin.scales.dtype), bp, bd, _p(y), _dt(y.dtype), x2.shape[0], lin.in_features, lin.out_features,
               lin.group_size, _p(ws), ws.numel(), _st())
+
+
+def gptq_matmul(raw, x2, y, bias=None):
+    """``y = x2 . deq(W)^T (+ bias)`` for a GPTQ-packed ``QuantWeight`` (4 or 8 bit, ``oxq_gptq_gemm``)."""
+    from .linear import _as_u32_words, _dt
+    k, n, g = raw.in_features(), raw.out_features(), raw.group_size()
+    ws = workspace(n, k, x2.device)
+    qw, sc = _as_u32_words(raw.qweight), raw.scales.contiguous()
+    qz = None if raw.qzeros is None else _as_u32_words(raw.qzeros)
+    sym = raw.qzeros is None or raw.zero_point == "symmetric"
+    bp, bd = _bias(bias)
+    _lib.call("oxq_gptq_gemm", _p(x2), _dt(x2.dtype), _p(qw), _p(qz), _p(sc), _dt(sc.dtype), bp, bd, _p(y), _dt(y.dtype),
+              x2.shape[0], k, n, g, raw.bits, int(sym), _p(ws), ws.numel(), _st())
 
 
 def awq_ffn_gate_up(lin, x2, y, activation: int):
