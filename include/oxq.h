@@ -58,6 +58,24 @@ int oxq_version(void);
 int oxq_awq_dequant(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
                     void *w_out, int out_dtype, int k, int n, int group_size, void *stream);
 
+/* PackedQuantLinear::forward, decode and continuous-batching sizes (linear.rs:450-505: the
+ * w4a16_matmul / batched-GEMV branch, metal_ops.rs:1821-1867,2326): y[m, n] = x[m, k] . deq(W) (+ bias[n])
+ * for 1 <= m <= oxq_decode_max_m() on the tcgen05 tensor cores. The packed words are read once and
+ * become one E4M3 byte per weight in shared memory (a nibble q read as E4M3 is q * 2^-9 exactly); each
+ * bf16 activation is split into three E5M2 values that add up to it exactly; scale and zero point are
+ * applied in f32 once per (out feature, 128-wide k group). Needs n % 32 == 0, k % 128 == 0 and
+ * group_size % 128 == 0 (other shapes: oxq_awq_gemv / oxq_awq_gemm). `workspace`: device memory of
+ * oxq_decode_workspace_bytes(m, k, n) bytes, 256-byte aligned, zero-filled once before its first use
+ * (only the first word, the bounded-wait flag read by oxq_gemm_check, has to start at zero); it
+ * holds the token pieces and the partial sums of out-feature tiles shared by several CTAs, and is
+ * rewritten by every call, so calls sharing it must be stream-ordered. Deterministic. */
+int oxq_decode_max_m(void);
+size_t oxq_decode_workspace_bytes(int m, int k, int n);
+int oxq_awq_decode_matmul(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros,
+                          const void *scales, int scales_dtype, const void *bias, int bias_dtype, void *y,
+                          int y_dtype, int m, int k, int n, int group_size, void *workspace,
+                          size_t workspace_bytes, void *stream);
+
 /* PackedQuantLinear::forward decode branch -> w4a16_matmul (linear.rs:450-480,
  * metal_ops.rs:1821-1867): y[m, n] = x[m, k] . deq(W) (+ bias[n]), 1 <= m <= 32,
  * x bf16, f32 accumulation, y in `y_dtype`. No workspace: the split along k is
@@ -132,13 +150,23 @@ int oxq_mxfp4_gemv(const void *x, int x_dtype, const uint8_t *blocks, const uint
  * cores (tcgen05, TMEM accumulators, TMA-fed operands), bf16 x bf16 -> f32.
  * `workspace` is caller-owned DEVICE memory, 256-byte aligned, of at least
  * oxq_gemm_workspace_bytes(n, k) bytes; its first word is a flag that a
- * kernel sets if one of its bounded waits ran out (see oxq_gemm_check).
- * Calls sharing a workspace must be stream-ordered. */
+ * kernel sets if one of its bounded waits ran out. The flag is sticky: no
+ * call clears it, it keeps the code of the FIRST wait that ran out in any call
+ * on this workspace until oxq_gemm_check reports and clears it. Fresh
+ * workspace memory must start with a zero flag: allocate it zero-filled or
+ * call oxq_gemm_workspace_init once. Calls sharing a workspace must be
+ * stream-ordered. The same holds for the workspaces of
+ * oxq_awq_decode_matmul and oxq_gptoss_moe_forward. */
 
 size_t oxq_gemm_workspace_bytes(int n, int k);
 
-/* Synchronises `stream`, reads the flag word of `workspace` and returns
- * OXQ_ERR_DEVICE_FLAG if a tensor-core kernel gave up on a wait. */
+/* Zeroes the 256-byte header (flag word) of a fresh workspace on `stream`. */
+int oxq_gemm_workspace_init(void *workspace, void *stream);
+
+/* Synchronises `stream`, reads the flag word of `workspace`; if a tensor-core
+ * kernel gave up on a wait in any call since the last check it clears the
+ * flag and returns OXQ_ERR_DEVICE_FLAG (the outputs of those calls are not
+ * to be trusted). */
 int oxq_gemm_check(const void *workspace, void *stream);
 
 /* PackedQuantLinear::forward prefill branch: maybe_mpp_quant_matmul, else
@@ -201,10 +229,13 @@ int oxq_moe_route(const float *router_logits, int tokens, int num_experts, int t
  * library until the process exits. Limits and rules:
  *   - in_features <= oxq_awq_gemm_noalloc_max_k() (16384), otherwise
  *     OXQ_ERR_WORKSPACE is returned and nothing is launched;
- *   - the first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress); make that first call outside any stream capture;
- *   - all calls share the one array: the flag word is cleared by each call,
- *     the slab is overwritten; calls that may overlap on the GPU (different
+ *   - the first call on each device is a set-up step: it looks up the array's
+ *     device address (cudaGetSymbolAddress), which under lazy module loading is
+ *     also where the driver loads the module and reserves the array; make that
+ *     first call outside any stream capture;
+ *   - all calls share the one array: the slab is overwritten by each call, the
+ *     flag word is sticky until oxq_awq_gemm_noalloc_check reads and clears
+ *     it; calls that may overlap on the GPU (different
  *     streams without ordering) race on it and give wrong results;
  *   - it calls no cudaMalloc/cudaFree and no allocating library routine.
  * oxq_awq_gemm_noalloc_check is oxq_gemm_check on that built-in array. */

@@ -21,6 +21,9 @@ SIGNATURES = {
     "oxq_version": [],
     "oxq_awq_dequant": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "oxq_awq_gemv": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
+    "oxq_decode_max_m": [],
+    "oxq_decode_workspace_bytes": [_i, _i, _i],
+    "oxq_awq_decode_matmul": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp],
     "oxq_awq_ffn_gate_up": [_vp, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp, ctypes.c_size_t, _vp],
     "oxq_gptq_dequant": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "oxq_gguf_dequant": [_i, _vp, _vp, _i, _i, _i, _vp],
@@ -31,6 +34,7 @@ SIGNATURES = {
     "oxq_mxfp4_gemv": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "oxq_gemm_workspace_bytes": [_i, _i],
     "oxq_gemm_check": [_vp, _vp],
+    "oxq_gemm_workspace_init": [_vp, _vp],
     "oxq_awq_gemm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp],
     "oxq_gptq_gemm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp],
     "oxq_gguf_gemm": [_i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp],
@@ -45,7 +49,7 @@ SIGNATURES = {
     "oxq_awq_gemm_noalloc_check": [_vp],
 }
 _RESTYPE = {"oxq_status_string": ctypes.c_char_p, "oxq_last_error": ctypes.c_char_p,
-            "oxq_gemm_workspace_bytes": ctypes.c_size_t, "oxq_gptoss_moe_workspace_bytes": ctypes.c_size_t, "oxq_awq_gemm_noalloc_max_k": ctypes.c_size_t}
+            "oxq_gemm_workspace_bytes": ctypes.c_size_t, "oxq_decode_workspace_bytes": ctypes.c_size_t, "oxq_gptoss_moe_workspace_bytes": ctypes.c_size_t, "oxq_awq_gemm_noalloc_max_k": ctypes.c_size_t}
 
 _lib = None
 
