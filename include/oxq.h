@@ -144,6 +144,26 @@ int oxq_mxfp4_dequant(const uint8_t *blocks, const uint8_t *scales, void *w_out,
 int oxq_mxfp4_gemv(const void *x, int x_dtype, const uint8_t *blocks, const uint8_t *scales, const void *bias,
                    int bias_dtype, void *y, int y_dtype, int m, int k, int n, void *stream);
 
+/* ------------------------------------------------------------------ GPTQ / W8A16 decode
+ * PackedQuantLinear::chunked_batch_gemv for the layouts next to 4-bit AWQ (linear.rs:450-480):
+ * gptq_matmul (PackDim::In, bits 4 or 8; metal_ops.rs:1960-2316, quant_kernels.metal:360-545,3501-3648) and
+ * w8a16_matmul (PackDim::Out at 8 bits; metal_ops.rs:1835, quant_kernels.metal:3349-3499,3650-3728).
+ * y[m, n] = x[m, k] . deq(W) (+ bias[n]), 1 <= m <= 32 (tokens are taken up to four per launch), x bf16,
+ * f32 accumulation, on the packed tensors as stored; no workspace; deterministic (fixed-order k split).
+ * GPTQ: qweight u32 [k / pf, n], qzeros u32 [k / g, n / pf] or NULL, w = (q - (zero + 1)) * scale, `sym`
+ * (or NULL qzeros) = the symmetric zero 2^(bits-1) - 1 (awq.rs:561-590).
+ * W8A16: qweight u32 [k, n / 4] (byte c of word j = out column 4 j + c), qzeros u32 [k / g, n / 4],
+ * w = (q - zero) * scale (quant_kernels.metal:1-16,40-48). in_features <= 40960. */
+int oxq_gptq_gemv(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
+                  int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+                  int group_size, int bits, int sym, void *stream);
+int oxq_w8a16_gemv(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
+                   int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+                   int group_size, void *stream);
+/* dequantize_w8 (metal_ops.rs, quant_kernels.metal:335-356): dense [n, k] weight of the 8-bit AWQ layout, bit-exact. */
+int oxq_w8a16_dequant(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                      void *w_out, int out_dtype, int k, int n, int group_size, void *stream);
+
 /* ------------------------------------------------- prefill-sized matmuls
  * m > 32 (any m >= 1 is accepted): weight rows are dequantized in slabs into
  * `workspace` by the bit-exact kernels above and contracted on the tensor
@@ -174,6 +194,11 @@ int oxq_gemm_check(const void *workspace, void *stream);
 int oxq_awq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
                  int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
                  int group_size, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Same branch for the 8-bit AWQ layout (dequantize_w8 + matmul, linear.rs:506-508). */
+int oxq_w8a16_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
+                   int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
+                   int group_size, void *workspace, size_t workspace_bytes, void *stream);
 
 /* Same branch for GPTQ-packed weights (dequantize_gptq_packed + matmul, linear.rs:509-520). */
 int oxq_gptq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,

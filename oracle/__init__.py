@@ -140,6 +140,24 @@ def gptq_dequant(qweight, qzeros, scales, bits: int, sym: bool = False) -> np.nd
     return out
 
 
+def w8a16_dequant(qweight, qzeros, scales) -> np.ndarray:
+    """8-bit AWQ layout ``[in, out / 4]`` (quant_kernels.metal:1-16,40-48) -> dense ``[out, in]`` f32."""
+    qweight = _c(np.asarray(qweight).astype(np.int64) & 0xFFFFFFFF, np.uint32)
+    qzeros = _c(np.asarray(qzeros).astype(np.int64) & 0xFFFFFFFF, np.uint32)
+    scales = _scales_f32(scales)
+    k, packed_out = qweight.shape
+    n = packed_out * 4
+    groups = scales.shape[0]
+    if scales.shape[1] != n or groups == 0 or k % groups or qzeros.shape != (groups, packed_out):
+        raise ValueError("W8A16 shape mismatch")
+    out = np.empty((n, k), np.float32)
+    rc = lib().orc_w8a16_dequant_f32(_p(qweight), _p(qzeros), _p(scales), ctypes.c_int64(k), ctypes.c_int64(n),
+                                     ctypes.c_int64(k // groups), _p(out))
+    if rc:
+        raise ValueError(f"orc_w8a16_dequant_f32 rc={rc}")
+    return out
+
+
 # ----------------------------------------------------------------------- FP8
 def e4m3_decode(b: np.ndarray) -> np.ndarray:
     """Spec decode of E4M3fn bytes (metal_ops.rs:2944-2956)."""

@@ -197,6 +197,28 @@ ORC_API int orc_gptq_dequant_f32(const uint32_t *qweight, const uint32_t *qzeros
     return 0;
 }
 
+/* W8A16: the AWQ layout at 8 bits, as the reference's shader source states it (quant_kernels.metal:1-16:
+ * qweight u32 [in, out / 4], slot c of word j = out column 4 j + c, identity order at 8 bits;
+ * unpack (:40-48); W[o][i] = (q - zero) * scale[group(i)][o]). The reference has no CPU code for it. */
+ORC_API int orc_w8a16_dequant_f32(const uint32_t *qweight, const uint32_t *qzeros, const float *scales,
+                                  int64_t in_features, int64_t out_features, int64_t group_size, float *w_out)
+{
+    if (out_features % 4 != 0 || group_size <= 0 || in_features % group_size != 0) return -1;
+    int64_t packed_out = out_features / 4;
+#pragma omp parallel for schedule(static)
+    for (int64_t o = 0; o < out_features; o++) {
+        uint32_t sh = (uint32_t)((o % 4) * 8);
+        float *row = w_out + o * in_features;
+        for (int64_t i = 0; i < in_features; i++) {
+            int64_t g = i / group_size;
+            int32_t q = (int32_t)((qweight[i * packed_out + o / 4] >> sh) & 0xFFu);
+            int32_t z = (int32_t)((qzeros[g * packed_out + o / 4] >> sh) & 0xFFu);
+            row[i] = (float)(q - z) * scales[g * out_features + o];
+        }
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------- FP8 */
 
 /* One E4M3fn byte per the spec decode the reference pins every encoding

@@ -25,6 +25,10 @@ SIGNATURES = {
     "oxq_decode_workspace_bytes": [_i, _i, _i],
     "oxq_awq_decode_matmul": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp],
     "oxq_awq_ffn_gate_up": [_vp, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp, ctypes.c_size_t, _vp],
+    "oxq_gptq_gemv": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "oxq_w8a16_gemv": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
+    "oxq_w8a16_dequant": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
+    "oxq_w8a16_gemm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp],
     "oxq_gptq_dequant": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "oxq_gguf_dequant": [_i, _vp, _vp, _i, _i, _i, _vp],
     "oxq_gguf_gemv": [_i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],

@@ -74,6 +74,28 @@ gptq_dequant_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__rest
     }
 }
 
+// ---- W8A16: the AWQ layout at 8 bits ------------------------------------------
+// qweight u32 [k, n / 4]: byte c of word j is out column 4 j + c (no interleave); qzeros u32 [k / g, n / 4];
+// w[o][i] = (q - zero) * scale (quant_kernels.metal:1-16,40-48). One thread per output element along k.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+w8a16_dequant_kernel(const uint32_t *__restrict__ qweight, const uint32_t *__restrict__ qzeros,
+                     const void *__restrict__ scales, int scales_dtype, OutT *__restrict__ w_out, int k, int n,
+                     int group_size, int n_full, int n_off)
+{
+    const size_t total = (size_t)n * k;
+    const int packed_out = n_full / 4;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int o = n_off + (int)(idx / k), i = (int)(idx % k);
+        const int g = i / group_size, sh = 8 * (o & 3);
+        const int q = (int)((qweight[(size_t)i * packed_out + (o >> 2)] >> sh) & 0xFFu);
+        const int zero = (int)((qzeros[(size_t)g * packed_out + (o >> 2)] >> sh) & 0xFFu);
+        const float s = load_as_f32(scales, scales_dtype, (size_t)g * n_full + o);
+        w_out[idx] = narrow<OutT>(__fmul_rn((float)(q - zero), s));
+    }
+}
+
 // ---- GGUF ------------------------------------------------------------------
 template <int TYPE, typename OutT>
 __global__ void __launch_bounds__(256)
@@ -651,6 +673,15 @@ int gptq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, cons
     return OXQ_OK;
 }
 
+int w8a16_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                            __nv_bfloat16 *out, int k, int n_full, int group_size, int n_off, int n_cnt, cudaStream_t st)
+{
+    w8a16_dequant_kernel<__nv_bfloat16><<<grid_for((size_t)n_cnt * k), 256, 0, st>>>(
+        qweight, qzeros, scales, scales_dtype, out, k, n_cnt, group_size, n_full, n_off);
+    OXQ_LAUNCH_CHECK("w8a16_dequant_kernel");
+    return OXQ_OK;
+}
+
 int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *out, int k, int n_off, int n_cnt,
                            cudaStream_t st)
 {
@@ -776,6 +807,21 @@ OXQ_EXPORT int oxq_gptq_dequant(const uint32_t *qweight, const uint32_t *qzeros,
     DISPATCH_OUT(out_dtype, gptq_dequant_kernel<OutT><<<grid_for((size_t)n * k), 256, 0, (cudaStream_t)stream>>>(
                                 qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size, bits, use_sym, n, 0));
     OXQ_LAUNCH_CHECK("gptq_dequant_kernel");
+    return OXQ_OK;
+}
+
+OXQ_EXPORT int oxq_w8a16_dequant(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                                 void *w_out, int out_dtype, int k, int n, int group_size, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(qweight && qzeros && scales && w_out, OXQ_ERR_NULL, "oxq_w8a16_dequant: null pointer");
+    OXQ_REQUIRE(valid_dtype(scales_dtype) && valid_dtype(out_dtype), OXQ_ERR_UNSUPPORTED, "oxq_w8a16_dequant: unsupported dtype");
+    OXQ_REQUIRE(k > 0 && n > 0 && group_size > 0, OXQ_ERR_BAD_SHAPE, "oxq_w8a16_dequant: non-positive size");
+    OXQ_REQUIRE(n % 4 == 0, OXQ_ERR_BAD_SHAPE, "W8A16 out_features (%d) not divisible by pack factor 4", n);
+    OXQ_REQUIRE(k % group_size == 0, OXQ_ERR_BAD_SHAPE, "quant in_features (%d) not divisible by group size (%d)", k, group_size);
+    DISPATCH_OUT(out_dtype, w8a16_dequant_kernel<OutT><<<grid_for((size_t)n * k), 256, 0, (cudaStream_t)stream>>>(
+                                qweight, qzeros, scales, scales_dtype, (OutT *)w_out, k, n, group_size, n, 0));
+    OXQ_LAUNCH_CHECK("w8a16_dequant_kernel");
     return OXQ_OK;
 }
 

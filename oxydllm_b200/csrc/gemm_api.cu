@@ -13,6 +13,8 @@ int awq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const
 int gptq_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
                            __nv_bfloat16 *out, int k, int n_full, int group_size, int bits, int sym, int n_off,
                            int n_cnt, cudaStream_t st);
+int w8a16_dequant_rows_bf16(const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype,
+                            __nv_bfloat16 *out, int k, int n_full, int group_size, int n_off, int n_cnt, cudaStream_t st);
 int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *out, int k, int n_off, int n_cnt,
                            cudaStream_t st);
 int fp8_dequant_rows_bf16(const uint8_t *weight, const float *scale_inv, int s_in, int block_out, int block_in,
@@ -161,6 +163,25 @@ OXQ_EXPORT int oxq_gptq_gemm(const void *x, int x_dtype, const uint32_t *qweight
     return run_slabs(c, [&](int n_off, int cnt) {
         return gptq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, bits, use_sym,
                                       n_off, cnt, c.st);
+    });
+}
+
+OXQ_EXPORT int oxq_w8a16_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros,
+                              const void *scales, int scales_dtype, const void *bias, int bias_dtype, void *y,
+                              int y_dtype, int m, int k, int n, int group_size, void *workspace, size_t workspace_bytes,
+                              void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(qweight && qzeros && scales, OXQ_ERR_NULL, "oxq_w8a16_gemm: null pointer");
+    OXQ_REQUIRE(valid_dtype(scales_dtype), OXQ_ERR_UNSUPPORTED, "oxq_w8a16_gemm: unsupported scales dtype");
+    OXQ_REQUIRE(group_size > 0 && n % 4 == 0 && k % group_size == 0, OXQ_ERR_BAD_SHAPE,
+                "oxq_w8a16_gemm: out_features %d must be a multiple of 4 and in_features %d a multiple of the group size %d",
+                n, k, group_size);
+    GemmCommon c;
+    int rc = prepare("oxq_w8a16_gemm", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n, workspace, workspace_bytes, stream);
+    if (rc) return rc;
+    return run_slabs(c, [&](int n_off, int cnt) {
+        return w8a16_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, n_off, cnt, c.st);
     });
 }
 

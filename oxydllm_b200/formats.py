@@ -50,6 +50,17 @@ def pack_awq(values: np.ndarray) -> np.ndarray:
     return word
 
 
+def pack_w8a16(values: np.ndarray) -> np.ndarray:
+    """Pack uint8 values ``[rows, out]`` into the 8-bit AWQ layout ``[rows, out/4]``: byte c of word j is out
+    column ``4 j + c`` (identity order at 8 bits, quant_kernels.metal:1-16)."""
+    values = np.asarray(values)
+    rows, out = values.shape
+    if out % 4:
+        raise ValueError(f"W8A16 out_features ({out}) not divisible by pack factor 4")
+    v = (values.astype(np.uint32) & 0xFF).reshape(rows, out // 4, 4)
+    return v[:, :, 0] | (v[:, :, 1] << np.uint32(8)) | (v[:, :, 2] << np.uint32(16)) | (v[:, :, 3] << np.uint32(24))
+
+
 def unpack_awq(words: np.ndarray) -> np.ndarray:
     """Inverse of :func:`pack_awq`: ``[rows, out/8]`` words -> ``[rows, out]`` uint8."""
     words = np.asarray(words).astype(np.int64).astype(np.uint32) if words.dtype != np.uint32 else words

@@ -87,10 +87,22 @@ def awq_matmul(lin, x2, y):
               lin.group_size, _p(ws), ws.numel(), _st())
 
 
+def w8a16_matmul(lin, x2, y):
+    """``y = x2 . deq(W)^T (+ bias)`` for the 8-bit AWQ layout (``oxq_w8a16_gemm``)."""
+    from .linear import _dt
+    ws = workspace(lin.out_features, lin.in_features, x2.device)
+    bp, bd = _bias(lin.bias)
+    _lib.call("oxq_w8a16_gemm", _p(x2), _dt(x2.dtype), _p(lin.qweight), _p(lin.qzeros), _p(lin.scales),
+              _dt(lin.scales.dtype), bp, bd, _p(y), _dt(y.dtype), x2.shape[0], lin.in_features, lin.out_features,
+              lin.group_size, _p(ws), ws.numel(), _st())
+
+
 def gptq_matmul(raw, x2, y, bias=None):
-    """``y = x2 . deq(W)^T (+ bias)`` for a GPTQ-packed ``QuantWeight`` (4 or 8 bit, ``oxq_gptq_gemm``)."""
+    """``y = x2 . deq(W)^T (+ bias)`` for a GPTQ-packed ``QuantWeight`` or ``PackedQuantLinear`` (4 or 8 bit,
+    ``oxq_gptq_gemm``)."""
     from .linear import _as_u32_words, _dt
-    k, n, g = raw.in_features(), raw.out_features(), raw.group_size()
+    feat = lambda v: v() if callable(v) else v
+    k, n, g = feat(raw.in_features), feat(raw.out_features), feat(raw.group_size)
     ws = workspace(n, k, x2.device)
     qw, sc = _as_u32_words(raw.qweight), raw.scales.contiguous()
     qz = None if raw.qzeros is None else _as_u32_words(raw.qzeros)

@@ -22,6 +22,8 @@ _DT = {torch.float32: _lib.OXQ_F32, torch.float16: _lib.OXQ_F16, torch.bfloat16:
 
 #: Largest m handled by the decode GEMV kernels; larger batches go to the tensor-core GEMM.
 GEMV_MAX_M = 32
+#: The same for the GPTQ and 8-bit GEMVs (one 8-token chunk of the reference's batched GEMV, linear.rs:461-478).
+PACKED_SIMT_GEMV_MAX_M = 8
 
 
 def _dt(t: torch.dtype) -> int:
@@ -179,9 +181,30 @@ def dequantize_gptq(raw: QuantWeight, out_dtype: torch.dtype = torch.float32) ->
     return out
 
 
+def dequantize_w8a16(raw: QuantWeight, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``dequantize_w8`` (metal_ops.rs, quant_kernels.metal:335-356): dense ``[out, in]`` weight of the 8-bit AWQ
+    layout (``qweight [in, out/4]``, byte c of word j = out column ``4 j + c``), bit-exact, on the GPU."""
+    if raw.bits != 8 or raw.pack_dim != "out":
+        raise ValueError(f"dequantize_w8a16: expected 8-bit PackDim::Out, got {raw.bits}-bit {raw.pack_dim}")
+    if raw.qzeros is None:
+        raise ValueError("W8A16 dequantize: qzeros tensor missing")
+    in_f, out_f, g = raw.in_features(), raw.out_features(), raw.group_size()
+    groups = in_f // g
+    if out_f % 4 or tuple(raw.qweight.shape) != (in_f, out_f // 4) or tuple(raw.qzeros.shape) != (groups, out_f // 4):
+        raise ValueError(f"W8A16 qweight/qzeros shapes {list(raw.qweight.shape)}/{list(raw.qzeros.shape)} do not match "
+                         f"[{in_f}, {out_f // 4}] / [{groups}, {out_f // 4}]")
+    _require_cuda(raw.qweight, raw.qzeros, raw.scales)
+    qw, qz, sc = _as_u32_words(raw.qweight), _as_u32_words(raw.qzeros), raw.scales.contiguous()
+    out = torch.empty((out_f, in_f), dtype=out_dtype, device=qw.device)
+    _lib.call("oxq_w8a16_dequant", _p(qw), _p(qz), _p(sc), _dt(sc.dtype), _p(out), _dt(out_dtype), in_f, out_f, g, _stream())
+    return out
+
+
 def dequantize_quant(raw: QuantWeight, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
     """``dequantize_quant`` (awq.rs:592-597)."""
-    return dequantize_awq(raw, out_dtype) if raw.pack_dim == "out" else dequantize_gptq(raw, out_dtype)
+    if raw.pack_dim == "out":
+        return dequantize_awq(raw, out_dtype) if raw.bits == 4 else dequantize_w8a16(raw, out_dtype)
+    return dequantize_gptq(raw, out_dtype)
 
 
 # ---------------------------------------------------------------------------
@@ -196,25 +219,38 @@ class Linear:
 
 
 class PackedQuantLinear:
-    """Resident packed-int linear layer (``PackedQuantLinear``, linear.rs:403-534), AWQ 4-bit.
+    """Resident packed-int linear layer (``PackedQuantLinear``, linear.rs:403-534): AWQ (``pack_dim="out"``) or
+    GPTQ (``pack_dim="in"``), 4 or 8 bits, on the packed tensors as stored.
 
-    ``forward`` keeps the reference's dispatch shape: decode-sized batches go to
-    the GEMV kernel, larger ones to the tensor-core GEMM (linear.rs:494-524).
-    Scales stay in their stored dtype and are widened to f32 inside the kernels
-    (the CPU convention, awq.rs:362-367); pass ``scales.to(dtype)`` yourself to
-    get the Metal resident convention (linear.rs:437).
+    ``forward`` keeps the reference's dispatch shape: decode-sized batches go to the GEMV kernels (the
+    reference chunks them by 8 tokens, linear.rs:450-480), larger ones to the tensor-core GEMM on slabs of the
+    dequantized weight (linear.rs:494-524). Scales stay in their stored dtype and are widened to f32 inside
+    the kernels (the CPU convention, awq.rs:362-367); pass ``scales.to(dtype)`` yourself to get the Metal
+    resident convention (linear.rs:437).
     """
 
     def __init__(self, raw: QuantWeight, bias: Optional[torch.Tensor] = None, dtype: torch.dtype = torch.bfloat16):
         if raw.bits not in (4, 8):
             raise ValueError(f"PackedQuantLinear: bits must be 4 or 8, got {raw.bits}")
-        if raw.qzeros is None:
+        self.bits, self.pack_dim = raw.bits, raw.pack_dim
+        self.sym = raw.pack_dim == "in" and (raw.qzeros is None or raw.zero_point == "symmetric")
+        if raw.qzeros is None and not self.sym:
             raise ValueError("PackedQuantLinear: qzeros missing")
-        if raw.pack_dim != "out" or raw.bits != 4:
-            raise NotImplementedError("PackedQuantLinear: only AWQ 4-bit is resident on this build")
-        self.in_features, self.out_features, self.group_size = _check_awq_shapes(raw)
+        pf = raw.pack_factor()
+        if raw.pack_dim == "out" and raw.bits == 4:
+            self.in_features, self.out_features, self.group_size = _check_awq_shapes(raw)
+        else:
+            self.in_features, self.out_features, self.group_size = raw.in_features(), raw.out_features(), raw.group_size()
+            groups = self.in_features // self.group_size
+            want_qw = (self.in_features, self.out_features // pf) if raw.pack_dim == "out" else (self.in_features // pf, self.out_features)
+            if self.out_features % pf or tuple(raw.qweight.shape) != want_qw:
+                raise ValueError(f"PackedQuantLinear: qweight shape {list(raw.qweight.shape)} != {list(want_qw)}")
+            if raw.qzeros is not None and tuple(raw.qzeros.shape) != (groups, self.out_features // pf):
+                raise ValueError(f"PackedQuantLinear: qzeros shape {list(raw.qzeros.shape)} != [{groups}, {self.out_features // pf}]")
+            if tuple(raw.scales.shape) != (groups, self.out_features):
+                raise ValueError(f"PackedQuantLinear: scales out_features {raw.scales.shape[1]} != derived {self.out_features}")
         self.qweight = _as_u32_words(raw.qweight)
-        self.qzeros = _as_u32_words(raw.qzeros)
+        self.qzeros = None if raw.qzeros is None else _as_u32_words(raw.qzeros)
         self.scales = raw.scales.contiguous()
         self.bias = None if bias is None else bias.contiguous()
         self.dtype = dtype
@@ -223,6 +259,11 @@ class PackedQuantLinear:
         b = self.bias
         self._const = (_p(self.qweight), _p(self.qzeros), _p(self.scales), _dt(self.scales.dtype), _p(b),
                        _dt(b.dtype) if b is not None else 0)
+
+    def gemv_max_m(self) -> int:
+        """Largest batch the decode kernels take before the tensor-core GEMM is the better tool: 32 for the
+        4-bit AWQ tensor-core GEMV, 8 (one chunk of the reference's batched GEMV) for GPTQ and 8-bit."""
+        return GEMV_MAX_M if (self.pack_dim == "out" and self.bits == 4) else PACKED_SIMT_GEMV_MAX_M
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``out``: optional preallocated contiguous ``[m, out_features]`` result tensor of x's dtype and device."""
@@ -239,17 +280,37 @@ class PackedQuantLinear:
             y = out
         if m == 0:
             return y.reshape(*lead, self.out_features)
-        if m <= GEMV_MAX_M:
+        if m <= self.gemv_max_m():
             self._gemv(x2, y, m)
         else:
             from . import gemm
-            gemm.awq_matmul(self, x2, y)
+            if self.pack_dim == "out" and self.bits == 4:
+                gemm.awq_matmul(self, x2, y)
+            elif self.pack_dim == "out":
+                gemm.w8a16_matmul(self, x2, y)
+            else:
+                gemm.gptq_matmul(self, x2, y, self.bias)
         return y.reshape(*lead, self.out_features)
 
     def _gemv(self, x2, y, m):
         qw, qz, sc, sc_dt, b, b_dt = self._const
-        _lib.call("oxq_awq_gemv", _p(x2), _dt(x2.dtype), qw, qz, sc, sc_dt, b, b_dt, _p(y), _dt(y.dtype), m,
-                  self.in_features, self.out_features, self.group_size, _stream())
+        if self.pack_dim == "out" and self.bits == 4:
+            _lib.call("oxq_awq_gemv", _p(x2), _dt(x2.dtype), qw, qz, sc, sc_dt, b, b_dt, _p(y), _dt(y.dtype), m,
+                      self.in_features, self.out_features, self.group_size, _stream())
+        elif self.pack_dim == "out":
+            _lib.call("oxq_w8a16_gemv", _p(x2), _dt(x2.dtype), qw, qz, sc, sc_dt, b, b_dt, _p(y), _dt(y.dtype), m,
+                      self.in_features, self.out_features, self.group_size, _stream())
+        else:
+            _lib.call("oxq_gptq_gemv", _p(x2), _dt(x2.dtype), qw, qz, sc, sc_dt, b, b_dt, _p(y), _dt(y.dtype), m,
+                      self.in_features, self.out_features, self.group_size, self.bits, int(self.sym), _stream())
+
+    # the attributes gemm.gptq_matmul reads from a QuantWeight
+    def pack_factor(self) -> int:
+        return 32 // self.bits
+
+    @property
+    def zero_point(self) -> str:
+        return "symmetric" if self.sym else ("plus_one" if self.pack_dim == "in" else "signed")
 
 
 ACTIVATIONS = {"silu": 1, "gelu_tanh": 2}
@@ -474,11 +535,9 @@ class AnyLinear:
 
     @classmethod
     def from_quant(cls, raw: QuantWeight, bias=None, device="cuda", dtype=torch.bfloat16):
-        """AWQ stays packed; GPTQ is dequantized at load on the GPU like the reference's loader path
-        (linear.rs:582-601)."""
-        if raw.pack_dim == "out" and raw.bits == 4:
-            return cls(PackedQuantLinear(raw.to(device), bias, dtype))
-        return cls(Linear(dequantize_quant(raw.to(device), dtype), bias))
+        """AWQ and GPTQ, 4 or 8 bits, all stay packed and resident (the reference keeps them packed on Metal,
+        linear.rs:561-580, and dequantizes at load elsewhere, linear.rs:582-601)."""
+        return cls(PackedQuantLinear(raw.to(device), bias, dtype))
 
     @classmethod
     def from_gguf(cls, ggml_type, blocks, out_features, in_features, bias=None, out_dtype=torch.bfloat16):

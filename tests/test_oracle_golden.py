@@ -276,3 +276,19 @@ def test_moe_route_and_dispatch_agree_with_dense_evaluation():
     lo = oracle.gptoss_moe(x, idx, vals, gu_b, gu_s, gu_bias, dn_b, dn_s, dn_bias, hidden, inter, expert_range=(0, 2))
     hi = oracle.gptoss_moe(x, idx, vals, gu_b, gu_s, gu_bias, dn_b, dn_s, dn_bias, hidden, inter, expert_range=(2, 4))
     assert np.abs((lo + hi) - sparse).max() < 1e-5 * max(1.0, np.abs(sparse).max())
+
+
+def test_w8a16_dequant_known_answer():
+    """8-bit AWQ layout (quant_kernels.metal:1-16,40-48): byte c of word j is out column 4 j + c, W = (q - z) * s."""
+    k, n, g = 4, 8, 2
+    iw = (np.arange(k * n, dtype=np.uint32).reshape(k, n) * 7 + 3) % 256
+    iz = np.array([[1, 2, 3, 4, 5, 6, 7, 8], [250, 128, 0, 9, 10, 11, 12, 13]], np.uint32)
+    sc = np.array([[0.5, 0.25, 1.0, 2.0, 0.125, 1.5, 0.75, 3.0], [1.0, 0.5, 2.0, 4.0, 0.25, 3.0, 1.5, 6.0]], np.float16)
+    qw, qz = F.pack_w8a16(iw), F.pack_w8a16(iz)
+    assert qw.shape == (k, n // 4) and int(qw[0, 0]) == (3 | (10 << 8) | (17 << 16) | (24 << 24))
+    got = oracle.w8a16_dequant(qw, qz, sc)
+    want = np.empty((n, k), np.float32)
+    for o in range(n):
+        for i in range(k):
+            want[o, i] = (float(int(iw[i, o]) - int(iz[i // g, o]))) * float(sc[i // g, o])
+    assert np.array_equal(got, want)
