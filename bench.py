@@ -44,8 +44,8 @@ def algo_bytes(m: int) -> int:
 
 BYTES_PER_STEP = LAYERS * sum(algo_bytes(m) for m in M_SWEEP)
 LAUNCHES_PER_STEP = LAYERS * len(M_SWEEP)
-# dram__bytes_read.sum + dram__bytes_write.sum of one m = 1 launch on this layer shape, from the ncu
-# capture summarised in profiles/awq_gemv_c1.md (algorithmic bytes of that launch: algo_bytes(1)).
+# dram__bytes_read.sum + dram__bytes_write.sum of one m = 1 launch of awq_gemv_group_kernel on this layer shape,
+# recorded from an ncu capture (not measured by this script; algorithmic bytes of that launch: algo_bytes(1)).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 30_547_712 + 72_192
 
 
@@ -224,9 +224,9 @@ def run_gpu(args):
         torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
 
-    extras = None
+    extras, sharded = None, None
     if not args.no_extras:
-        extras = run_extras(args, world, rank, layers[0])
+        extras, sharded = run_extras(args, world, rank, layers[0])
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -257,6 +257,7 @@ def run_gpu(args):
                 "d2h_bytes_per_step": LAYERS * sum(m * N * 2 for m in M_SWEEP)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "traffic_source": "recorded ncu capture of one m = 1 launch (dram read + write bytes)",
                      "kernel": "awq_gemv_group_kernel (every m of the sweep; m = 32 as four 8-token CTAs per n tile)",
                      "peak_kind": f"{peak_kind} copy bandwidth", "per_m": per_m},
         "clocks": clocks,
@@ -265,6 +266,8 @@ def run_gpu(args):
         out["cpu_baseline"] = cpu
     if extras is not None:
         out["other_configs"] = extras
+    if sharded:
+        out["sharded"] = sharded
     print(json.dumps(out), flush=True)
 
 
@@ -312,6 +315,7 @@ def run_extras(args, world, rank, c1_layer):
     hbm = float(peaks.get("hbm_gbs", 6650.0))
     tf_burst = float(peaks.get("bf16_tflops", 1590.0))
     out = {}
+    sharded = {}  # legs that split one operator over the ranks (tensor / expert parallel), with parity against one GPU
     dev = lambda a, dt=None: (torch.from_numpy(np.ascontiguousarray(a)).to(dt) if dt else torch.from_numpy(np.ascontiguousarray(a))).cuda()
 
     def graph_us(fn_once, launches, reps=20):
@@ -352,6 +356,46 @@ def run_extras(args, world, rank, c1_layer):
     except Exception as e:  # keep the headline line alive
         out["c0_q4k_gemv_m1"] = {"error": str(e)[:200]}
 
+    # ---- C1 shape beyond the sweep: continuous-batching sizes through the operator (tensor-core GEMM on dequantized slabs
+    #      above 32 tokens), the tcgen05 decode matmul on one-byte weights (opt-in entry point), and the GPTQ 4-bit GEMV
+    try:
+        if "c1x" not in want:
+            raise _NotSelected()
+        lins = [c1_layer] + [L.PackedQuantLinear(L.QuantWeight.new_awq(4, torch.roll(c1_layer.qweight, 64 * (i + 1), 0),
+                                                                       c1_layer.qzeros, c1_layer.scales)) for i in range(5)]
+        res = {}
+        for m in (64, 128, 256):
+            x = dev(synth.activations(m, K, seed=m), torch.bfloat16)
+            y = torch.empty((m, N), dtype=torch.bfloat16, device="cuda")
+            us = graph_us(lambda: [lin.forward(x, out=y) for lin in lins], len(lins), reps=10)
+            res[f"operator_m{m}"] = {"us_per_call": round(us, 2), "gbs": round(algo_bytes(m) / us / 1e3, 1),
+                                     "frac_of_hbm_peak": round(algo_bytes(m) / us / 1e3 / hbm, 4),
+                                     "tflops": round(2.0 * m * N * K / us / 1e6, 1)}
+        for m in (1, 8, 16, 32):
+            x = dev(synth.activations(m, K, seed=m), torch.bfloat16)
+            y = torch.empty((m, N), dtype=torch.bfloat16, device="cuda")
+            us = graph_us(lambda: [gemm.awq_decode_matmul(lin, x, y) for lin in lins], len(lins), reps=10)
+            res[f"tcgen05_decode_matmul_m{m}"] = {"us_per_call": round(us, 2), "gbs": round(algo_bytes(m) / us / 1e3, 1),
+                                                  "frac_of_hbm_peak": round(algo_bytes(m) / us / 1e3 / hbm, 4)}
+        gemm.check(gemm.decode_workspace(32, K, N, "cuda"))
+        rng = np.random.default_rng(11)
+        glins = []
+        for i in range(4):
+            gq = dev(rng.integers(0, 2 ** 32, size=(K // 8, N), dtype=np.uint64).astype(np.uint32).view(np.int32))
+            gz = dev(rng.integers(0, 2 ** 32, size=(K // G, N // 8), dtype=np.uint64).astype(np.uint32).view(np.int32))
+            glins.append(L.PackedQuantLinear(L.QuantWeight.new_gptq(4, False, gq, gz, c1_layer.scales)))
+        for m in (1, 8):
+            x = dev(synth.activations(m, K, seed=m), torch.bfloat16)
+            us = graph_us(lambda: [lin.forward(x) for lin in glins], len(glins), reps=10)
+            res[f"gptq4_gemv_m{m}"] = {"us_per_call": round(us, 2), "gbs": round(algo_bytes(m) / us / 1e3, 1),
+                                       "frac_of_hbm_peak": round(algo_bytes(m) / us / 1e3 / hbm, 4)}
+        out["c1_shape_other_batches_and_layouts"] = res
+        del lins, glins
+    except _NotSelected:
+        pass
+    except Exception as e:
+        out["c1_shape_other_batches_and_layouts"] = {"error": str(e)[:200]}
+
     # ---- C2: AWQ prefill GEMM M = 2048, K = 4096, N in {4096, 14336}
     try:
         if "c2" not in want:
@@ -383,17 +427,40 @@ def run_extras(args, world, rank, c1_layer):
         res["ffn_gate_up_silu_i14336"] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_bf16_burst_peak": round(tf / tf_burst, 4)}
         del glin, ffn, fused
         gemm.check(gemm.workspace(1, 8, "cuda"))
-        if world > 1:  # tensor-parallel column split of N = 14336 + all-gather
-            n = 14336
-            a, b_ = parallel.column_shard(n, world, rank)
-            qw, qz, sc = parallel.ColumnParallelLinear.slice_awq(c1_layer.qweight, c1_layer.qzeros, c1_layer.scales, a, b_)
-            shard = L.PackedQuantLinear(L.QuantWeight.new_awq(4, qw, qz, sc))
-            tp = parallel.ColumnParallelLinear(shard.forward, n, chunks=1)  # one call: the shard is dequantized once
-            for _ in range(3):
-                tp.forward(x)
-            ms = _timed_ms(torch, dist, world, lambda: tp.forward(x), 10)
-            tf = 2.0 * m * n * K / ms / 1e9
-            res[f"n{n}_tp{world}_allgather"] = {"ms": round(ms, 4), "tflops_whole_job": round(tf, 1)}
+        # lm_head-class width (src/common/block.rs:598): the C1 layer's packed columns tiled to N = 128256 (throughput is
+        # data-independent; parity at this width is covered by the tests)
+        n_big = 128256
+        reps = -(-n_big // N)
+        big = [torch.cat([t] * reps, dim=1)[:, :w].contiguous() for t, w in
+               ((c1_layer.qweight, n_big // 8), (c1_layer.qzeros, n_big // 8), (c1_layer.scales, n_big))]
+        lin_big = L.PackedQuantLinear(L.QuantWeight.new_awq(4, *big))
+        y_big = torch.empty((m, n_big), dtype=torch.bfloat16, device="cuda")
+        for _ in range(2):
+            gemm.awq_matmul(lin_big, x, y_big)
+        ms_big = _timed_ms(torch, dist, world, lambda: gemm.awq_matmul(lin_big, x, y_big), 5)
+        tf = 2.0 * m * n_big * K / ms_big / 1e9
+        res[f"n{n_big}"] = {"ms": round(ms_big, 4), "tflops": round(tf, 1), "frac_of_bf16_burst_peak": round(tf / tf_burst, 4),
+                            "note": "weight cut into 8 dequantization slabs of 128 MiB"}
+        gemm.check(gemm.workspace(1, 8, "cuda"))
+        if world > 1:  # tensor-parallel column split + all-gather, checked against the single-GPU result of this rank
+            for n, lin_full, y_full, ms_1gpu in ((14336, lin, y, res["n14336"]["ms"]), (n_big, lin_big, y_big, ms_big)):
+                a, b_ = parallel.column_shard(n, world, rank)
+                qw, qz, sc = parallel.ColumnParallelLinear.slice_awq(lin_full.qweight, lin_full.qzeros, lin_full.scales, a, b_)
+                shard = L.PackedQuantLinear(L.QuantWeight.new_awq(4, qw, qz, sc))
+                tp = parallel.ColumnParallelLinear(shard.forward, n, chunks=1)  # one call: the shard is dequantized once
+                for _ in range(3):
+                    y_tp = tp.forward(x)
+                ms = _timed_ms(torch, dist, world, lambda: tp.forward(x), 10 if n == 14336 else 5)
+                gemm.awq_matmul(lin_full, x, y_full)
+                ref = y_full.float()
+                ok = bool(((y_tp.float() - ref).abs() <= 2e-2 * ref.abs().amax(dim=1, keepdim=True) + 1e-6).all().item())
+                tf = 2.0 * m * n * K / ms / 1e9
+                sharded[f"tp{world}_c2_awq_gemm_n{n}_allgather"] = {
+                    "ms": round(ms, 4), "tflops_whole_job": round(tf, 1), "ms_1gpu": round(ms_1gpu, 4),
+                    "speedup_vs_1gpu": round(ms_1gpu / ms, 3), "parity_ok": ok,
+                    "gathered_bytes_per_rank": int(m * n * 2 * (world - 1) / world)}
+                del tp, shard
+        del lin_big, y_big, big
         out["c2_awq_gemm_m2048"] = res
     except _NotSelected:
         pass
@@ -471,16 +538,20 @@ def run_extras(args, world, rank, c1_layer):
             ep = parallel.ExpertParallelMoe(e, lambda l_: moe.route(l_, 4, True), parallel.gptoss_local_experts(layer))
             xl, ll = x[sl].contiguous(), lg[sl].contiguous()
             for _ in range(2):
-                ep.forward(xl, ll)
-            ms = _timed_ms(torch, dist, world, lambda: ep.forward(xl, ll), 5)
-            res[f"ep{world}_all_to_all"] = {"ms": round(ms, 3), "tflops_whole_job": round(fl / ms / 1e9, 1),
-                                            "tokens_per_s_whole_job": round(tokens / ms * 1e3, 0)}
+                y_ep = ep.forward(xl, ll)
+            ms_ep = _timed_ms(torch, dist, world, lambda: ep.forward(xl, ll), 5)
+            ref = layer.forward_with_logits(xl, ll).float()  # the same tokens through all experts on this GPU
+            ok = bool(((y_ep.float() - ref).abs() <= 2e-2 * ref.abs().amax(dim=1, keepdim=True) + 1e-3).all().item())
+            sharded[f"ep{world}_c4_mxfp4_moe_all_to_all"] = {
+                "ms": round(ms_ep, 3), "tflops_whole_job": round(fl / ms_ep / 1e9, 1),
+                "tokens_per_s_whole_job": round(tokens / ms_ep * 1e3, 0), "ms_1gpu": round(ms, 3),
+                "speedup_vs_1gpu": round(ms / ms_ep, 3), "parity_ok": ok}
         out["c4_mxfp4_moe"] = res
     except _NotSelected:
         pass
     except Exception as e:
         out["c4_mxfp4_moe"] = {"error": str(e)[:200]}
-    return out
+    return out, sharded
 
 # --------------------------------------------------------------------------- CPU arm
 def cpu_sweep_once(w_f32, xs):
@@ -492,6 +563,12 @@ def cpu_sweep_once(w_f32, xs):
 def cpu_prepare():
     import oracle
     from oxydllm_b200 import synth
+    # torchrun exports OMP_NUM_THREADS=1: take every core this process may run on
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    oracle.set_num_threads(cores)
     qw, qz, sc = synth.awq_layer(K, N, G, seed=0)
     w = oracle.awq_dequant(qw, qz, sc)  # at load, untimed: what the reference does off Metal
     xs = {m: synth.activations(m, K, seed=m) for m in M_SWEEP}
@@ -551,7 +628,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip configurations 0, 2, 3, 4 (headline C1 line only)")
-    ap.add_argument("--configs", default="c0,c2,c3,c4",
+    ap.add_argument("--configs", default="c0,c1x,c2,c3,c4",
                     help="which of the other configurations to run, e.g. 'c3' (used to keep profiler captures small)")
     args = ap.parse_args()
     if args.impl == "reference":

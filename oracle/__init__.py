@@ -56,6 +56,12 @@ def num_threads() -> int:
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n: int) -> int:
+    """Use ``n`` OpenMP threads from now on (launchers such as torchrun export OMP_NUM_THREADS=1); returns the count in effect."""
+    lib().orc_set_num_threads(ctypes.c_int(int(n)))
+    return num_threads()
+
+
 # ------------------------------------------------------------------ rounding
 def to_bf16_bits(x: np.ndarray) -> np.ndarray:
     """f32 -> bf16 bit patterns (uint16), round-to-nearest-even."""

@@ -477,6 +477,12 @@ ORC_API int orc_num_threads(void)
 #endif
 }
 
+/* Thread count of the parallel loops from now on (a launcher may have exported OMP_NUM_THREADS=1). */
+ORC_API void orc_set_num_threads(int n)
+{
+    if (n > 0) omp_set_num_threads(n);
+}
+
 /* ------------------------------------------------------------------- MoE */
 
 /*
