@@ -442,8 +442,16 @@ def run_extras(args, world, rank, c1_layer):
         res[f"n{n_big}"] = {"ms": round(ms_big, 4), "tflops": round(tf, 1), "frac_of_bf16_burst_peak": round(tf / tf_burst, 4),
                             "note": "weight cut into 8 dequantization slabs of 128 MiB"}
         gemm.check(gemm.workspace(1, 8, "cuda"))
-        if world > 1:  # tensor-parallel column split + all-gather, checked against the single-GPU result of this rank
-            for n, lin_full, y_full, ms_1gpu in ((14336, lin, y, res["n14336"]["ms"]), (n_big, lin_big, y_big, ms_big)):
+        if world > 1:  # tensor-parallel column split, checked against the single-GPU result of this rank
+            # every rank must hold the SAME layer here (the headline layers differ per rank): one common seed
+            cqw, cqz, csc = synth.awq_layer(K, N, G, seed=4242)
+            common = [dev(cqw.view(np.int32)), dev(cqz.view(np.int32)), dev(csc)]
+            lin_c = L.PackedQuantLinear(L.QuantWeight.new_awq(4, *common))
+            big_c = [torch.cat([t] * reps, dim=1)[:, :w].contiguous() for t, w in
+                     ((common[0], n_big // 8), (common[1], n_big // 8), (common[2], n_big))]
+            lin_big_c = L.PackedQuantLinear(L.QuantWeight.new_awq(4, *big_c))
+            y_c = torch.empty((m, N), dtype=torch.bfloat16, device="cuda")
+            for n, lin_full, y_full, ms_1gpu in ((14336, lin_c, y_c, res["n14336"]["ms"]), (n_big, lin_big_c, y_big, ms_big)):
                 a, b_ = parallel.column_shard(n, world, rank)
                 qw, qz, sc = parallel.ColumnParallelLinear.slice_awq(lin_full.qweight, lin_full.qzeros, lin_full.scales, a, b_)
                 shard = L.PackedQuantLinear(L.QuantWeight.new_awq(4, qw, qz, sc))
@@ -459,7 +467,21 @@ def run_extras(args, world, rank, c1_layer):
                     "ms": round(ms, 4), "tflops_whole_job": round(tf, 1), "ms_1gpu": round(ms_1gpu, 4),
                     "speedup_vs_1gpu": round(ms_1gpu / ms, 3), "parity_ok": ok,
                     "gathered_bytes_per_rank": int(m * n * 2 * (world - 1) / world)}
+                try:  # direct placement: the GEMM epilogue stores each tile into every rank's output (no gather, no re-layout)
+                    ps = parallel.PeerStoreColumnLinear(shard, n, m_max=m)
+                    for _ in range(3):
+                        y_ps = ps.forward(x)
+                    ms_ps = _timed_ms(torch, dist, world, lambda: ps.forward(x), 10 if n == 14336 else 5)
+                    ok_ps = bool(((y_ps.float() - ref).abs() <= 2e-2 * ref.abs().amax(dim=1, keepdim=True) + 1e-6).all().item())
+                    sharded[f"tp{world}_c2_awq_gemm_n{n}_peer_store"] = {
+                        "ms": round(ms_ps, 4), "tflops_whole_job": round(2.0 * m * n * K / ms_ps / 1e9, 1),
+                        "ms_1gpu": round(ms_1gpu, 4), "speedup_vs_1gpu": round(ms_1gpu / ms_ps, 3), "parity_ok": ok_ps,
+                        "stored_to_peers_bytes_per_rank": int(m * (b_ - a) * 2 * (world - 1))}
+                    del ps, y_ps
+                except Exception as e:
+                    sharded[f"tp{world}_c2_awq_gemm_n{n}_peer_store"] = {"error": str(e)[:200]}
                 del tp, shard
+            del lin_c, lin_big_c, big_c, common, y_c
         del lin_big, y_big, big
         out["c2_awq_gemm_m2048"] = res
     except _NotSelected:

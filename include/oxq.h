@@ -195,6 +195,20 @@ int oxq_awq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint
                  int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
                  int group_size, void *workspace, size_t workspace_bytes, void *stream);
 
+/* Tensor-parallel column shard of the same matmul (no counterpart in the reference, which runs on one device; the
+ * sharding rule is the column-slice property concat_awq_along_out relies on, awq.rs:256-323). The packed tensors are
+ * this rank's columns [col_base, col_base + n_local) of a layer with n_full out features; the result is written into
+ * y[:, col_base : col_base + n_local] (y has n_full columns) and then copied by a small kernel of this library, with the
+ * same offsets, into the n_peers (<= 7) buffers y_peers[i]: device pointers into the OTHER ranks' output buffers
+ * (peer-mapped or symmetric memory), given as a HOST array. Only plain stores cross NVLink; nothing is read from a peer
+ * and no tensor map covers peer memory. `bias`, if given, has n_full entries. The column block and the rows of y must
+ * be 16-byte aligned. The caller orders the ranks (a barrier after the call before anyone reads y, and before
+ * the next call overwrites it). */
+int oxq_awq_gemm_tp(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
+                    int scales_dtype, const void *bias, int bias_dtype, void *y, void *const *y_peers, int n_peers,
+                    int y_dtype, int m, int k, int n_local, int col_base, int n_full, int group_size, void *workspace,
+                    size_t workspace_bytes, void *stream);
+
 /* Same branch for the 8-bit AWQ layout (dequantize_w8 + matmul, linear.rs:506-508). */
 int oxq_w8a16_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
                    int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
@@ -238,6 +252,21 @@ int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *router_logit
                            const uint8_t *dn_scales, const void *dn_bias, int bias_dtype, float limit, int expert_lo,
                            int expert_hi, void *out, int out_dtype, void *workspace, size_t workspace_bytes,
                            void *stream);
+
+/* The owner side of expert parallelism (no counterpart in the reference, which dispatches on one device,
+ * moe.rs:563-607): rows that already carry their expert id go through that expert with weight one,
+ * out[r] = MoeExpert::GptOss(expert_ids[r]).forward(rows[r]) (moe.rs:152-173). Only experts in
+ * [expert_lo, expert_hi) may occur. Workspace: oxq_gptoss_moe_workspace_bytes(n_rows, 1, expert_hi - expert_lo, ...). */
+int oxq_gptoss_experts_forward(const void *rows, int x_dtype, const int32_t *expert_ids, int n_rows, int num_experts,
+                               int hidden, int inter, const uint8_t *gu_blocks, const uint8_t *gu_scales,
+                               const void *gu_bias, const uint8_t *dn_blocks, const uint8_t *dn_scales, const void *dn_bias,
+                               int bias_dtype, float limit, int expert_lo, int expert_hi, void *out, int out_dtype,
+                               void *workspace, size_t workspace_bytes, void *stream);
+
+/* The combine of dispatch_sparse (moe.rs:593-605: expert outputs times routing weight, added in ascending expert order):
+ * out[t] = sum_s top_w[t, s] * rows[pos[t * top_k + s]], rows bf16 [*, hidden], f32 accumulation, one rounding. */
+int oxq_moe_combine(const void *rows, const int32_t *top_idx, const float *top_w, const int32_t *pos, int tokens,
+                    int top_k, int hidden, int num_experts, void *out, int out_dtype, void *stream);
 
 /* Routing alone: softmax over all experts, top-k (ties: lower index), optional
  * renormalisation (moe.rs:472-487). top_idx i32 [tokens, top_k], top_w f32. */

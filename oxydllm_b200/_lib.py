@@ -40,6 +40,7 @@ SIGNATURES = {
     "oxq_gemm_check": [_vp, _vp],
     "oxq_gemm_workspace_init": [_vp, _vp],
     "oxq_awq_gemm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp],
+    "oxq_awq_gemm_tp": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp],
     "oxq_gptq_gemm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp],
     "oxq_gguf_gemm": [_i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp],
     "oxq_fp8_gemm": [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp],
@@ -47,6 +48,9 @@ SIGNATURES = {
     "oxq_gptoss_moe_workspace_bytes": [_i, _i, _i, _i, _i],
     "oxq_gptoss_moe_forward": [_vp, _i, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, ctypes.c_float,
                                _i, _i, _vp, _i, _vp, _sz, _vp],
+    "oxq_gptoss_experts_forward": [_vp, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, ctypes.c_float, _i, _i,
+                                   _vp, _i, _vp, _sz, _vp],
+    "oxq_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
     "oxq_moe_route": [_vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "oxq_awq_gemm_noalloc_max_k": [],
     "oxq_awq_gemm_noalloc": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],

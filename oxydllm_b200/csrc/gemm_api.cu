@@ -56,6 +56,9 @@ struct GemmCommon {
     __nv_bfloat16 *slab;
     int rows;
     cudaStream_t st;
+    // tensor-parallel placement (oxq_awq_gemm_tp): this call's weight is columns [col_base, col_base + n) of an
+    // output with `ldy` columns
+    int col_base = 0, ldy = 0;
 };
 
 static int prepare(const char *who, GemmCommon &c, const void *x, int x_dtype, const void *bias, int bias_dtype,
@@ -84,7 +87,9 @@ template <typename Dequant> static int run_slabs(const GemmCommon &c, Dequant de
         const int cnt = c.n - n_off < c.rows ? c.n - n_off : c.rows;
         int rc = dequant(n_off, cnt);
         if (rc) return rc;
-        rc = gemm_bf16_tn(c.x, c.slab, c.bias, c.bias_dtype, c.y, c.y_dtype, c.m, cnt, c.k, n_off, c.n, c.flag, c.st);
+        // bias of a column shard is indexed like the output (caller passes the full-width bias)
+        rc = gemm_bf16_tn(c.x, c.slab, c.bias, c.bias_dtype, c.y, c.y_dtype, c.m, cnt, c.k, c.col_base + n_off,
+                          c.ldy ? c.ldy : c.n, c.flag, c.st);
         if (rc) return rc;
     }
     return OXQ_OK;
@@ -142,6 +147,67 @@ OXQ_EXPORT int oxq_awq_gemm(const void *x, int x_dtype, const uint32_t *qweight,
     return run_slabs(c, [&](int n_off, int cnt) {
         return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, n_off, cnt, c.st);
     });
+}
+
+// Column block [rows x chunks * 16 bytes] at byte offset col_off of every row of `src` -> the same place in each peer's
+// buffer. Local loads, plain 16-byte stores through the peer pointers; consecutive threads take consecutive chunks of a row.
+struct PeerCopyParams {
+    const unsigned char *src;
+    unsigned char *dst[7];
+    int n_peers, rows, chunks;
+    size_t ld_bytes, col_off;
+};
+__global__ void __launch_bounds__(256) peer_column_copy_kernel(const PeerCopyParams p)
+{
+    const size_t total = (size_t)p.rows * p.chunks;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / p.chunks, c = idx - r * p.chunks;
+        const size_t off = r * p.ld_bytes + p.col_off + c * 16;
+        const uint4 v = *reinterpret_cast<const uint4 *>(p.src + off);
+        for (int pe = 0; pe < p.n_peers; pe++) *reinterpret_cast<uint4 *>(p.dst[pe] + off) = v;
+    }
+}
+
+OXQ_EXPORT int oxq_awq_gemm_tp(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros,
+                               const void *scales, int scales_dtype, const void *bias, int bias_dtype, void *y,
+                               void *const *y_peers, int n_peers, int y_dtype, int m, int k, int n_local, int col_base,
+                               int n_full, int group_size, void *workspace, size_t workspace_bytes, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(qweight && qzeros && scales, OXQ_ERR_NULL, "oxq_awq_gemm_tp: null pointer");
+    OXQ_REQUIRE(valid_dtype(scales_dtype), OXQ_ERR_UNSUPPORTED, "oxq_awq_gemm_tp: unsupported scales dtype");
+    OXQ_REQUIRE(group_size > 0 && n_local % 8 == 0 && k % group_size == 0, OXQ_ERR_BAD_SHAPE,
+                "oxq_awq_gemm_tp: shard width %d must be a multiple of 8 and in_features %d a multiple of the group size %d",
+                n_local, k, group_size);
+    OXQ_REQUIRE(col_base >= 0 && n_full > 0 && col_base + n_local <= n_full, OXQ_ERR_BAD_SHAPE,
+                "oxq_awq_gemm_tp: columns [%d, %d) do not lie inside an output of width %d", col_base, col_base + n_local, n_full);
+    OXQ_REQUIRE(n_peers >= 0 && n_peers <= 7 && (n_peers == 0 || y_peers != nullptr), OXQ_ERR_UNSUPPORTED,
+                "oxq_awq_gemm_tp: between 0 and 7 peer outputs");
+    for (int i = 0; i < n_peers; i++) OXQ_REQUIRE(y_peers[i] != nullptr, OXQ_ERR_NULL, "oxq_awq_gemm_tp: null peer output %d", i);
+    GemmCommon c;
+    int rc = prepare("oxq_awq_gemm_tp", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n_local, workspace, workspace_bytes, stream);
+    if (rc) return rc;
+    c.col_base = col_base; c.ldy = n_full;
+    rc = run_slabs(c, [&](int n_off, int cnt) {
+        return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n_local, group_size, n_off, cnt, c.st);
+    });
+    if (rc || n_peers == 0) return rc;
+    // The finished column block goes to the same place in every peer's output: long contiguous runs (a row of the
+    // block) in 16-byte stores. Stores from the GEMM's epilogue (64-byte pieces per thread) were tried first and
+    // moved only about 170 GB/s over NVLink.
+    const size_t es = dtype_size(y_dtype);
+    OXQ_REQUIRE(((size_t)col_base * es) % 16 == 0 && ((size_t)n_local * es) % 16 == 0 && ((size_t)n_full * es) % 16 == 0 &&
+                    aligned(y, 16),
+                OXQ_ERR_BAD_ALIGN, "oxq_awq_gemm_tp: the column block and the rows of y must be 16-byte aligned");
+    PeerCopyParams pc;
+    pc.src = reinterpret_cast<const unsigned char *>(y);
+    pc.n_peers = n_peers;
+    for (int i = 0; i < 7; i++) pc.dst[i] = i < n_peers ? reinterpret_cast<unsigned char *>(y_peers[i]) : nullptr;
+    for (int i = 0; i < n_peers; i++) OXQ_REQUIRE(aligned(y_peers[i], 16), OXQ_ERR_BAD_ALIGN, "oxq_awq_gemm_tp: peer output %d not 16-byte aligned", i);
+    pc.rows = m; pc.ld_bytes = (size_t)n_full * es; pc.col_off = (size_t)col_base * es; pc.chunks = (int)((size_t)n_local * es / 16);
+    peer_column_copy_kernel<<<sm_count() * 4, 256, 0, c.st>>>(pc);
+    OXQ_LAUNCH_CHECK("peer_column_copy_kernel");
+    return OXQ_OK;
 }
 
 OXQ_EXPORT int oxq_gptq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros,

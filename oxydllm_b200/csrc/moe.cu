@@ -280,15 +280,22 @@ OXQ_EXPORT size_t oxq_gptoss_moe_workspace_bytes(int tokens, int top_k, int num_
     return moe_layout(tokens, top_k, num_local_experts, hidden, inter).total;
 }
 
-OXQ_EXPORT int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *router_logits, int tokens, int num_experts,
-                                      int top_k, int norm_topk, int hidden, int inter, const uint8_t *gu_blocks,
-                                      const uint8_t *gu_scales, const void *gu_bias, const uint8_t *dn_blocks,
-                                      const uint8_t *dn_scales, const void *dn_bias, int bias_dtype, float limit,
-                                      int expert_lo, int expert_hi, void *out, int out_dtype, void *workspace,
-                                      size_t workspace_bytes, void *stream)
+// Rows that already carry their expert: top_idx = the given id, weight one (the owner side of expert parallelism).
+__global__ void __launch_bounds__(256) moe_assign_kernel(const int32_t *__restrict__ ids, int rows, int *__restrict__ top_idx,
+                                                         float *__restrict__ top_w)
 {
-    clear_error();
-    OXQ_REQUIRE(x && router_logits && gu_blocks && gu_scales && dn_blocks && dn_scales && out, OXQ_ERR_NULL,
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < rows) { top_idx[i] = ids[i]; top_w[i] = 1.0f; }
+}
+
+static int moe_forward_impl(const void *x, int x_dtype, const float *router_logits, const int32_t *given_ids, int tokens,
+                            int num_experts, int top_k, int norm_topk, int hidden, int inter, const uint8_t *gu_blocks,
+                            const uint8_t *gu_scales, const void *gu_bias, const uint8_t *dn_blocks,
+                            const uint8_t *dn_scales, const void *dn_bias, int bias_dtype, float limit,
+                            int expert_lo, int expert_hi, void *out, int out_dtype, void *workspace,
+                            size_t workspace_bytes, void *stream)
+{
+    OXQ_REQUIRE(x && (router_logits || given_ids) && gu_blocks && gu_scales && dn_blocks && dn_scales && out, OXQ_ERR_NULL,
                 "oxq_gptoss_moe_forward: null pointer");
     OXQ_REQUIRE(x_dtype == OXQ_BF16, OXQ_ERR_UNSUPPORTED, "oxq_gptoss_moe_forward: activations must be bf16");
     OXQ_REQUIRE(valid_dtype(out_dtype) && (!(gu_bias || dn_bias) || valid_dtype(bias_dtype)), OXQ_ERR_UNSUPPORTED,
@@ -321,8 +328,9 @@ OXQ_EXPORT int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *r
     __nv_bfloat16 *slab = reinterpret_cast<__nv_bfloat16 *>(ws + L.slab);
     const int pairs = tokens * top_k;
 
-    moe_route_kernel<<<ceil_div(tokens * 32, 256), 256, 0, st>>>(router_logits, tokens, num_experts, top_k, norm_topk,
-                                                                 top_idx, top_w);
+    if (given_ids) moe_assign_kernel<<<ceil_div(tokens, 256), 256, 0, st>>>(given_ids, tokens, top_idx, top_w);
+    else moe_route_kernel<<<ceil_div(tokens * 32, 256), 256, 0, st>>>(router_logits, tokens, num_experts, top_k, norm_topk,
+                                                                      top_idx, top_w);
     if (L.decode) {
         OXQ_REQUIRE(aligned(gu_blocks, 16) && aligned(dn_blocks, 16), OXQ_ERR_BAD_ALIGN,
                     "oxq_gptoss_moe_forward: expert blocks must be 16-byte aligned");
@@ -373,6 +381,51 @@ OXQ_EXPORT int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *r
     }
     moe_combine_kernel<<<sm_count() * 8, 256, 0, st>>>(xs, top_idx, top_w, inv, tokens, top_k, hidden, expert_lo, expert_hi, out,
                                                 out_dtype);
+    OXQ_LAUNCH_CHECK("moe_combine_kernel");
+    return OXQ_OK;
+}
+
+OXQ_EXPORT int oxq_gptoss_moe_forward(const void *x, int x_dtype, const float *router_logits, int tokens, int num_experts,
+                                      int top_k, int norm_topk, int hidden, int inter, const uint8_t *gu_blocks,
+                                      const uint8_t *gu_scales, const void *gu_bias, const uint8_t *dn_blocks,
+                                      const uint8_t *dn_scales, const void *dn_bias, int bias_dtype, float limit,
+                                      int expert_lo, int expert_hi, void *out, int out_dtype, void *workspace,
+                                      size_t workspace_bytes, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(router_logits != nullptr, OXQ_ERR_NULL, "oxq_gptoss_moe_forward: null pointer");
+    return moe_forward_impl(x, x_dtype, router_logits, nullptr, tokens, num_experts, top_k, norm_topk, hidden, inter, gu_blocks,
+                            gu_scales, gu_bias, dn_blocks, dn_scales, dn_bias, bias_dtype, limit, expert_lo, expert_hi, out,
+                            out_dtype, workspace, workspace_bytes, stream);
+}
+
+// Each row through the expert it is already assigned to, weight one: out[r] = expert[ids[r]](rows[r]).
+OXQ_EXPORT int oxq_gptoss_experts_forward(const void *rows, int x_dtype, const int32_t *expert_ids, int n_rows, int num_experts,
+                                          int hidden, int inter, const uint8_t *gu_blocks, const uint8_t *gu_scales,
+                                          const void *gu_bias, const uint8_t *dn_blocks, const uint8_t *dn_scales,
+                                          const void *dn_bias, int bias_dtype, float limit, int expert_lo, int expert_hi,
+                                          void *out, int out_dtype, void *workspace, size_t workspace_bytes, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(expert_ids != nullptr, OXQ_ERR_NULL, "oxq_gptoss_experts_forward: null pointer");
+    return moe_forward_impl(rows, x_dtype, nullptr, expert_ids, n_rows, num_experts, 1, 0, hidden, inter, gu_blocks, gu_scales,
+                            gu_bias, dn_blocks, dn_scales, dn_bias, bias_dtype, limit, expert_lo, expert_hi, out, out_dtype,
+                            workspace, workspace_bytes, stream);
+}
+
+// Weighted sum of each token's k result rows in ascending expert order (moe.rs:593-605: index_add per expert in order):
+// out[t] = sum_s top_w[t, s] * rows[pos[t * k + s]]; f32 accumulation, one rounding. Same bits every run.
+OXQ_EXPORT int oxq_moe_combine(const void *rows, const int32_t *top_idx, const float *top_w, const int32_t *pos, int tokens,
+                               int top_k, int hidden, int num_experts, void *out, int out_dtype, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(rows && top_idx && top_w && pos && out, OXQ_ERR_NULL, "oxq_moe_combine: null pointer");
+    OXQ_REQUIRE(valid_dtype(out_dtype), OXQ_ERR_UNSUPPORTED, "oxq_moe_combine: unsupported dtype");
+    OXQ_REQUIRE(tokens > 0 && top_k > 0 && top_k <= MOE_MAX_TOPK && hidden > 0 && hidden % 8 == 0, OXQ_ERR_BAD_SHAPE,
+                "oxq_moe_combine: tokens %d, top_k %d (max %d), hidden %d (multiple of 8)", tokens, top_k, MOE_MAX_TOPK, hidden);
+    OXQ_REQUIRE(aligned(rows, 16), OXQ_ERR_BAD_ALIGN, "oxq_moe_combine: rows must be 16-byte aligned");
+    moe_combine_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)rows, top_idx, top_w, pos, tokens,
+                                                                          top_k, hidden, 0, num_experts, out, out_dtype);
     OXQ_LAUNCH_CHECK("moe_combine_kernel");
     return OXQ_OK;
 }

@@ -38,6 +38,19 @@ def route(logits: torch.Tensor, top_k: int, norm_topk: bool = True):
     return idx, w
 
 
+def combine(rows: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, pos: torch.Tensor, num_experts: int,
+            out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``out[t] = sum_s top_w[t, s] * rows[pos[t, s]]`` in ascending expert order (moe.rs:593-605), on the device."""
+    t, k = top_idx.shape
+    hidden = rows.shape[1]
+    out = torch.empty((t, hidden), dtype=out_dtype or rows.dtype, device=rows.device)
+    if t:
+        _lib.call("oxq_moe_combine", _p(rows.contiguous()), _p(top_idx.to(torch.int32).contiguous()),
+                  _p(top_w.to(torch.float32).contiguous()), _p(pos.to(torch.int32).contiguous()), t, k, hidden, num_experts,
+                  _p(out), _dt(out.dtype), _stream())
+    return out
+
+
 class GptOssMoe:
     """``gu_*``: fused gate/up projection (even rows gate, odd rows up), ``dn_*``: down projection, per expert."""
 
@@ -92,6 +105,28 @@ class GptOssMoe:
                   ctypes.c_float(self.limit), lo, hi, _p(out), _dt(out.dtype), _p(ws), ws.numel(), _stream())
         self.last_workspace = ws
         return out.reshape(shape)
+
+    def forward_experts(self, rows: torch.Tensor, expert_ids: torch.Tensor, expert_range=None) -> torch.Tensor:
+        """Each row through the expert it is already assigned to, weight one (the owner side of expert parallelism)."""
+        if rows.shape[-1] != self.hidden:
+            raise ValueError(f"Mxfp4Linear: x last dim {rows.shape[-1]} != in_features {self.hidden}")
+        if not rows.is_cuda:
+            raise ValueError("oxydllm_b200 operators run on CUDA tensors only (no CPU path)")
+        rows = rows.contiguous()
+        ids = expert_ids.to(torch.int32).contiguous()
+        r = rows.shape[0]
+        out = torch.empty_like(rows)
+        if r == 0:
+            return out
+        lo, hi = (0, self.num_experts) if expert_range is None else expert_range
+        need = int(_lib.load().oxq_gptoss_moe_workspace_bytes(r, 1, hi - lo, self.hidden, self.inter))
+        ws = _workspace(need, rows.device)
+        _lib.call("oxq_gptoss_experts_forward", _p(rows), _dt(rows.dtype), _p(ids), r, self.num_experts, self.hidden, self.inter,
+                  _p(self.gu_blocks), _p(self.gu_scales), _p(self.gu_bias), _p(self.dn_blocks), _p(self.dn_scales),
+                  _p(self.dn_bias), _dt(self.gu_bias.dtype), ctypes.c_float(self.limit), lo, hi, _p(out), _dt(out.dtype),
+                  _p(ws), ws.numel(), _stream())
+        self.last_workspace = ws
+        return out
 
     def check(self):
         """Synchronise and raise if a tensor-core kernel of the last forward gave up on a wait."""

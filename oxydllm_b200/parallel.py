@@ -141,6 +141,54 @@ class ColumnParallelLinear:
         return out
 
 
+class PeerStoreColumnLinear:
+    """Column-split AWQ linear that places its output block straight into ``out[:, a:b]`` of EVERY rank.
+
+    No all-gather and no re-layout: ``oxq_awq_gemm_tp`` runs the tensor-core GEMM of the shard into the local output
+    and copies the finished column block, through peer pointers, to the same place in the other ranks' outputs
+    (plain stores over NVLink from a small kernel of the library; nothing is read from a peer). The output buffer ``[m_max, n]`` is symmetric memory
+    (``torch.distributed._symmetric_memory``), allocated and exchanged once. Two barriers order the ranks: one
+    before the GEMM (nobody still reads the previous result) and one after it (every tile has landed).
+    ``forward`` returns a view of that buffer, valid until the next ``forward``.
+    """
+
+    def __init__(self, shard, out_features: int, m_max: int, group=None, dtype: torch.dtype = torch.bfloat16):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.shard, self.n, self.m_max = shard, out_features, m_max
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.a, self.b = column_shard(out_features, self.world, self.rank)
+        if shard.out_features != self.b - self.a:
+            raise ValueError(f"shard has {shard.out_features} out features, rank {self.rank} owns {self.b - self.a}")
+        if self.world > 8:
+            raise ValueError("PeerStoreColumnLinear: at most 8 ranks (7 peer outputs)")
+        self.out = symm_mem.empty((m_max, out_features), dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        self.hdl = symm_mem.rendezvous(self.out, self.group.group_name)
+        import ctypes
+        peers = [int(self.hdl.buffer_ptrs[r]) for r in range(self.world) if r != self.rank]
+        self._peers = (ctypes.c_void_p * max(1, len(peers)))(*peers)
+        self._n_peers = len(peers)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        from . import _lib, gemm
+        from .linear import _dt, _p, _stream
+        m = x.shape[0]
+        if m > self.m_max:
+            raise ValueError(f"PeerStoreColumnLinear: batch {m} exceeds the buffer ({self.m_max} rows)")
+        lin = self.shard
+        ws = gemm.workspace(lin.out_features, lin.in_features, x.device)
+        y = self.out[:m]
+        self.hdl.barrier(channel=0)  # the previous result is no longer read anywhere
+        # row stride of the output buffer is n for any m (a leading slice), so peer offsets equal local ones
+        import ctypes
+        _lib.call("oxq_awq_gemm_tp", _p(x), _dt(x.dtype), _p(lin.qweight), _p(lin.qzeros), _p(lin.scales), _dt(lin.scales.dtype),
+                  _p(lin.bias), _dt(lin.bias.dtype) if lin.bias is not None else 0, _p(y),
+                  ctypes.cast(self._peers, ctypes.c_void_p), self._n_peers, _dt(y.dtype), m, lin.in_features, lin.out_features,
+                  self.a, self.n, lin.group_size, _p(ws), ws.numel(), _stream())
+        self.hdl.barrier(channel=1)  # every rank's tiles have landed here
+        return y
+
+
 # ----------------------------------------------------------------------------- expert parallel MoE
 class ExpertParallelMoe:
     """All-to-all expert parallelism around a local expert function.
@@ -167,23 +215,19 @@ class ExpertParallelMoe:
         got_ids = all_to_all_rows(ids[:, None], sc, rc, self.group)[:, 0]
         y = self.local_experts(got_rows, got_ids) if got_rows.shape[0] else got_rows
         back = all_to_all_rows(y.to(x.dtype), rc, sc, self.group)
+        if back.is_cuda and back.dtype == torch.bfloat16 and back.shape[1] % 8 == 0:
+            from . import moe  # the device combine: one kernel, ascending expert order, f32 accumulation
+            pos = torch.empty_like(send_order)
+            pos[send_order] = torch.arange(send_order.numel(), device=send_order.device)
+            return moe.combine(back, top_idx, top_w, pos, self.num_experts, x.dtype)
         return combine_rows(back, send_order, top_idx, top_w).to(x.dtype)
 
 
 def gptoss_local_experts(layer) -> Callable:
     """``local_experts`` callable over a :class:`moe.GptOssMoe` holding ALL expert tensors (only the local
-    ones are touched): each received row goes through its expert with weight one."""
+    ones are touched): each received row goes through its expert with weight one (``oxq_gptoss_experts_forward``)."""
     def run(rows: torch.Tensor, expert_ids: torch.Tensor) -> torch.Tensor:
-        e = layer.num_experts
-        # one-hot logits: softmax puts all mass on the row's expert; top-1 routing then reproduces the given ids
-        logits = torch.full((rows.shape[0], e), -30000.0, dtype=torch.float32, device=rows.device)
-        logits.scatter_(1, expert_ids.to(torch.int64)[:, None], 0.0)
-        saved = layer.top_k
-        layer.top_k = 1
-        try:
-            world = dist.get_world_size() if dist.is_initialized() else 1
-            rank = dist.get_rank() if dist.is_initialized() else 0
-            return layer.forward_with_logits(rows, logits, expert_shard(e, world, rank))
-        finally:
-            layer.top_k = saved
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        return layer.forward_experts(rows, expert_ids, expert_shard(layer.num_experts, world, rank))
     return run

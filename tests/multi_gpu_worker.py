@@ -40,6 +40,18 @@ def main():
         tol = 2e-2 * float(ref.float().abs().max())
         assert err <= tol, f"TP m={m}: {err} > {tol}"
 
+    # --- the same split with direct placement: each rank's GEMM stores its tile into every rank's output
+    ps = parallel.PeerStoreColumnLinear(shard, n, m_max=256)
+    for m in (200, 64, 200):
+        x = dev(synth.activations(m, k, seed=m + 7), torch.bfloat16)
+        y = ps.forward(x)
+        ref = full.forward(x)
+        err = float((y.float() - ref.float()).abs().max())
+        tol = 2e-2 * float(ref.float().abs().max())
+        assert err <= tol, f"peer-store TP m={m}: {err} > {tol}"
+    from oxydllm_b200 import gemm
+    gemm.check(gemm.workspace(shard.out_features, k, "cuda"))
+
     # --- expert parallel all-to-all dispatch / combine
     e, hidden, inter, t_local = 8, 128, 128, 96
     d = synth.gptoss_moe(e, hidden, inter, t_local * world, seed=2)

@@ -192,3 +192,31 @@ def test_c3_every_m(cuda, m):
     for a, b in col_windows(n) + [(7168 - 64, 7168 + 64)]:
         wa = oracle.round_bf16(w[a:b]) if m > 32 else w[a:b]
         close(y[rows][:, a:b], oracle.linear(x[rows], wa), f"C3 m={m} rows {a}:{b}")
+
+
+def test_awq_gemm_tp_entry_places_tile_in_local_and_peer_outputs(cuda):
+    """oxq_awq_gemm_tp on one GPU: a second buffer of the same GPU stands in for a peer's output. Both receive this
+    shard's columns [col_base, col_base + n_local) of an n_full-wide output and nothing else."""
+    import ctypes
+    from oxydllm_b200 import _lib
+    m, k, n_full, g = 200, 512, 1024, 128
+    a, b = 256, 768
+    qw, qz, sc = synth.awq_layer(k, n_full, g, seed=21)
+    bias = synth.bf16_round(np.random.default_rng(4).standard_normal(n_full).astype(np.float32))
+    x = synth.activations(m, k, seed=22)
+    xd, qwd, qzd, scd = dev(x, torch.bfloat16), words(qw[:, a // 8:b // 8]), words(qz[:, a // 8:b // 8]), dev(sc[:, a:b])
+    bd = dev(bias, torch.bfloat16)
+    y_local = torch.full((m, n_full), 7.0, dtype=torch.bfloat16, device="cuda")
+    y_peer = torch.full((m, n_full), 7.0, dtype=torch.bfloat16, device="cuda")
+    peers = (ctypes.c_void_p * 1)(y_peer.data_ptr())
+    ws = gemm.workspace(b - a, k, "cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    _lib.call("oxq_awq_gemm_tp", p(xd), _lib.OXQ_BF16, p(qwd), p(qzd), p(scd), _lib.OXQ_F16, p(bd), _lib.OXQ_BF16, p(y_local),
+              ctypes.cast(peers, ctypes.c_void_p), 1, _lib.OXQ_BF16, m, k, b - a, a, n_full, g, p(ws), ws.numel(),
+              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    gemm.check(ws)
+    ref = oracle.linear(x, oracle.round_bf16(oracle.awq_dequant(qw[:, a // 8:b // 8], qz[:, a // 8:b // 8], sc[:, a:b])), bias[a:b])
+    for y in (y_local, y_peer):
+        close(y[:, a:b], ref, "tp tile")
+        assert bool((y[:, :a] == 7.0).all()) and bool((y[:, b:] == 7.0).all())
+    assert torch.equal(y_local, y_peer)

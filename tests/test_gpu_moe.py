@@ -107,3 +107,36 @@ def test_moe_decode_path_gpt_oss_shape(cuda, tokens):
     got_hi = layer.forward_with_logits(x, lg, (4, 8)).float().cpu().numpy()
     ref_hi = oracle.gptoss_moe(d["x"], idx, w, *args, expert_range=(4, 8))
     assert (np.abs(got_hi - ref_hi) <= 2e-2 * np.abs(ref).max(axis=1, keepdims=True) + 1e-5).all()
+
+
+def test_forward_experts_with_given_ids_matches_oracle(cuda):
+    """Rows that already carry their expert (the owner side of expert parallelism): each row through that expert, weight one."""
+    e, hidden, inter, rows = 8, 128, 96, 150
+    d = synth.gptoss_moe(e, hidden, inter, rows, seed=3)
+    layer = build(d)
+    lo, hi = 2, 6
+    ids = np.random.default_rng(0).integers(lo, hi, size=rows).astype(np.int32)
+    y = layer.forward_experts(dev(d["x"], torch.bfloat16), dev(ids), (lo, hi))
+    layer.check()
+    got = y.float().cpu().numpy()
+    for r in range(0, rows, 7):
+        ex = int(ids[r])
+        w_gu = oracle.mxfp4_dequant(d["gu_blocks"][ex], d["gu_scales"][ex], 2 * inter, hidden)
+        w_dn = oracle.mxfp4_dequant(d["dn_blocks"][ex], d["dn_scales"][ex], hidden, inter)
+        ref = oracle.gptoss_expert(d["x"][r:r + 1], w_gu, d["gu_bias"][ex], w_dn, d["dn_bias"][ex])[0]
+        assert np.abs(got[r] - ref).max() <= 2e-2 * np.abs(ref).max() + 1e-5, r
+
+
+def test_device_combine_matches_host_combine(cuda):
+    from oxydllm_b200 import parallel
+    t, k, hidden, e = 37, 4, 64, 16
+    rng = np.random.default_rng(1)
+    top_idx = np.stack([rng.permutation(e)[:k] for _ in range(t)]).astype(np.int32)
+    top_w = rng.random((t, k)).astype(np.float32)
+    rows = synth.bf16_round(rng.standard_normal((t * k, hidden)).astype(np.float32))
+    send_order = torch.from_numpy(rng.permutation(t * k))
+    pos = torch.empty_like(send_order)
+    pos[send_order] = torch.arange(t * k)
+    ref = parallel.combine_rows(torch.from_numpy(rows), send_order, torch.from_numpy(top_idx), torch.from_numpy(top_w))
+    got = moe.combine(dev(rows, torch.bfloat16), dev(top_idx), dev(top_w), pos.cuda(), e, torch.float32)
+    assert torch.allclose(got.cpu(), ref, rtol=1e-6, atol=1e-6)
