@@ -1,25 +1,28 @@
-// AWQ W4A16 batched decode GEMV, 1 <= m <= 32.
+// AWQ W4A16 batched decode GEMV, 1 <= m <= 32. Two kernels:
 //
-// The kernel is bound by the stream of packed weights from HBM (0.5 B/weight
-// plus scales/zeros), so everything is arranged around that stream:
+//  * awq_gemv_group_kernel (second half of this file) is the one the operator
+//    launches whenever group_size is a power of two >= 16 and the shape tiles
+//    (every benchmark layer): k slices aligned to quantization groups, packed
+//    words streamed from HBM straight into registers a few steps ahead, x staged
+//    once per CTA in shared memory as f16, nibbles turned into exact f16 values
+//    with one lop3 each, mma.sync m16n8k16 f16 with f32 accumulation, scale and
+//    zero point folded once per group in f32, split-k partials summed in fixed
+//    order through (distributed) shared memory of a thread-block cluster. Its
+//    own comment below has the details.
+//  * awq_gemv_kernel (first half) is the general fallback for the remaining
+//    shapes (odd group sizes, k not a multiple of the slice): every lane copies
+//    the packed words it will consume with cp.async into a lane-private slot of
+//    a shared-memory ring (GEMV_STAGES deep, no barrier between producer and
+//    consumer); a warp step covers 16 input rows x 8V packed words; nibbles
+//    become bf16 pairs along k with one prmt + one lop3 per weight
+//    (0x4300 | q == 128 + q exactly) and meet up to 8 tokens in mma.sync
+//    m16n8k16 bf16; one extra MMA against an all-ones operand yields sum_k x
+//    per token, so  y += s * (sum (128+q) x - (128+z) sum x)  per group in f32;
+//    the split along k is reduced in fixed rank order through distributed
+//    shared memory: no workspace, no second launch, no atomics.
 //
-//  * every lane copies exactly the packed words it will consume with cp.async
-//    into a lane-private slot of a shared-memory ring (STAGES deep), so the
-//    number of bytes in flight does not depend on registers and no barrier is
-//    needed between producer and consumer;
-//  * a warp-level step covers 16 input rows x (8 * V) packed words; lanes with
-//    the same lane%4 read one row, 8 lanes x 4V bytes contiguous, 4 rows per
-//    instruction;
-//  * the 4-bit values are turned into bf16 pairs along k with one prmt + one
-//    lop3 per weight (magic-number conversion: 0x4300 | q == 128 + q exactly),
-//    and contracted on the tensor cores (mma.sync m16n8k16, weights as the
-//    16-row operand, up to 8 tokens as the 8-column operand) with f32
-//    accumulation. One extra MMA with an all-ones operand yields sum_k x per
-//    token, so scale and zero point are applied once per quantization group in
-//    f32:  y += s * (sum (128+q) x - (128+z) sum x);
-//  * the split along k (needed to fill 148 SMs with a skinny problem) is
-//    reduced in fixed rank order through distributed shared memory inside a
-//    thread-block cluster: no workspace, no second launch, no atomics.
+// Both are bound by the stream of packed weights from HBM (0.5 B per weight
+// plus scales and zeros); neither allocates or synchronises.
 #include <cooperative_groups.h>
 
 #include <cstdio>
