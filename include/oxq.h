@@ -84,6 +84,11 @@ int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight, const uint
                  int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
                  int group_size, void *stream);
 
+/* oxq_awq_gemv streams weight boxes into shared memory with the TMA unit and waits for each with a
+ * bounded wait. Synchronises `stream`; returns OXQ_ERR_DEVICE_FLAG (once) if such a wait ran out on
+ * the current device in any oxq_awq_gemv call since the last check. No counterpart in the reference. */
+int oxq_awq_gemv_check(void *stream);
+
 /* Gated FFN projection on a fused AWQ [gate | up] weight (concat_awq_along_out of gate_proj and
  * up_proj, ffn.rs:235-254): y[m, inter] = act(x . W_gate^T) * (x . W_up^T), act = 1 SiLU, 2 GeLU-tanh
  * (FeedForward::forward, ffn.rs:385-470; gated_silu_fused / gated_gelu_tanh_fused, metal_ops.rs:1243-1277).

@@ -29,12 +29,20 @@
 #include <cstdlib>
 
 #include "oxq_common.cuh"
+#include "tc_common.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace oxq {
 
 constexpr int GEMV_STAGES = 8;
+
+#ifdef OXQ_TUNING
+__device__ unsigned long long g_gv_cta[1024][8]; // per-CTA time stamps of the last launch (tuning builds only)
+#define GV_CTA(slot) do { if (threadIdx.x == 0) { const unsigned b_ = blockIdx.y * gridDim.x + blockIdx.x; if (b_ < 1024) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_gv_cta[b_][slot] = t_; } } } while (0)
+#else
+#define GV_CTA(slot) do { } while (0)
+#endif
 
 struct AwqGemvParams {
     const __nv_bfloat16 *x;
@@ -47,6 +55,7 @@ struct AwqGemvParams {
     int m, k, n, group_size;
     int packed_out;
     int steps_per_cta; // 16-row steps handled by one CTA of the cluster
+    int stages;        // TMA variant: depth of a warp's ring of weight boxes
     int token_split;   // main variant: neighbouring CTAs that share an n tile and take 8*MT tokens each (>= 1)
 };
 
@@ -330,7 +339,9 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
     constexpr int KW = GK_KW;
     constexpr int NACC = V * 4 * MT * 4;
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
 
+    GV_CTA(0);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, c = lane & 3;
     const int rank = blockIdx.y, nranks = gridDim.y;
@@ -373,6 +384,7 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
     float4 *mine = red + (size_t)warp * (NACC / 4) * 32 + lane;
 #pragma unroll
     for (int i = 0; i < NACC / 4; i++) mine[i * 32] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    pdl_wait(); // x may come from the kernel before this one; the first weights are already on their way
     for (int row = 0; row < m_loc; row++) {
         const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)(m0 + row) * p.k + k_cta);
         uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
@@ -402,6 +414,7 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
     int grp = (step_beg * 16) / p.group_size;
     fetch_group(grp);
     __syncthreads();
+    GV_CTA(1);
 
     float acc[V][4][MT][4], sx[MT][4];
 #pragma unroll
@@ -520,8 +533,10 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
         }
         wsrc += (size_t)16 * D * row_stride;
     }
+    GV_CTA(2);
     cg::cluster_group cluster = cg::this_cluster();
     if (nranks > 1) cluster.sync(); else __syncthreads();
+    GV_CTA(3);
 
     // Every tile slot (tile, lane) that holds a real token is summed by one thread of the cluster
     // over the KW * R slices in ascending k order (bank-conflict-free: lane-minor, 16-byte loads).
@@ -554,7 +569,9 @@ __global__ void __launch_bounds__(GK_KW * 32, MINB) awq_gemv_group_kernel(const 
             }
         }
     }
+    GV_CTA(4);
     if (nranks > 1) cluster.sync();
+    GV_CTA(5);
 }
 
 template <int MT, int V, int D, int MINB>
@@ -578,14 +595,369 @@ static int launch_awq_gemv_group(const AwqGemvParams &p, int nranks, cudaStream_
     cfg.blockDim = dim3(GK_KW * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = nranks;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    allow_early_start(attr, cfg.numAttrs);
     OXQ_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
+    return OXQ_OK;
+}
+
+// ---------------------------------------------------------------------------
+// TMA-ring variant of the main kernel (same slicing, same arithmetic, same fixed-order reduction).
+//
+// The register-streaming kernel above keeps at most D steps of weights in flight per warp, because
+// bytes in flight are registers; at four CTAs per SM that is about 25 KB per SM, well short of what
+// the memory system needs to stay busy. Here every warp owns a ring of `stages` shared-memory slots;
+// lane 0 asks the TMA unit for one box of GT_ROWS input rows x 16 packed words (2 KB) per slot and
+// refills a slot as soon as the warp has read it, so a warp keeps stages x 2 KB on their way with one
+// instruction per box and no registers. A box lands as dense 64-byte rows. Within a 16-row step lane
+// (g, c) reads rows c, 4 + c, 8 + c, 12 + c (consecutive rows across c: the four rows of one
+// instruction are 256 contiguous bytes); x is staged in the matching order, so element 4c + i of a
+// 16-block is x[4i + c] and a lane's B fragment is still one 8-byte read.
+constexpr int GT_KW = 4;
+constexpr int GT_ROWS = 32;
+constexpr int GT_STAGE_BYTES = GT_ROWS * 64;
+constexpr int GT_MAX_STAGES = 8;
+
+__device__ int g_awq_gemv_flag; // non-zero after a wait on a weight box gave up
+
+template <int MT, int MINB>
+__global__ void __launch_bounds__(GT_KW * 32, MINB)
+    awq_gemv_tma_kernel(const AwqGemvParams p, const __grid_constant__ CUtensorMap wmap)
+{
+    constexpr int KW = GT_KW, V = 2;
+    constexpr int NACC = V * 4 * MT * 4;
+    extern __shared__ __align__(1024) unsigned char smem[];
+
+    GV_CTA(0);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, c = lane & 3;
+    const int rank = blockIdx.y, nranks = gridDim.y;
+    const int zt = blockIdx.x % p.token_split;
+    const int m0 = zt * 8 * MT, m_loc = min(8 * MT, p.m - m0);
+    const int jtile = (blockIdx.x / p.token_split) * 8 * V;
+    const int jbase = jtile + g * V;
+    const int steps = p.steps_per_cta; // 16-row steps per warp slice (even)
+    const int boxes = steps >> 1;
+    const int gsteps = p.group_size >> 4;
+    const int S = p.stages;
+    uint32_t mask_lo, mask_hi, kmagic;
+    asm volatile("mov.b32 %0, 0x000F000F;\n\tmov.b32 %1, 0x00F000F0;\n\tmov.b32 %2, 0x64006400;"
+                 : "=r"(mask_lo), "=r"(mask_hi), "=r"(kmagic));
+    const int kr = KW * steps * 16;
+    const int k_cta = rank * kr;
+    const int step_beg = (rank * KW + warp) * steps;
+
+    // shared memory: rings | barriers | x | zeros | totals
+    unsigned char *ring = smem + (size_t)warp * S * GT_STAGE_BYTES;
+    const uint32_t ring_addr = smem_u32(ring);
+    const uint32_t bar0 = smem_u32(smem + (size_t)KW * S * GT_STAGE_BYTES) + warp * GT_MAX_STAGES * 8;
+    unsigned char *rest = smem + (size_t)KW * S * GT_STAGE_BYTES + KW * GT_MAX_STAGES * 8;
+
+    // The next launch on the stream may start its own weight boxes while this one drains; nothing
+    // that another kernel may have produced (x) or may still read (y) is touched before the wait below.
+    pdl_launch_dependents();
+    if (nranks > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); // met again before the first remote store
+
+    if (lane == 0) {
+        for (int s = 0; s < S; s++) mbar_init(bar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int s = 0; s < S && s < boxes; s++) {
+            mbar_arrive_expect_tx(bar0 + 8 * s, GT_STAGE_BYTES);
+            tma_load_2d(ring_addr + s * GT_STAGE_BYTES, &wmap, bar0 + 8 * s, jtile, step_beg * 16 + s * GT_ROWS);
+        }
+    }
+    __syncwarp();
+
+    const int xrow = kr + 16; // elements; the 32-byte pad keeps the fragment reads of four tokens in distinct banks
+    __half *xs = reinterpret_cast<__half *>(rest);
+    uint32_t *zeros = reinterpret_cast<uint32_t *>(rest + (size_t)m_loc * xrow * sizeof(__half));
+    if (tid < 4) zeros[tid] = 0u;
+    float4 *red = reinterpret_cast<float4 *>(zeros + 4);
+    float4 *mine = red + (size_t)warp * (NACC / 4) * 32 + lane;
+    float4 *inbox = red + (size_t)KW * (NACC / 4) * 32; // [source rank][local tile][lane], written by the whole cluster
+#pragma unroll
+    for (int i = 0; i < NACC / 4; i++) mine[i * 32] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+
+    const bool sc16 = p.scales_dtype != OXQ_F32;
+    const bool is_f16 = p.scales_dtype == OXQ_F16;
+    uint32_t zw[V], sraw[V][4];
+    auto fetch_group = [&](int grp) {
+#pragma unroll
+        for (int v = 0; v < V; v++) {
+            zw[v] = __ldg(p.qzeros + (size_t)grp * p.packed_out + jbase + v);
+            uint4 r = make_uint4(0u, 0u, 0u, 0u);
+            if (sc16)
+                r = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.scales) +
+                                                          (size_t)grp * p.n + (size_t)(jbase + v) * 8));
+            sraw[v][0] = r.x; sraw[v][1] = r.y; sraw[v][2] = r.z; sraw[v][3] = r.w;
+        }
+    };
+    int grp = (step_beg * 16) / p.group_size;
+    fetch_group(grp);
+
+    pdl_wait();
+    {   // x[m0 .. m0 + m_loc) x [k_cta, k_cta + kr) -> f16 in the order the fragments want; loads of four items
+        // are issued before the first is converted, so the staging costs about one memory round trip.
+        const int per = kr >> 2, items = m_loc * per;
+        for (int base = tid; base < items; base += 4 * KW * 32) {
+            uint2 raw[4];
+            int at[4];
+#pragma unroll
+            for (int j4 = 0; j4 < 4; j4++) {
+                const int idx = base + j4 * KW * 32;
+                at[j4] = -1;
+                if (idx < items) {
+                    const int row = idx / per, q4 = idx - row * per;
+                    raw[j4] = __ldg(reinterpret_cast<const uint2 *>(p.x + (size_t)(m0 + row) * p.k + k_cta) + q4);
+                    at[j4] = row * xrow + (q4 >> 2) * 16 + (q4 & 3); // x[16 blk + 4 i + cc] -> element 16 blk + 4 cc + i
+                }
+            }
+#pragma unroll
+            for (int j4 = 0; j4 < 4; j4++) {
+                if (at[j4] < 0) continue;
+                const uint32_t h01 = f32x2_to_f16x2_sat(bf16_lo_f32(raw[j4].x), bf16_hi_f32(raw[j4].x));
+                const uint32_t h23 = f32x2_to_f16x2_sat(bf16_lo_f32(raw[j4].y), bf16_hi_f32(raw[j4].y));
+                unsigned short *d16 = reinterpret_cast<unsigned short *>(xs) + at[j4];
+                d16[0] = (unsigned short)(h01 & 0xFFFFu);
+                d16[4] = (unsigned short)(h01 >> 16);
+                d16[8] = (unsigned short)(h23 & 0xFFFFu);
+                d16[12] = (unsigned short)(h23 >> 16);
+            }
+        }
+    }
+    __syncthreads();
+    GV_CTA(1);
+
+    float acc[V][4][MT][4], sx[MT][4];
+#pragma unroll
+    for (int v = 0; v < V; v++)
+#pragma unroll
+        for (int t = 0; t < 4; t++)
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[v][t][mt][e] = 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) sx[mt][e] = 0.0f;
+
+    // Same fold as the register-streaming kernel: even tiles carry 1024 + q, odd tiles 1024 + 16 q.
+    auto fold = [&]() {
+#pragma unroll
+        for (int v = 0; v < V; v++) {
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                float s0, s1;
+                if (sc16) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&sraw[v][t]));
+                    const float b0 = __uint_as_float(sraw[v][t] << 16), b1 = __uint_as_float(sraw[v][t] & 0xFFFF0000u);
+                    s0 = is_f16 ? f.x : b0;
+                    s1 = is_f16 ? f.y : b1;
+                } else {
+                    const size_t n0 = (size_t)(jbase + v) * 8 + 2 * t;
+                    s0 = reinterpret_cast<const float *>(p.scales)[(size_t)grp * p.n + n0];
+                    s1 = reinterpret_cast<const float *>(p.scales)[(size_t)grp * p.n + n0 + 1];
+                }
+                const uint32_t zq = zw[v] >> (4 * t);
+                const float off = (t & 1) ? 64.0f : 1024.0f;
+                const float u0 = s0 * (off + (float)(zq & 0xFu)), u1 = s1 * (off + (float)((zq >> 16) & 0xFu));
+                const float a0 = (t & 1) ? s0 * 0.0625f : s0, a1 = (t & 1) ? s1 * 0.0625f : s1;
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    float(&a4)[4] = acc[v][t][mt];
+                    float4 &slot = mine[((v * 4 + t) * MT + mt) * 32];
+                    float4 t4 = slot;
+                    t4.x = fmaf(a0, a4[0], fmaf(-u0, sx[mt][0], t4.x));
+                    t4.y = fmaf(a0, a4[1], fmaf(-u0, sx[mt][1], t4.y));
+                    t4.z = fmaf(a1, a4[2], fmaf(-u1, sx[mt][0], t4.z));
+                    t4.w = fmaf(a1, a4[3], fmaf(-u1, sx[mt][1], t4.w));
+                    slot = t4;
+                    a4[0] = a4[1] = a4[2] = a4[3] = 0.0f;
+                }
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) sx[mt][0] = sx[mt][1] = sx[mt][2] = sx[mt][3] = 0.0f;
+    };
+
+    const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u}; // f16 1.0
+    const __half *xw[MT];
+    int xstep[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        const bool real = 8 * mt + g < m_loc;
+        xw[mt] = real ? xs + (size_t)(8 * mt + g) * xrow + warp * steps * 16 + 4 * c : reinterpret_cast<const __half *>(zeros);
+        xstep[mt] = real ? 16 : 0;
+    }
+    int to_fold = min(steps, gsteps - (step_beg % gsteps));
+    const uint32_t lane_off = (uint32_t)c * 64 + g * 8;
+
+    int slot = 0, phase = 0, done = 0;
+    for (int it = 0; it < boxes; it++) {
+        if (!mbar_wait(bar0 + 8 * slot, phase, &g_awq_gemv_flag, 1)) break;
+        const unsigned char *st = ring + (size_t)slot * GT_STAGE_BYTES + lane_off;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            uint32_t w[4][V], xb[MT][2];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint2 t2 = *reinterpret_cast<const uint2 *>(st + (h * 16 + 4 * i) * 64);
+                w[i][0] = t2.x; w[i][1] = t2.y;
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                const uint2 t2 = *reinterpret_cast<const uint2 *>(xw[mt]);
+                xw[mt] += xstep[mt];
+                xb[mt][0] = t2.x; xb[mt][1] = t2.y;
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) mma_f16_16816_awq(sx[mt], ones, xb[mt]);
+#pragma unroll
+            for (int v = 0; v < V; v++) {
+                const uint32_t pa[4] = {gather_byte<0>(w[0][v], w[1][v]), gather_byte<1>(w[0][v], w[1][v]),
+                                        gather_byte<2>(w[0][v], w[1][v]), gather_byte<3>(w[0][v], w[1][v])};
+                const uint32_t pb[4] = {gather_byte<0>(w[2][v], w[3][v]), gather_byte<1>(w[2][v], w[3][v]),
+                                        gather_byte<2>(w[2][v], w[3][v]), gather_byte<3>(w[2][v], w[3][v])};
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    const uint32_t mk = (t & 1) ? mask_hi : mask_lo;
+                    const uint32_t a[4] = {and_or(pa[t >> 1], mk, kmagic), and_or(pa[2 + (t >> 1)], mk, kmagic),
+                                           and_or(pb[t >> 1], mk, kmagic), and_or(pb[2 + (t >> 1)], mk, kmagic)};
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) mma_f16_16816_awq(acc[v][t][mt], a, xb[mt]);
+                }
+            }
+            done += 1;
+            if (--to_fold == 0) {
+                fold();
+                if (done < steps) {
+                    grp += 1;
+                    fetch_group(grp);
+                    to_fold = min(gsteps, steps - done);
+                }
+            }
+        }
+        __syncwarp(); // every lane has read the slot
+        if (lane == 0 && it + S < boxes) {
+            mbar_arrive_expect_tx(bar0 + 8 * slot, GT_STAGE_BYTES);
+            tma_load_2d(ring_addr + slot * GT_STAGE_BYTES, &wmap, bar0 + 8 * slot, jtile, step_beg * 16 + (it + S) * GT_ROWS);
+        }
+        if (++slot == S) { slot = 0; phase ^= 1; }
+    }
+    GV_CTA(2);
+    // Reduction: every CTA adds its KW warp slices (ascending k) and sends the sum of tile t to the CTA
+    // that owns it (t % nranks); after one cluster barrier the owner adds the nranks partial sums in
+    // rank order (ascending k again) and stores. Nobody reads another CTA's memory, so a CTA may leave
+    // right after the barrier.
+    constexpr int NT = NACC / 4;
+    const int LT = (NT + nranks - 1) / nranks;
+    cg::cluster_group cluster = cg::this_cluster();
+    __syncthreads();
+    if (nranks > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); // every CTA of the cluster has started
+    for (int o = tid; o < NT * 32; o += KW * 32) {
+        const int tile = o >> 5, ol = o & 31;
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+        for (int ks = 0; ks < KW; ks++) {
+            const float4 pv = red[((size_t)ks * NT + tile) * 32 + ol];
+            sum.x += pv.x; sum.y += pv.y; sum.z += pv.z; sum.w += pv.w;
+        }
+        const int owner = tile % nranks, lt = tile / nranks;
+        float4 *dst = nranks > 1 ? cluster.map_shared_rank(inbox, owner) : inbox;
+        dst[((size_t)rank * LT + lt) * 32 + ol] = sum;
+    }
+    if (nranks > 1) cluster.sync(); else __syncthreads();
+    GV_CTA(3);
+    for (int o = tid; o < LT * 32; o += KW * 32) {
+        const int lt = o >> 5, ol = o & 31;
+        const int tile = lt * nranks + rank;
+        if (tile >= NT) continue;
+        const int mt = tile % MT, vt = tile / MT, t = vt & 3, v = vt >> 2;
+        const int og = ol >> 2, oc = ol & 3;
+        const int word = jtile + og * V + v;
+        const int row = 8 * mt + 2 * oc;
+        if (row < m_loc) {
+            float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int q = 0; q < nranks; q++) {
+                const float4 pv = inbox[((size_t)q * LT + lt) * 32 + ol];
+                sum.x += pv.x; sum.y += pv.y; sum.z += pv.z; sum.w += pv.w;
+            }
+            const size_t col = (size_t)word * 8 + 2 * t;
+            float b0 = 0.0f, b1 = 0.0f;
+            if (p.bias) { b0 = load_as_f32(p.bias, p.bias_dtype, col); b1 = load_as_f32(p.bias, p.bias_dtype, col + 1); }
+            store_as(p.y, p.y_dtype, (size_t)(m0 + row) * p.n + col, sum.x + b0);
+            store_as(p.y, p.y_dtype, (size_t)(m0 + row) * p.n + col + 1, sum.z + b1);
+            if (row + 1 < m_loc) {
+                store_as(p.y, p.y_dtype, (size_t)(m0 + row + 1) * p.n + col, sum.y + b0);
+                store_as(p.y, p.y_dtype, (size_t)(m0 + row + 1) * p.n + col + 1, sum.w + b1);
+            }
+        }
+    }
+    GV_CTA(4);
+    GV_CTA(5);
+}
+
+template <int MT, int MINB>
+static int launch_awq_gemv_tma(AwqGemvParams p, int nranks, cudaStream_t stream)
+{
+    constexpr int NACC = 2 * 4 * MT * 4;
+    EncodeTiledFn fn = encode_tiled_fn();
+    OXQ_REQUIRE(fn != nullptr, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    CUtensorMap wmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)p.packed_out, (cuuint64_t)p.k};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.packed_out * 4};
+    const cuuint32_t box[2] = {16, GT_ROWS};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t *>(p.qweight), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+
+    const int m_cta = p.m < 8 * MT ? p.m : 8 * MT;
+    const size_t xbytes = (size_t)m_cta * (GT_KW * p.steps_per_cta * 16 + 16) * sizeof(__half) + 16;
+    const size_t inbox = (size_t)nranks * ceil_div(NACC / 4, nranks) * 32 * sizeof(float4);
+    const size_t red = (size_t)GT_KW * NACC * 32 * sizeof(float) + inbox;
+    const size_t fixed = xbytes + red + GT_KW * GT_MAX_STAGES * 8;
+    // As many ring slots as still let MINB CTAs share an SM (228 KB, 1 KB reserved per CTA), at most the boxes of a slice.
+    const size_t per_cta = (size_t)(228 * 1024) / MINB - 1024;
+    int stages = per_cta > fixed ? (int)((per_cta - fixed) / (GT_KW * GT_STAGE_BYTES)) : 0;
+    if (stages > GT_MAX_STAGES) stages = GT_MAX_STAGES;
+    if (stages > p.steps_per_cta / 2) stages = p.steps_per_cta / 2;
+    if (const char *env = tuning_env("OXQ_AWQ_GEMV_STAGES")) stages = atoi(env) < stages ? atoi(env) : stages;
+    if (stages < 2) return OXQ_ERR_UNSUPPORTED; // the caller falls back to the register-streaming kernel
+    p.stages = stages;
+    const size_t smem = (size_t)GT_KW * stages * GT_STAGE_BYTES + fixed;
+
+    auto kern = awq_gemv_tma_kernel<MT, MINB>;
+    static size_t configured[64] = {};
+    int device = 0;
+    OXQ_CUDA(cudaGetDevice(&device));
+    if (device >= 64 || configured[device] < smem) {
+        OXQ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (device < 64) configured[device] = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.packed_out / 16) * p.token_split, nranks, 1);
+    cfg.blockDim = dim3(GT_KW * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = nranks;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    allow_early_start(attr, cfg.numAttrs);
+    OXQ_CUDA(cudaLaunchKernelEx(&cfg, kern, p, wmap));
     return OXQ_OK;
 }
 
@@ -699,6 +1071,13 @@ OXQ_EXPORT int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight,
         if (ok && r != 0) {
             p.steps_per_cta = total_steps / (GK_KW * r);
             p.token_split = split;
+            // TMA ring when the shape tiles into 16-word boxes and two-step slots.
+            const char *tma_env = tuning_env("OXQ_AWQ_GEMV_TMA");
+            if (fv == 2 && p.packed_out % 16 == 0 && p.steps_per_cta % 2 == 0 && !(tma_env && tma_env[0] == '0')) {
+                // (a 16-token variant of the same kernel needs 156 registers and 80 KB per CTA: two waves, slower)
+                const int rc = mtc == 1 ? launch_awq_gemv_tma<1, 4>(p, r, st) : OXQ_ERR_UNSUPPORTED;
+                if (rc != OXQ_ERR_UNSUPPORTED) return rc;
+            }
             if (mtc == 1 && fv == 4) return launch_awq_gemv_group<1, 4, 2, 2>(p, r, st);
             if (mtc == 1 && fv == 2 && depth == 2 && minb == 6) return launch_awq_gemv_group<1, 2, 2, 6>(p, r, st);
             if (mtc == 1 && fv == 2 && depth == 2) return launch_awq_gemv_group<1, 2, 2, 4>(p, r, st);
@@ -730,3 +1109,25 @@ OXQ_EXPORT int oxq_awq_gemv(const void *x, int x_dtype, const uint32_t *qweight,
     if (mt == 2 && v == 2) return launch_awq_gemv<2, 2, NW>(p, ksplit, st);
     return launch_awq_gemv<4, 1, NW>(p, ksplit, st);
 }
+
+OXQ_EXPORT int oxq_awq_gemv_check(void *stream)
+{
+    clear_error();
+    OXQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    int flag = 0;
+    OXQ_CUDA(cudaMemcpyFromSymbol(&flag, g_awq_gemv_flag, sizeof(int)));
+    if (flag != 0) { // report once
+        const int zero = 0;
+        OXQ_CUDA(cudaMemcpyToSymbol(g_awq_gemv_flag, &zero, sizeof(int)));
+    }
+    OXQ_REQUIRE(flag == 0, OXQ_ERR_DEVICE_FLAG,
+                "oxq_awq_gemv: a bounded wait on a weight box ran out in a call since the last check (outputs of those calls are not valid)");
+    return OXQ_OK;
+}
+
+#ifdef OXQ_TUNING
+OXQ_EXPORT int oxq_gv_cta_read(unsigned long long *host_out)
+{
+    return cudaMemcpyFromSymbol(host_out, g_gv_cta, sizeof(unsigned long long) * 1024 * 8) == cudaSuccess ? 0 : -6;
+}
+#endif

@@ -626,23 +626,6 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---- host side ---------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
 // 2-D bf16 row-major [rows, cols] tensor, box [box_rows, 64 cols], 128-byte swizzle, zero fill.
 static int make_map_bf16(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows)
 {

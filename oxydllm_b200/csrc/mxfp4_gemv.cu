@@ -61,6 +61,8 @@ template <int MT, int D>
 __global__ void __launch_bounds__(256, MT == 1 ? 4 : MT == 2 ? 3 : 2) mxfp4_gemv_kernel(const Mx4GemvParams p)
 {
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
+    if (p.pair_expert) pdl_wait(); // the routing table comes from the kernel before this one
     cg::cluster_group cluster = cg::this_cluster();
     const int nrt = p.row_tiles, ks = (int)gridDim.y, rank = (int)blockIdx.y; // cluster = the y extent of the grid
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
@@ -106,6 +108,7 @@ __global__ void __launch_bounds__(256, MT == 1 ? 4 : MT == 2 ? 3 : 2) mxfp4_gemv
         }
 
     if (tid < 4) zeros[tid] = 0.0f;
+    if (!p.pair_expert) pdl_wait(); // x may come from the kernel before this one; the first weights are already on their way
     for (int row = 0; row < m_loc; row++) {
         const uint2 *src = reinterpret_cast<const uint2 *>(xin + (size_t)(m0 + row) * p.k + k_cta);
         uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
@@ -209,13 +212,14 @@ template <int MT, int D> static int launch_mx4(const Mx4GemvParams &p, int ks, c
     cfg.blockDim = dim3(nw * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = ks;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ks > 1 ? 1 : 0;
+    allow_early_start(attr, cfg.numAttrs);
     OXQ_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
     return OXQ_OK;
 }

@@ -132,4 +132,25 @@ __device__ __forceinline__ float bf16_hi_f32(uint32_t w) { return __uint_as_floa
 
 #endif // __CUDACC__
 
+// ---- programmatic dependent launch --------------------------------------------------------------
+// A decode kernel spends a good part of its few microseconds starting up and draining. Launched with
+// allow_early_start(), a kernel may become resident while the previous kernel on the stream is still
+// running; it calls pdl_launch_dependents() at entry (so that its own successor may do the same) and
+// pdl_wait() before it touches anything a previous kernel may write or still read (x, y, routing
+// tables). Only reads of weights, scales and zero points, which no kernel writes, go in front of
+// the wait. pdl_wait() returns when the previous kernel has completed and its writes are visible;
+// without the launch attribute both calls do nothing.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+inline void allow_early_start(cudaLaunchAttribute *attrs, unsigned int &count)
+{
+    if (const char *env = tuning_env("OXQ_PDL"))
+        if (env[0] == '0') return;
+    attrs[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[count].val.programmaticStreamSerializationAllowed = 1;
+    count += 1;
+}
+
 } // namespace oxq

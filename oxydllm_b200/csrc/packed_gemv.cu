@@ -61,6 +61,8 @@ __device__ __forceinline__ void stage_x(const PackedGemvParams &p, float *xs, fl
 template <int BITS, int MT>
 __global__ void __launch_bounds__(PG_WARPS * 32) gptq_gemv_kernel(const PackedGemvParams p)
 {
+    pdl_launch_dependents();
+    pdl_wait(); // x is staged first: only the start-up of the kernel overlaps the previous one
     constexpr int PF = 32 / BITS;
     constexpr uint32_t QMASK = (1u << BITS) - 1u;
     extern __shared__ __align__(16) float smem_f[];
@@ -132,6 +134,8 @@ __global__ void __launch_bounds__(PG_WARPS * 32) gptq_gemv_kernel(const PackedGe
 template <int MT>
 __global__ void __launch_bounds__(PG_WARPS * 32) w8a16_gemv_kernel(const PackedGemvParams p)
 {
+    pdl_launch_dependents();
+    pdl_wait(); // x is staged first: only the start-up of the kernel overlaps the previous one
     extern __shared__ __align__(16) float smem_f[];
     const int groups = p.k / p.group_size;
     float *xs = smem_f, *gsum = xs + (size_t)MT * p.k, *red = gsum + MT * groups;
@@ -228,6 +232,8 @@ constexpr int GQ_TILES = 2; // 16-column tiles per warp: a CTA covers 32 output 
 
 __global__ void __launch_bounds__(PG_WARPS * 32) gptq4_gemv_mma_kernel(const PackedGemvParams p)
 {
+    pdl_launch_dependents();
+    pdl_wait(); // x is staged first: only the start-up of the kernel overlaps the previous one
     extern __shared__ __align__(16) unsigned char smem_b[];
     const int groups = p.k / p.group_size;
     const int mloc = min(8, p.m - p.y_row0);
@@ -407,8 +413,16 @@ static int launch_packed(Kern kern, const char *name, PackedGemvParams p, int mt
     const int ctas = ceil_div(p.n, cols_per_cta);
     for (int row0 = 0; row0 < p.m; row0 += mt) {
         p.y_row0 = row0;
-        kern<<<ctas, PG_WARPS * 32, smem, st>>>(p);
-        cudaError_t e = cudaGetLastError();
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(ctas, 1, 1);
+        cfg.blockDim = dim3(PG_WARPS * 32, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        cfg.attrs = attr;
+        cfg.numAttrs = 0;
+        allow_early_start(attr, cfg.numAttrs);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
         if (e != cudaSuccess) return fail(OXQ_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
     }
     return OXQ_OK;

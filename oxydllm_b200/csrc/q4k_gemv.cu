@@ -107,6 +107,7 @@ template <int MT, bool FIVE>
 __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4kGemvParams p)
 {
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
     cg::cluster_group cluster = cg::this_cluster();
     const int nrt = p.row_tiles, kwn = p.k_warps, ks = (int)gridDim.y, rank = (int)blockIdx.y; // cluster = grid y extent
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
@@ -144,6 +145,7 @@ __global__ void __launch_bounds__(256, MT == 1 ? 2 : 1) q4k_gemv_kernel(const Q4
     if (tid < 4) zeros[tid] = 0.0f;
     for (int idx = tid; idx < 8 * MT * (kl >> 5); idx += blockDim.x) sx[idx] = 0.0f; // rows without a token
     __syncthreads();
+    pdl_wait(); // x may come from the kernel before this one; the first weights are already on their way
     for (int row = 0; row < m_loc; row++) {
         const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)(m0 + row) * p.k + k_cta);
         uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
@@ -300,13 +302,14 @@ template <int MT, bool FIVE> static int launch_q4k(const Q4kGemvParams &p, int k
     cfg.blockDim = dim3(nw * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = ks;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ks > 1 ? 1 : 0;
+    allow_early_start(attr, cfg.numAttrs);
     OXQ_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
     return OXQ_OK;
 }

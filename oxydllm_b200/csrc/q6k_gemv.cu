@@ -79,6 +79,7 @@ __device__ __forceinline__ float q6k_i8_to_f32(uint32_t byte)
 __global__ void __launch_bounds__(256, 3) q6k_gemv_kernel(const Q6kGemvParams p)
 {
     extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
     cg::cluster_group cluster = cg::this_cluster();
     const int nrt = p.row_tiles, ks = (int)gridDim.y, rank = (int)blockIdx.y; // cluster = the y extent of the grid
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
@@ -111,6 +112,7 @@ __global__ void __launch_bounds__(256, 3) q6k_gemv_kernel(const Q6kGemvParams p)
     if (tid < 4) zeros[tid] = 0.0f;
     for (int idx = tid; idx < (kl >> 4) * 8; idx += blockDim.x) sx[idx] = 0.0f;
     __syncthreads();
+    pdl_wait(); // x may come from the kernel before this one; the first weights are already on their way
     for (int row = 0; row < m_loc; row++) {
         const uint2 *src = reinterpret_cast<const uint2 *>(p.x + (size_t)(m0 + row) * p.k + k_cta);
         uint2 *dst = reinterpret_cast<uint2 *>(xs + (size_t)row * xrow);
@@ -227,13 +229,14 @@ static int launch_q6k(const Q6kGemvParams &p, int ks, cudaStream_t st)
     cfg.blockDim = dim3(nw * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = ks;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ks > 1 ? 1 : 0;
+    allow_early_start(attr, cfg.numAttrs);
     OXQ_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
     return OXQ_OK;
 }

@@ -207,6 +207,53 @@ def test_awq_gemv_leading_dims_and_determinism(cuda):
     assert torch.equal(y1[0], y0.reshape(6, n)[0])  # batch-size invariant summation order per row
 
 
+@pytest.mark.parametrize("m", [1, 5, 8])
+def test_awq_gemv_dependent_launches_back_to_back(cuda, m):
+    # The decode kernel lets the next launch on the stream start early and orders itself behind the
+    # previous one before it reads x: a chain y -> x of launches without host synchronisation (eager and
+    # replayed from a CUDA graph) must give the bits of the same chain with a synchronisation per step.
+    from oxydllm_b200 import _lib
+    k = n = 2048
+    layers = []
+    for seed in range(5):
+        qw, qz, sc = synth.awq_layer(k, n, 128, seed=40 + seed)
+        layers.append(L.PackedQuantLinear(L.QuantWeight.new_awq(4, words(qw), words(qz), dev(sc))))
+    x0 = dev(synth.activations(m, k, seed=3), torch.bfloat16)
+
+    def chain(sync):
+        x = x0
+        for lin in layers:
+            x = lin.forward(x)
+            if sync:
+                torch.cuda.synchronize()
+        return x
+
+    want = chain(True)
+    assert torch.isfinite(want.float()).all()
+    for _ in range(3):
+        assert torch.equal(chain(False), want)
+    bufs = [torch.empty((m, n), dtype=torch.bfloat16, device="cuda") for _ in layers]
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        def run():
+            x = x0
+            for lin, y in zip(layers, bufs):
+                lin._gemv(x, y, m)
+                x = y
+        run()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            run()
+        for _ in range(3):
+            bufs[-1].zero_()
+            graph.replay()
+            stream.synchronize()
+            assert torch.equal(bufs[-1], want)
+    torch.cuda.current_stream().wait_stream(stream)
+    assert _lib.load().oxq_awq_gemv_check(None) == 0
+
+
 def test_awq_prefill_sized_batch_matches_oracle(cuda):
     k, n, g, m = 512, 256, 128, 70
     qw, qz, sc = synth.awq_layer(k, n, g, seed=11)
