@@ -133,7 +133,7 @@ def run_gpu(args):
     def sweep(ms=M_SWEEP):
         for m in ms:
             for lin in layers:
-                lin._gemv(xs[m], ys[m], m)
+                lin.forward(xs[m], out=ys[m])  # the operator's own dispatch: split-k GEMV up to 16 tokens, fused tcgen05 kernel at 32
 
     def make_graph(fn):
         fn()
@@ -258,7 +258,7 @@ def run_gpu(args):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
                      "traffic_source": "recorded ncu capture of one m = 1 launch (dram read + write bytes)",
-                     "kernel": "awq_gemv_group_kernel (every m of the sweep; m = 32 as four 8-token CTAs per n tile)",
+                     "kernel": "awq_gemv_tma_kernel (m <= 8), awq_gemv_group_kernel (m = 16), awq_fused_tc_kernel (m = 32)",
                      "peak_kind": f"{peak_kind} copy bandwidth", "per_m": per_m},
         "clocks": clocks,
     }

@@ -22,6 +22,11 @@ int fp8_dequant_rows_bf16(const uint8_t *weight, const float *scale_inv, int s_i
 int mxfp4_dequant_rows_bf16(const uint8_t *blocks, const uint8_t *scales, __nv_bfloat16 *out, int k, int n_off,
                             int n_cnt, cudaStream_t st);
 bool gguf_block_layout_host(int ggml_type, int &bel, int &bby);
+bool awq_fused_supported(int m, int k, int n, int group_size, int scales_dtype, const void *x, const void *qweight,
+                         const void *scales);
+int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype, const void *bias,
+                     int bias_dtype, void *y, int y_dtype, int m, int k, int n, int group_size, int col_base, int ldy,
+                     int *flag, cudaStream_t st);
 
 constexpr size_t WS_HEADER = 256;                // flag word + padding, keeps the slab 256-byte aligned
 constexpr size_t SLAB_LIMIT_BYTES = 128u << 20;  // dequantized rows held at once (whole weight if it fits)
@@ -144,6 +149,9 @@ OXQ_EXPORT int oxq_awq_gemm(const void *x, int x_dtype, const uint32_t *qweight,
     GemmCommon c;
     int rc = prepare("oxq_awq_gemm", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n, workspace, workspace_bytes, stream);
     if (rc) return rc;
+    // Up to 256 tokens: unpack inside the tensor-core kernel, no dense copy of the weight.
+    if (awq_fused_supported(m, k, n, group_size, scales_dtype, x, qweight, scales))
+        return awq_fused_matmul(x, qweight, qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n, group_size, 0, n, c.flag, c.st);
     return run_slabs(c, [&](int n_off, int cnt) {
         return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, n_off, cnt, c.st);
     });

@@ -24,6 +24,10 @@ _DT = {torch.float32: _lib.OXQ_F32, torch.float16: _lib.OXQ_F16, torch.bfloat16:
 GEMV_MAX_M = 32
 #: The same for the GPTQ and 8-bit GEMVs (one 8-token chunk of the reference's batched GEMV, linear.rs:461-478).
 PACKED_SIMT_GEMV_MAX_M = 8
+# AWQ 4-bit layers whose shape the fused unpack + tcgen05 kernel serves (out_features % 128, in_features % 64,
+# group size % 64, 16-bit scales) leave the split-k GEMV at this batch: measured on a 4096 x 14336 layer the GEMV
+# takes 25 us at 16 tokens and 47 us at 32, the fused kernel about 34 us for any batch up to 64.
+AWQ_FUSED_MIN_M = 17
 
 
 def _dt(t: torch.dtype) -> int:
@@ -262,8 +266,13 @@ class PackedQuantLinear:
 
     def gemv_max_m(self) -> int:
         """Largest batch the decode kernels take before the tensor-core GEMM is the better tool: 32 for the
-        4-bit AWQ tensor-core GEMV, 8 (one chunk of the reference's batched GEMV) for GPTQ and 8-bit."""
-        return GEMV_MAX_M if (self.pack_dim == "out" and self.bits == 4) else PACKED_SIMT_GEMV_MAX_M
+        4-bit AWQ tensor-core GEMV (16 where the fused unpack + tcgen05 kernel takes over), 8 (one chunk of the
+        reference's batched GEMV) for GPTQ and 8-bit."""
+        if self.pack_dim == "out" and self.bits == 4:
+            fused = (self.out_features % 128 == 0 and self.in_features % 64 == 0 and self.group_size % 64 == 0
+                     and self.scales.dtype in (torch.float16, torch.bfloat16))
+            return AWQ_FUSED_MIN_M - 1 if fused else GEMV_MAX_M
+        return PACKED_SIMT_GEMV_MAX_M
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``out``: optional preallocated contiguous ``[m, out_features]`` result tensor of x's dtype and device."""
