@@ -6,8 +6,8 @@
 //                       as far ahead as the ring allows: this ring is what is in flight from HBM;
 //   warp 2 (one lane)   TMA: the stage's tile of x ([tokens, 64] bf16, 128-byte swizzle) into one of the
 //                       two or four operand slots;
-//   warps 4..19         unpack, two teams of eight warps taking stages in turn: every thread turns four
-//                       packed words into 4 x 8 bf16 weights, the same bits the dequantization kernel
+//   warps 4..19         unpack, two teams of eight warps taking rounds of two stages in turn: every thread
+//                       turns four packed words per stage into 4 x 8 bf16 weights, the same bits the dequantization kernel
 //                       writes ((128 + q) - (128 + z) exactly in bf16, times the scale with one
 //                       rounding: see split_scales), and stores each word's
 //                       eight out features, which are neighbours in memory in the MN-major operand
@@ -26,17 +26,21 @@ namespace oxq {
 
 constexpr int FT_ROWS = 128;
 constexpr int FT_BK = 64;
-constexpr int FT_TEAM_WARPS = 8;                 // warps that unpack one stage together (256 threads x 4 words)
-constexpr int FT_TEAMS = 2;                      // teams take stages in turn, so one team's store-fence-arrive tail overlaps the other's unpack
-constexpr int FT_UNPACK_WARPS = FT_TEAM_WARPS * FT_TEAMS;
+constexpr int FT_UNPACK_WARPS = 16;
+constexpr int FT_TEAMS = 2;                      // teams of unpack warps take rounds in turn (measured: 29 us with two teams, 33 us with one)
+constexpr int FT_TEAM_WARPS = FT_UNPACK_WARPS / FT_TEAMS;
+constexpr int FT_WORDS = FT_BK * 16 / (FT_TEAM_WARPS * 32); // packed words per thread and stage
+constexpr int FT_ROUND = 2;                      // stages per round: polls, proxy fence and arrivals are paid once per round
+constexpr int FT_ROUND_SLOTS = 2;                // rounds of operand slots: S = FT_ROUND * FT_ROUND_SLOTS, a multiple of the teams' rounds
 constexpr int FT_THREADS = (4 + FT_UNPACK_WARPS) * 32;
 constexpr int FT_BOX_BYTES = FT_BK * 16 * 4;      // 64 input rows x 16 packed words
 constexpr int FT_ZERO_BYTES = 64, FT_SCALE_BYTES = 256; // the box's group: 16 zero-point words, 128 16-bit scales
 constexpr int FT_RAW_BYTES = FT_BOX_BYTES + 384;  // ring slot: box | zero points | scales | pad to 128 bytes
 constexpr int FT_A_BYTES = FT_ROWS * FT_BK * 2;
-constexpr int FT_MAX_STAGES = 4;                 // operand slots (A tile + x tile)
+constexpr int FT_MAX_STAGES = FT_ROUND * FT_ROUND_SLOTS; // operand slots (A tile + x tile)
 constexpr int FT_MAX_RAW = 32;                   // ring slots of packed boxes: what is in flight from HBM
 constexpr int FT_NUM_BARS = 2 * FT_MAX_RAW + 3 * FT_MAX_STAGES + 1;
+static_assert(FT_ROUND_SLOTS % FT_TEAMS == 0 && FT_MAX_RAW % (FT_ROUND * FT_TEAMS) == 0, "a slot must always meet the same team");
 constexpr int FT_MAX_M = 256;
 constexpr int FT_SMEM_BUDGET = 227 * 1024;
 
@@ -56,6 +60,7 @@ struct FusedParams {
     int bias_dtype, y_dtype;
     int m, mpad, k, n, group_size, packed_out;
     int stages, raw_slots, stage_bytes, tmem_cols;
+    int gshift;        // log2(stages per quantization group)
     int col_base, ldy; // y column of out feature 0 and the row pitch of y in elements
     int *flag;
 };
@@ -66,6 +71,28 @@ __device__ __forceinline__ uint64_t ft_a_desc(uint32_t smem_addr)
 {
     return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)(8192 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint32_t ft_and_or(uint32_t v, uint32_t mask, uint32_t magic) // (v & mask) | magic
+{
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(v), "r"(mask), "r"(magic));
+    return r;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4 &v)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 // D f32, A bf16 MN-major, B bf16 K-major.
 __device__ __forceinline__ uint32_t ft_idesc(int n)
@@ -119,7 +146,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---- TMA, packed words: runs as far ahead of the unpack teams as the ring of boxes allows ------------
+        // ---- TMA, packed words: runs as far ahead of the unpack warps as the ring of boxes allows ------------
         if (elect_one()) {
             int r = 0;
             uint32_t ph = 0;
@@ -175,12 +202,12 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         }
     } else if (warp >= 4) {
         // ---- unpack ------------------------------------------------------------------------------------
-        // S and R are multiples of the number of teams, so a slot always meets the same team: every waiter
-        // of a barrier sees each of its phases.
+        // A slot always meets the same team (the slot counts are multiples of the teams' rounds), so every waiter of a
+        // barrier sees each of its phases.
         const int team = (warp - 4) / FT_TEAM_WARPS;
-        const int ut = (threadIdx.x - 128) % (FT_TEAM_WARPS * 32); // 0..255 inside the team
-        const int j = ut & 15, r0 = ut >> 4;  // word column (8 out features) and first of this thread's four rows
-        const int gstages = p.group_size / FT_BK;
+        const int ut = (threadIdx.x - 128) % (FT_TEAM_WARPS * 32);
+        constexpr int ROW_STEP = FT_BK / FT_WORDS; // this thread's rows of a stage: r0, r0 + ROW_STEP, ...
+        const int j = ut & 15, r0 = ut >> 4;       // word column (8 out features) and first row
         // A scale s (f16: 11 significant bits) is used as s_hi + s_lo, two bf16 values that
         // add up to it exactly; for d = q - z (an integer of at most 4 bits) d * s_lo is exact in bf16 and
         // fma(d, s_hi, d * s_lo) rounds the exact d * s once: the bits of bf16(f32(d) * f32(s)).
@@ -202,69 +229,83 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         };
         int cur_qg = -1;
         __nv_bfloat162 zp[4], shi[4], slo[4];
-        // byte offset of this thread's first 16-byte chunk inside the A slot; rows r0 + 16 i are 2 KB apart
+        uint32_t nib_mask, nib_magic; // in registers, opaque to constant propagation: one LOP3 per pair instead of two
+        asm volatile("mov.b32 %0, 0x000F000F;\n\tmov.b32 %1, 0x43004300;" : "=r"(nib_mask), "=r"(nib_magic));
+        // byte offset of this thread's first 16-byte chunk inside the A slot; rows ROW_STEP apart are ROW_STEP * 128 bytes apart
         const uint32_t a_off = (uint32_t)(j >> 3) * 8192u + (uint32_t)(r0 >> 3) * 1024u + (uint32_t)(r0 & 7) * 128u +
                                (uint32_t)(((j & 7) ^ (r0 & 7)) << 4);
         const uint32_t raw_idx = raw_base + (uint32_t)(r0 * 16 + j) * 4u;
-        int s = team % S, r = team % R;
-        uint32_t ph = (uint32_t)(team / S) & 1u, rph = (uint32_t)(team / R) & 1u;
+        // FT_ROUND consecutive stages per round: the barrier polls, the proxy fence and the arrivals, which
+        // cost more than the arithmetic of one stage, are paid once per round. Shared memory
+        // is addressed with 32-bit shared-space addresses throughout (no generic-pointer arithmetic in the loop).
+        const uint32_t a_addr = base + a_off;                           // first 16-byte chunk in slot 0
+        const uint32_t box_addr0 = base + raw_idx;                      // this thread's first word in ring slot 0
+        const uint32_t aux_addr0 = base + raw_base + FT_BOX_BYTES;      // zero points of ring slot 0
+        int r = FT_ROUND * team;                                       // first ring slot of the round
+        uint32_t my_s = (uint32_t)(FT_ROUND * team) % (uint32_t)S;      // first operand slot of the round
+        uint32_t ph = ((uint32_t)(FT_ROUND * team) / (uint32_t)S) & 1u, rph = 0; // phases of the operand-slot and ring barriers
         bool ok = true;
-        for (int it = team; it < nk; it += FT_TEAMS) {
-            // the box: four words into registers, then the ring slot goes back to the producer
-            if (ut == 0) FT_TRACE(7, it);
-            ok = mbar_wait(rawfull_bar(r), rph, p.flag, 3);
+        for (int it0 = FT_ROUND * team; it0 < nk; it0 += FT_ROUND * FT_TEAMS) {
+            if (ut == 0) FT_TRACE(7, it0);
+            // all polls of the round first (they do not depend on each other), the bounded waits only where one failed
+            bool t0 = mbar_test(rawfull_bar(r), rph), t1 = mbar_test(rawfull_bar(r + 1), rph);
+            bool t2 = true, t3 = true;
+            if (it0 >= S) { // the operand slots are free once the MMAs of the stages that used them last have completed
+                t2 = mbar_test(empty_bar(my_s), ph ^ 1u);
+                t3 = mbar_test(empty_bar(my_s + 1), ph ^ 1u);
+            }
+            if (!t0) ok = mbar_wait(rawfull_bar(r), rph, p.flag, 3);
+            if (ok && !t1) ok = mbar_wait(rawfull_bar(r + 1), rph, p.flag, 3);
+            if (ok && !t2) ok = mbar_wait(empty_bar(my_s), ph ^ 1u, p.flag, 7);
+            if (ok && !t3) ok = mbar_wait(empty_bar(my_s + 1), ph ^ 1u, p.flag, 7);
             if (!ok) break;
-            if (ut == 0) FT_TRACE(3, it);
-            const unsigned char *raw = base_ptr + raw_idx + (size_t)r * FT_RAW_BYTES;
-            uint32_t w[4];
+            if (ut == 0) FT_TRACE(3, it0);
 #pragma unroll
-            for (int i = 0; i < 4; i++) w[i] = *reinterpret_cast<const uint32_t *>(raw + i * 16 * 64);
-            if (ut == 0) FT_TRACE(8, it);
-            const int qg = it / gstages;
-            if (qg != cur_qg) { // a new quantization group: its zero points and scales sit behind the box
-                cur_qg = qg;
-                const unsigned char *aux = base_ptr + raw_base + (size_t)r * FT_RAW_BYTES + FT_BOX_BYTES;
-                const uint32_t zw = *reinterpret_cast<const uint32_t *>(aux + 4 * j);
-                split_scales(*reinterpret_cast<const uint4 *>(aux + FT_ZERO_BYTES + 16 * j), shi, slo);
+            for (int h = 0; h < FT_ROUND; h++) {
+                const uint32_t ring = (uint32_t)(r + h) * FT_RAW_BYTES;
+                uint32_t w[FT_WORDS];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t v = ((zw >> (4 * i)) & 0x000F000Fu) | 0x43004300u; // bf16 pair (128 + z, 128 + z')
-                    zp[i] = *reinterpret_cast<const __nv_bfloat162 *>(&v);
+                for (int i = 0; i < FT_WORDS; i++) w[i] = lds32(box_addr0 + ring + i * ROW_STEP * 64);
+                const int qg = (it0 + h) >> p.gshift;
+                if (qg != cur_qg) { // a new quantization group: its zero points and scales sit behind the box
+                    cur_qg = qg;
+                    const uint32_t zw = lds32(aux_addr0 + ring + 4 * j);
+                    split_scales(lds128(aux_addr0 + ring + FT_ZERO_BYTES + 16 * j), shi, slo);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const uint32_t v = ((zw >> (4 * i)) & 0x000F000Fu) | 0x43004300u; // bf16 pair (128 + z, 128 + z')
+                        zp[i] = *reinterpret_cast<const __nv_bfloat162 *>(&v);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < FT_WORDS; i++) {
+                    uint4 o;
+                    uint32_t *ov = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) { // nibbles q and q + 4 are out features 2q and 2q + 1 of the word
+                        const uint32_t v = ft_and_or(w[i] >> (4 * q), nib_mask, nib_magic); // bf16 pair (128 + q, 128 + q')
+                        const __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&v), zp[q]); // q - z, exact
+                        const __nv_bfloat162 b2 = __hfma2(d, shi[q], __hmul2(d, slo[q])); // s_lo is zero for bf16 scales
+                        ov[q] = *reinterpret_cast<const uint32_t *>(&b2);
+                    }
+                    sts128(a_addr + (my_s + h) * p.stage_bytes + i * ROW_STEP * 128, o);
                 }
             }
-            if (ut == 0) FT_TRACE(9, it);
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(rawempty_bar(r)) : "memory");
-            if (ut == 0) FT_TRACE(10, it);
-            // the operand slot is free once the MMAs of the stage that used it last have completed
-            if (it >= S) {
-                ok = mbar_wait(empty_bar(s), ph ^ 1u, p.flag, 7);
-                if (!ok) break;
-            }
-            unsigned char *slot = base_ptr + (size_t)s * p.stage_bytes;
-            if (ut == 0) FT_TRACE(6, it);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                uint4 o;
-                uint32_t *ov = reinterpret_cast<uint32_t *>(&o);
-#pragma unroll
-                for (int q = 0; q < 4; q++) { // nibbles q and q + 4 are out features 2q and 2q + 1 of the word
-                    const uint32_t v = ((w[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u; // bf16 pair (128 + q, 128 + q')
-                    const __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&v), zp[q]); // q - z, exact
-                    const __nv_bfloat162 b2 = __hfma2(d, shi[q], __hmul2(d, slo[q]));
-                    ov[q] = *reinterpret_cast<const uint32_t *>(&b2);
-                }
-                *reinterpret_cast<uint4 *>(slot + a_off + i * 2048) = o;
-            }
-            if (ut == 0) FT_TRACE(4, it);
+            if (ut == 0) FT_TRACE(4, it0);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the MMA
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready_bar(s)) : "memory");
-            if (ut == 0) FT_TRACE(5, it);
-            s += FT_TEAMS;
-            while (s >= S) { s -= S; ph ^= 1u; }
-            r += FT_TEAMS;
-            while (r >= R) { r -= R; rph ^= 1u; }
+            if (lane == 0) {
+#pragma unroll
+                for (int h = 0; h < FT_ROUND; h++) {
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ready_bar(my_s + h)) : "memory");
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(rawempty_bar(r + h)) : "memory");
+                }
+            }
+            if (ut == 0) FT_TRACE(5, it0);
+            my_s += FT_ROUND * FT_TEAMS;
+            if (my_s >= (uint32_t)S) { my_s -= (uint32_t)S; ph ^= 1u; }
+            r += FT_ROUND * FT_TEAMS;
+            if (r >= R) { r -= R; rph ^= 1u; }
         }
 
         // ---- epilogue: lane = out feature inside this warp's quarter of the accumulator rows -----------------
@@ -299,7 +340,8 @@ bool awq_fused_supported(int m, int k, int n, int group_size, int scales_dtype, 
 {
     if (const char *env = tuning_env("OXQ_AWQ_FUSED"))
         if (env[0] == '0') return false;
-    return m >= 1 && m <= FT_MAX_M && n % FT_ROWS == 0 && k % FT_BK == 0 && group_size % FT_BK == 0 &&
+    return m >= 1 && m <= FT_MAX_M && n % FT_ROWS == 0 && k % (FT_BK * FT_ROUND) == 0 && group_size % FT_BK == 0 &&
+           (group_size & (group_size - 1)) == 0 &&
            (scales_dtype == OXQ_F16 || scales_dtype == OXQ_BF16) && aligned(x, 16) && aligned(qweight, 16) && aligned(scales, 16);
 }
 
@@ -314,16 +356,17 @@ int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qze
     p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
     p.m = m; p.mpad = (m + 15) / 16 * 16; p.k = k; p.n = n; p.group_size = group_size; p.packed_out = n / 8;
     p.col_base = col_base; p.ldy = ldy; p.flag = flag;
+    p.gshift = 0;
+    while ((FT_BK << p.gshift) < group_size) p.gshift += 1;
     p.stage_bytes = FT_A_BYTES + p.mpad * 128;
     const int fixed = 1024 + 8 * FT_NUM_BARS + 16;
     const int nk = k / FT_BK;
-    // Operand slots: four when that still leaves eight boxes in flight, else two; the rest of shared memory is the
-    // ring of packed boxes. Both counts are multiples of the number of unpack teams.
-    p.stages = (FT_SMEM_BUDGET - fixed - 8 * FT_RAW_BYTES) / p.stage_bytes >= 4 ? 4 : 2;
-    p.raw_slots = (FT_SMEM_BUDGET - fixed - p.stages * p.stage_bytes) / FT_RAW_BYTES / FT_TEAMS * FT_TEAMS;
+    // Four operand slots (two rounds of two stages); the rest of shared memory is the ring of packed boxes, a multiple of four.
+    p.stages = FT_MAX_STAGES;
+    p.raw_slots = (FT_SMEM_BUDGET - fixed - p.stages * p.stage_bytes) / FT_RAW_BYTES / FT_MAX_STAGES * FT_MAX_STAGES;
     if (p.raw_slots > FT_MAX_RAW) p.raw_slots = FT_MAX_RAW;
     if (const char *env = tuning_env("OXQ_AWQ_FUSED_RAW")) p.raw_slots = atoi(env) < p.raw_slots ? atoi(env) : p.raw_slots;
-    OXQ_REQUIRE(p.raw_slots >= FT_TEAMS && nk >= 1, OXQ_ERR_UNSUPPORTED, "awq_fused_matmul: no room for the ring of boxes");
+    OXQ_REQUIRE(p.raw_slots >= FT_MAX_STAGES && nk >= 1, OXQ_ERR_UNSUPPORTED, "awq_fused_matmul: no room for the ring of boxes");
     p.tmem_cols = 32;
     while (p.tmem_cols < p.mpad) p.tmem_cols *= 2;
     const size_t smem = (size_t)p.stages * p.stage_bytes + (size_t)p.raw_slots * FT_RAW_BYTES + fixed;

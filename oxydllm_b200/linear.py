@@ -24,9 +24,9 @@ _DT = {torch.float32: _lib.OXQ_F32, torch.float16: _lib.OXQ_F16, torch.bfloat16:
 GEMV_MAX_M = 32
 #: The same for the GPTQ and 8-bit GEMVs (one 8-token chunk of the reference's batched GEMV, linear.rs:461-478).
 PACKED_SIMT_GEMV_MAX_M = 8
-# AWQ 4-bit layers whose shape the fused unpack + tcgen05 kernel serves (out_features % 128, in_features % 64,
-# group size % 64, 16-bit scales) leave the split-k GEMV at this batch: measured on a 4096 x 14336 layer the GEMV
-# takes 25 us at 16 tokens and 47 us at 32, the fused kernel about 34 us for any batch up to 64.
+# AWQ 4-bit layers whose shape the fused unpack + tcgen05 kernel serves (out_features % 128, in_features % 128,
+# group size a power of two >= 64, 16-bit scales) leave the split-k GEMV at this batch: measured on a 4096 x 14336 layer the GEMV
+# takes 24 us at 16 tokens and 47 us at 32, the fused kernel 28 to 31 us for any batch up to 128.
 AWQ_FUSED_MIN_M = 17
 
 
@@ -269,7 +269,8 @@ class PackedQuantLinear:
         4-bit AWQ tensor-core GEMV (16 where the fused unpack + tcgen05 kernel takes over), 8 (one chunk of the
         reference's batched GEMV) for GPTQ and 8-bit."""
         if self.pack_dim == "out" and self.bits == 4:
-            fused = (self.out_features % 128 == 0 and self.in_features % 64 == 0 and self.group_size % 64 == 0
+            fused = (self.out_features % 128 == 0 and self.in_features % 128 == 0 and self.group_size % 64 == 0
+                     and self.group_size & (self.group_size - 1) == 0
                      and self.scales.dtype in (torch.float16, torch.bfloat16))
             return AWQ_FUSED_MIN_M - 1 if fused else GEMV_MAX_M
         return PACKED_SIMT_GEMV_MAX_M
