@@ -40,7 +40,7 @@ typedef enum { OXQ_F32 = 0, OXQ_F16 = 1, OXQ_BF16 = 2 } oxq_dtype;
 /* GGML block types, numbered as in GGUF files (candle GgmlDType; linear.rs:199-211). */
 typedef enum {
     OXQ_GGML_Q4_0 = 2, OXQ_GGML_Q4_1 = 3, OXQ_GGML_Q5_0 = 6, OXQ_GGML_Q5_1 = 7, OXQ_GGML_Q8_0 = 8,
-    OXQ_GGML_Q4_K = 12, OXQ_GGML_Q5_K = 13, OXQ_GGML_Q6_K = 14
+    OXQ_GGML_Q2_K = 10, OXQ_GGML_Q3_K = 11, OXQ_GGML_Q4_K = 12, OXQ_GGML_Q5_K = 13, OXQ_GGML_Q6_K = 14
 } oxq_ggml_type;
 
 const char *oxq_status_string(int status);

@@ -21,8 +21,9 @@ _SRC = os.path.join(_HERE, "oracle.c")
 
 GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 2, 8, 12, 14
 GGML_Q4_1, GGML_Q5_0, GGML_Q5_1, GGML_Q5_K = 3, 6, 7, 13
+GGML_Q2_K, GGML_Q3_K = 10, 11
 GGML_BLOCK = {GGML_Q4_0: (32, 18), GGML_Q8_0: (32, 34), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210),
-              GGML_Q4_1: (32, 20), GGML_Q5_0: (32, 22), GGML_Q5_1: (32, 24), GGML_Q5_K: (256, 176)}
+              GGML_Q4_1: (32, 20), GGML_Q5_0: (32, 22), GGML_Q5_1: (32, 24), GGML_Q5_K: (256, 176), GGML_Q2_K: (256, 84), GGML_Q3_K: (256, 110)}
 
 
 def build(force: bool = False) -> str:

@@ -297,7 +297,8 @@ ORC_API int orc_mxfp4_dequant_f32(const uint8_t *blocks, const uint8_t *scales, 
 /* ------------------------------------------------------------------ GGUF */
 
 /* GGML type ids as stored in GGUF files. */
-enum { ORC_Q4_0 = 2, ORC_Q4_1 = 3, ORC_Q5_0 = 6, ORC_Q5_1 = 7, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q5_K = 13, ORC_Q6_K = 14 };
+enum { ORC_Q4_0 = 2, ORC_Q4_1 = 3, ORC_Q5_0 = 6, ORC_Q5_1 = 7, ORC_Q8_0 = 8, ORC_Q2_K = 10, ORC_Q3_K = 11, ORC_Q4_K = 12, ORC_Q5_K = 13,
+       ORC_Q6_K = 14 };
 
 static inline uint16_t ld16(const uint8_t *p) { return (uint16_t)(p[0] | (p[1] << 8)); }
 
@@ -341,6 +342,8 @@ ORC_API int orc_gguf_dequant_f32(int ggml_type, const uint8_t *data, int64_t row
     case ORC_Q5_0: bel = 32; bby = 22; break;
     case ORC_Q5_1: bel = 32; bby = 24; break;
     case ORC_Q5_K: bel = 256; bby = 176; break;
+    case ORC_Q2_K: bel = 256; bby = 84; break;
+    case ORC_Q3_K: bel = 256; bby = 110; break;
     default: return -3;
     }
     if (cols % bel != 0) return -1;
@@ -410,6 +413,32 @@ ORC_API int orc_gguf_dequant_f32(int ggml_type, const uint8_t *data, int64_t row
                     uint32_t nib = lo == 0 ? (qs[iq * 32 + el] & 0x0Fu) : (uint32_t)(qs[iq * 32 + el] >> 4);
                     uint32_t q = nib | (((uint32_t)(qh[el] >> sub) & 1u) << 4);
                     o[j] = sub_rn(mul_rn(sc_v, (float)q), m_v);
+                }
+            } else if (ggml_type == ORC_Q2_K) {
+                /* {u8 scales[16]; u8 qs[64]; f16 d, dmin} (block_q2_K; the README lists Q2_K among the supported
+                 * quants, the arithmetic is ggml's dequantize_row_q2_K as candle's k_quants restates it): sixteen
+                 * sub-blocks of 16, scale nibble and min nibble per sub-block, (d*sc)*q - dmin*mn */
+                const uint8_t *sc = blk, *qs = blk + 16;
+                float d = f16_to_f32(ld16(blk + 80)), dmin = f16_to_f32(ld16(blk + 82));
+                for (int j = 0; j < 256; j++) {
+                    float dl = mul_rn(d, (float)(sc[j / 16] & 0x0Fu)), ml = mul_rn(dmin, (float)(sc[j / 16] >> 4));
+                    uint32_t q = ((uint32_t)qs[(j / 128) * 32 + j % 32] >> (2 * ((j / 32) % 4))) & 3u;
+                    o[j] = sub_rn(mul_rn(dl, (float)q), ml);
+                }
+            } else if (ggml_type == ORC_Q3_K) {
+                /* {u8 hmask[32]; u8 qs[64]; u8 scales[12]; f16 d} (block_q3_K, dequantize_row_q3_K): sixteen 6-bit
+                 * scales (low nibbles of bytes 0..7, then their high nibbles; two more bits each from bytes 8..11),
+                 * (d*(scale-32)) * (two-bit - (hmask bit ? 0 : 4)) */
+                const uint8_t *hm = blk, *qs = blk + 32, *scb = blk + 96;
+                float d = f16_to_f32(ld16(blk + 108));
+                for (int j = 0; j < 256; j++) {
+                    int is = j / 16;
+                    uint32_t lo4 = is < 8 ? (scb[is] & 0x0Fu) : (uint32_t)(scb[is - 8] >> 4);
+                    uint32_t hi2 = ((uint32_t)scb[8 + is % 4] >> (2 * (is / 4))) & 3u;
+                    float dl = mul_rn(d, (float)((int)(lo4 | (hi2 << 4)) - 32));
+                    int q2 = (int)(((uint32_t)qs[(j / 128) * 32 + j % 32] >> (2 * ((j / 32) % 4))) & 3u);
+                    int hb = (hm[j % 32] >> (j / 32)) & 1;
+                    o[j] = mul_rn(dl, (float)(q2 - (hb ? 0 : 4)));
                 }
             } else { /* Q6_K */
                 const uint8_t *ql = blk, *qh = blk + 128;

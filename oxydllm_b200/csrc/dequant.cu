@@ -696,7 +696,8 @@ int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *
         OXQ_LAUNCH_CHECK("q4k_slab_bf16_kernel");
         return OXQ_OK;
     }
-    if (aligned(b, 2) && aligned(out, 16) && ggml_type != OXQ_GGML_Q4_K && ggml_type != OXQ_GGML_Q5_K) {
+    if (aligned(b, 2) && aligned(out, 16) && ggml_type != OXQ_GGML_Q4_K && ggml_type != OXQ_GGML_Q5_K &&
+        ggml_type != OXQ_GGML_Q2_K && ggml_type != OXQ_GGML_Q3_K) {
         const int g32 = grid_for(total / 32);
         if (ggml_type == OXQ_GGML_Q8_0) q80_slab_bf16_kernel<<<g32, 256, 0, st>>>(b, out, total / 32);
         else if (ggml_type == OXQ_GGML_Q4_0) q40_slab_bf16_kernel<0><<<g32, 256, 0, st>>>(b, out, total / 32);
@@ -712,6 +713,7 @@ int gguf_dequant_rows_bf16(int ggml_type, const uint8_t *blocks, __nv_bfloat16 *
     switch (ggml_type) {
     OXQ_GGUF_CASE(OXQ_GGML_Q4_0) OXQ_GGUF_CASE(OXQ_GGML_Q8_0) OXQ_GGUF_CASE(OXQ_GGML_Q4_K) OXQ_GGUF_CASE(OXQ_GGML_Q4_1)
     OXQ_GGUF_CASE(OXQ_GGML_Q5_0) OXQ_GGUF_CASE(OXQ_GGML_Q5_1) OXQ_GGUF_CASE(OXQ_GGML_Q5_K)
+    OXQ_GGUF_CASE(OXQ_GGML_Q2_K) OXQ_GGUF_CASE(OXQ_GGML_Q3_K)
     default: gguf_dequant_kernel<OXQ_GGML_Q6_K, __nv_bfloat16><<<grid, 256, 0, st>>>(b, out, total); break;
     }
 #undef OXQ_GGUF_CASE
@@ -849,6 +851,7 @@ OXQ_EXPORT int oxq_gguf_dequant(int ggml_type, const void *blocks, void *w_out, 
     switch (ggml_type) {
     OXQ_GGUF_CASE(OXQ_GGML_Q4_0) OXQ_GGUF_CASE(OXQ_GGML_Q8_0) OXQ_GGUF_CASE(OXQ_GGML_Q4_K) OXQ_GGUF_CASE(OXQ_GGML_Q4_1)
     OXQ_GGUF_CASE(OXQ_GGML_Q5_0) OXQ_GGUF_CASE(OXQ_GGML_Q5_1) OXQ_GGUF_CASE(OXQ_GGML_Q5_K)
+    OXQ_GGUF_CASE(OXQ_GGML_Q2_K) OXQ_GGUF_CASE(OXQ_GGML_Q3_K)
     default:
         DISPATCH_OUT(out_dtype, gguf_dequant_kernel<OXQ_GGML_Q6_K, OutT><<<grid, 256, 0, st>>>(b, (OutT *)w_out, total));
         break;

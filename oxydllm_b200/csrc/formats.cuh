@@ -19,6 +19,8 @@ __host__ __device__ inline bool gguf_block_layout(int ggml_type, int &block_elem
     case OXQ_GGML_Q5_0: block_elems = 32; block_bytes = 22; return true;
     case OXQ_GGML_Q5_1: block_elems = 32; block_bytes = 24; return true;
     case OXQ_GGML_Q5_K: block_elems = 256; block_bytes = 176; return true;
+    case OXQ_GGML_Q2_K: block_elems = 256; block_bytes = 84; return true;
+    case OXQ_GGML_Q3_K: block_elems = 256; block_bytes = 110; return true;
     default: return false;
     }
 }
@@ -51,6 +53,10 @@ __device__ __forceinline__ void q4k_scale_min(int j, const uint8_t *q, uint32_t 
 //   Q5_0 {f16 d; u8 qh[4]; u8 qs[16]}: ((nibble | bit j of qh << 4) - 16) * d.
 //   Q5_1 {f16 d, m; u8 qh[4]; u8 qs[16]}: (nibble | bit j of qh << 4) * d + m.
 //   Q5_K {f16 d, dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]}: Q4_K with bit `sub` of qh[el] as fifth bit.
+//   Q2_K {u8 scales[16]; u8 qs[64]; f16 d, dmin}: sub-block j / 16 has scale nibble and min nibble in scales[j / 16];
+//        (d*sc) * two-bit - (dmin*mn), two-bit = (qs[(j >> 7) * 32 + (j & 31)] >> 2 * ((j >> 5) & 3)) & 3.
+//   Q3_K {u8 hmask[32]; u8 qs[64]; u8 scales[12]; f16 d}: 6-bit scale of sub-block j / 16 from the 12 packed bytes;
+//        (d * (scale - 32)) * (two-bit - (bit j >> 5 of hmask[j & 31] ? 0 : 4)).
 template <int TYPE> __device__ __forceinline__ float gguf_decode_elem(const uint8_t *blk, int j)
 {
     if (TYPE == OXQ_GGML_Q4_0) {
@@ -86,6 +92,21 @@ template <int TYPE> __device__ __forceinline__ float gguf_decode_elem(const uint
         uint32_t b = blk[48 + (sub >> 1) * 32 + el];
         uint32_t q = ((sub & 1) ? (b >> 4) : (b & 0x0Fu)) | ((((uint32_t)blk[16 + el] >> sub) & 1u) << 4);
         return __fsub_rn(__fmul_rn(sc_v, (float)q), m_v);
+    } else if (TYPE == OXQ_GGML_Q2_K) {
+        const float d = half_bits_to_f32((uint16_t)ld_u16(blk + 80)), dmin = half_bits_to_f32((uint16_t)ld_u16(blk + 82));
+        const uint32_t sc = blk[j >> 4];
+        const float dl = __fmul_rn(d, (float)(sc & 0x0Fu)), ml = __fmul_rn(dmin, (float)(sc >> 4));
+        const uint32_t q = ((uint32_t)blk[16 + (j >> 7) * 32 + (j & 31)] >> (2 * ((j >> 5) & 3))) & 3u;
+        return __fsub_rn(__fmul_rn(dl, (float)q), ml);
+    } else if (TYPE == OXQ_GGML_Q3_K) {
+        const uint8_t *scb = blk + 96;
+        const int is = j >> 4;
+        const uint32_t lo4 = is < 8 ? (scb[is] & 0x0Fu) : ((uint32_t)scb[is - 8] >> 4);
+        const uint32_t hi2 = ((uint32_t)scb[8 + (is & 3)] >> (2 * (is >> 2))) & 3u;
+        const float dl = __fmul_rn(half_bits_to_f32((uint16_t)ld_u16(blk + 108)), (float)((int)(lo4 | (hi2 << 4)) - 32));
+        const int q2 = (int)(((uint32_t)blk[32 + (j >> 7) * 32 + (j & 31)] >> (2 * ((j >> 5) & 3))) & 3u);
+        const int hb = (blk[j & 31] >> (j >> 5)) & 1;
+        return __fmul_rn(dl, (float)(q2 - (hb ? 0 : 4)));
     } else if (TYPE == OXQ_GGML_Q4_K) {
         float d = half_bits_to_f32((uint16_t)ld_u16(blk));
         float dmin = half_bits_to_f32((uint16_t)ld_u16(blk + 2));

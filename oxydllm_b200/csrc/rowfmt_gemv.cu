@@ -257,6 +257,8 @@ OXQ_EXPORT int oxq_gguf_gemv(int ggml_type, const void *x, int x_dtype, const vo
     case OXQ_GGML_Q5_0: return launch_rowfmt<RF_GGUF_ELEM + OXQ_GGML_Q5_0>(p, st);
     case OXQ_GGML_Q5_1: return launch_rowfmt<RF_GGUF_ELEM + OXQ_GGML_Q5_1>(p, st);
     case OXQ_GGML_Q5_K: return launch_rowfmt<RF_GGUF_ELEM + OXQ_GGML_Q5_K>(p, st);
+    case OXQ_GGML_Q2_K: return launch_rowfmt<RF_GGUF_ELEM + OXQ_GGML_Q2_K>(p, st);
+    case OXQ_GGML_Q3_K: return launch_rowfmt<RF_GGUF_ELEM + OXQ_GGML_Q3_K>(p, st);
     case OXQ_GGML_Q4_0: return launch_rowfmt<RF_Q4_0>(p, st);
     case OXQ_GGML_Q8_0: return launch_rowfmt<RF_Q8_0>(p, st);
     case OXQ_GGML_Q4_K: return launch_rowfmt<RF_Q4_K>(p, st);

@@ -29,11 +29,12 @@ AWQ_PACK_FACTOR = 8
 
 GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 2, 8, 12, 14
 GGML_Q4_1, GGML_Q5_0, GGML_Q5_1, GGML_Q5_K = 3, 6, 7, 13
+GGML_Q2_K, GGML_Q3_K = 10, 11
 #: ggml type id -> (elements per block, bytes per block)
 GGML_BLOCK = {GGML_Q4_0: (32, 18), GGML_Q8_0: (32, 34), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210),
-              GGML_Q4_1: (32, 20), GGML_Q5_0: (32, 22), GGML_Q5_1: (32, 24), GGML_Q5_K: (256, 176)}
+              GGML_Q4_1: (32, 20), GGML_Q5_0: (32, 22), GGML_Q5_1: (32, 24), GGML_Q5_K: (256, 176), GGML_Q2_K: (256, 84), GGML_Q3_K: (256, 110)}
 GGML_NAME = {GGML_Q4_0: "Q4_0", GGML_Q8_0: "Q8_0", GGML_Q4_K: "Q4_K", GGML_Q6_K: "Q6_K",
-             GGML_Q4_1: "Q4_1", GGML_Q5_0: "Q5_0", GGML_Q5_1: "Q5_1", GGML_Q5_K: "Q5_K"}
+             GGML_Q4_1: "Q4_1", GGML_Q5_0: "Q5_0", GGML_Q5_1: "Q5_1", GGML_Q5_K: "Q5_K", GGML_Q2_K: "Q2_K", GGML_Q3_K: "Q3_K"}
 
 
 # ----------------------------------------------------------------------- AWQ
@@ -435,7 +436,67 @@ def quantize_q5_k(weight: np.ndarray) -> np.ndarray:
     out[:, :, 48:] = (lo[:, :, :, 0, :] | (lo[:, :, :, 1, :] << 4)).reshape(rows, nb, 128)
     return out.reshape(-1)
 
+def quantize_q2_k(weight: np.ndarray) -> np.ndarray:
+    """Own Q2_K encoder (block_q2_K: ``scales[16]``, ``qs[64]``, f16 ``d``, f16 ``dmin``): sixteen sub-blocks of 16
+    with a 4-bit scale and a 4-bit min each; element e sits in ``qs[(e >> 7) * 32 + (e & 31)]`` at bit ``2 * ((e >> 5) & 3)``."""
+    w = np.ascontiguousarray(weight, np.float32)
+    rows, k = w.shape
+    assert k % 256 == 0
+    nb = k // 256
+    x = w.reshape(rows, nb, 16, 16)
+    mins = np.maximum(-x.min(axis=3), 0.0)                    # [rows, nb, 16]
+    scl = (x.max(axis=3) + mins) / 3.0
+    d = (scl.max(axis=2) / 15.0).astype(np.float16).astype(np.float32)
+    dmin = (mins.max(axis=2) / 15.0).astype(np.float16).astype(np.float32)
+    sc = np.where(d[..., None] > 0, np.clip(np.rint(scl / np.where(d > 0, d, 1.0)[..., None]), 0, 15), 0).astype(np.uint8)
+    mn = np.where(dmin[..., None] > 0, np.clip(np.rint(mins / np.where(dmin > 0, dmin, 1.0)[..., None]), 0, 15), 0).astype(np.uint8)
+    dl = d[..., None] * sc
+    ml = dmin[..., None] * mn
+    q = np.where(dl[..., None] > 0, np.clip(np.rint((x + ml[..., None]) / np.where(dl > 0, dl, 1.0)[..., None]), 0, 3), 0).astype(np.uint8)
+    q = q.reshape(rows, nb, 2, 4, 32)                          # [half, shift index, byte]
+    qs = (q[:, :, :, 0] | (q[:, :, :, 1] << 2) | (q[:, :, :, 2] << 4) | (q[:, :, :, 3] << 6)).astype(np.uint8)
+    out = np.empty((rows, nb, 84), np.uint8)
+    out[:, :, 0:16] = sc | (mn << 4)
+    out[:, :, 16:80] = qs.reshape(rows, nb, 64)
+    out[:, :, 80:82] = d.astype(np.float16).view(np.uint8).reshape(rows, nb, 2)
+    out[:, :, 82:84] = dmin.astype(np.float16).view(np.uint8).reshape(rows, nb, 2)
+    return out.reshape(-1)
+
+
+def quantize_q3_k(weight: np.ndarray) -> np.ndarray:
+    """Own Q3_K encoder (block_q3_K: ``hmask[32]``, ``qs[64]``, ``scales[12]``, f16 ``d``): sixteen sub-blocks of 16 with
+    a signed 6-bit scale each; a 3-bit code is two bits in ``qs`` (as in Q2_K) and bit ``e >> 5`` of ``hmask[e & 31]``."""
+    w = np.ascontiguousarray(weight, np.float32)
+    rows, k = w.shape
+    assert k % 256 == 0
+    nb = k // 256
+    x = w.reshape(rows, nb, 16, 16)
+    scl = np.abs(x).max(axis=3) / 4.0                          # codes -4..3
+    d = (scl.max(axis=2) / 31.0).astype(np.float16).astype(np.float32)
+    sc = np.where(d[..., None] > 0, np.clip(np.rint(scl / np.where(d > 0, d, 1.0)[..., None]), 0, 31), 0).astype(np.int32)
+    dl = d[..., None] * sc
+    q = np.where(dl[..., None] > 0, np.clip(np.rint(x / np.where(dl > 0, dl, 1.0)[..., None]), -4, 3), 0).astype(np.int32) + 4
+    q = q.reshape(rows, nb, 2, 4, 32).astype(np.uint8)        # [half, shift index, byte]
+    lo = q & 3
+    qs = (lo[:, :, :, 0] | (lo[:, :, :, 1] << 2) | (lo[:, :, :, 2] << 4) | (lo[:, :, :, 3] << 6)).astype(np.uint8)
+    hb = (q >> 2).reshape(rows, nb, 8, 32)                     # bit index = half * 4 + shift index
+    hmask = np.zeros((rows, nb, 32), np.uint8)
+    for b in range(8):
+        hmask |= (hb[:, :, b] << b).astype(np.uint8)
+    s6 = (sc + 32).astype(np.uint8)                            # stored scale
+    scales = np.zeros((rows, nb, 12), np.uint8)
+    scales[:, :, 0:8] = (s6[:, :, 0:8] & 0x0F) | ((s6[:, :, 8:16] & 0x0F) << 4)
+    for i in range(16):
+        scales[:, :, 8 + (i & 3)] |= ((s6[:, :, i] >> 4) & 3) << (2 * (i >> 2))
+    out = np.empty((rows, nb, 110), np.uint8)
+    out[:, :, 0:32] = hmask
+    out[:, :, 32:96] = qs.reshape(rows, nb, 64)
+    out[:, :, 96:108] = scales
+    out[:, :, 108:110] = d.astype(np.float16).view(np.uint8).reshape(rows, nb, 2)
+    return out.reshape(-1)
+
 
 GGML_QUANTIZE = {GGML_Q4_0: quantize_q4_0, GGML_Q8_0: quantize_q8_0, GGML_Q4_K: quantize_q4_k,
                  GGML_Q6_K: quantize_q6_k, GGML_Q4_1: quantize_q4_1, GGML_Q5_0: quantize_q5_0,
-                 GGML_Q5_1: quantize_q5_1, GGML_Q5_K: quantize_q5_k}
+                 GGML_Q5_1: quantize_q5_1, GGML_Q5_K: quantize_q5_k, GGML_Q2_K: quantize_q2_k,
+                 GGML_Q3_K: quantize_q3_k}

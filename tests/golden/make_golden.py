@@ -20,9 +20,11 @@ from gguf import quants  # noqa: E402
 from oxydllm_b200 import formats as F  # noqa: E402
 
 TYPES = {F.GGML_Q4_0: T.Q4_0, F.GGML_Q8_0: T.Q8_0, F.GGML_Q4_K: T.Q4_K, F.GGML_Q6_K: T.Q6_K,
-         F.GGML_Q4_1: T.Q4_1, F.GGML_Q5_0: T.Q5_0, F.GGML_Q5_1: T.Q5_1, F.GGML_Q5_K: T.Q5_K}
+         F.GGML_Q4_1: T.Q4_1, F.GGML_Q5_0: T.Q5_0, F.GGML_Q5_1: T.Q5_1, F.GGML_Q5_K: T.Q5_K,
+         F.GGML_Q2_K: T.Q2_K, F.GGML_Q3_K: T.Q3_K}
 F16_FIELDS = {F.GGML_Q4_0: [0], F.GGML_Q8_0: [0], F.GGML_Q4_K: [0, 2], F.GGML_Q6_K: [208],
-              F.GGML_Q4_1: [0, 2], F.GGML_Q5_0: [0], F.GGML_Q5_1: [0, 2], F.GGML_Q5_K: [0, 2]}
+              F.GGML_Q4_1: [0, 2], F.GGML_Q5_0: [0], F.GGML_Q5_1: [0, 2], F.GGML_Q5_K: [0, 2],
+              F.GGML_Q2_K: [80, 82], F.GGML_Q3_K: [108]}
 
 
 def main():

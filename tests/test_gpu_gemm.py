@@ -57,7 +57,8 @@ def test_awq_gemm_matches_gemv_rows(cuda):
     assert torch.allclose(big[:8], small, rtol=2e-2, atol=2e-2 * float(small.abs().max()))
 
 
-@pytest.mark.parametrize("ggml_type", [F.GGML_Q4_0, F.GGML_Q8_0, F.GGML_Q4_K, F.GGML_Q6_K, F.GGML_Q4_1, F.GGML_Q5_0, F.GGML_Q5_1, F.GGML_Q5_K])
+@pytest.mark.parametrize("ggml_type", [F.GGML_Q4_0, F.GGML_Q8_0, F.GGML_Q4_K, F.GGML_Q6_K, F.GGML_Q4_1, F.GGML_Q5_0, F.GGML_Q5_1, F.GGML_Q5_K,
+                                       F.GGML_Q2_K, F.GGML_Q3_K])
 @pytest.mark.parametrize("n,k,m", [(512, 2048, 33), (1001, 512, 70), (2048, 2048, 9 * 8)])
 def test_gguf_gemm(cuda, ggml_type, n, k, m):
     # shapes/m of metal_ops.rs:6386-6470 (m in {33, 70}, odd n = 1001)

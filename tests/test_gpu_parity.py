@@ -96,7 +96,8 @@ def test_gptq_dequant_bit_exact(cuda, bits_, sym):
         assert np.array_equal(bits(L.dequantize_gptq(raw, TORCH_OUT[out])), narrowed(ref, out))
 
 
-@pytest.mark.parametrize("ggml_type", [F.GGML_Q4_0, F.GGML_Q8_0, F.GGML_Q4_K, F.GGML_Q6_K, F.GGML_Q4_1, F.GGML_Q5_0, F.GGML_Q5_1, F.GGML_Q5_K])
+@pytest.mark.parametrize("ggml_type", [F.GGML_Q4_0, F.GGML_Q8_0, F.GGML_Q4_K, F.GGML_Q6_K, F.GGML_Q4_1, F.GGML_Q5_0, F.GGML_Q5_1, F.GGML_Q5_K,
+                                       F.GGML_Q2_K, F.GGML_Q3_K])
 def test_gguf_dequant_bit_exact_golden_and_oracle(cuda, ggml_type):
     z = np.load(GOLDEN)
     rows, cols = (int(v) for v in z[f"shape_{ggml_type}"])
@@ -263,7 +264,8 @@ def test_awq_prefill_sized_batch_matches_oracle(cuda):
     assert_matmul_close(lin.forward(dev(x, torch.bfloat16)), ref, "awq m=70")
 
 
-@pytest.mark.parametrize("ggml_type", [F.GGML_Q4_0, F.GGML_Q8_0, F.GGML_Q4_K, F.GGML_Q6_K, F.GGML_Q4_1, F.GGML_Q5_0, F.GGML_Q5_1, F.GGML_Q5_K])
+@pytest.mark.parametrize("ggml_type", [F.GGML_Q4_0, F.GGML_Q8_0, F.GGML_Q4_K, F.GGML_Q6_K, F.GGML_Q4_1, F.GGML_Q5_0, F.GGML_Q5_1, F.GGML_Q5_K,
+                                       F.GGML_Q2_K, F.GGML_Q3_K])
 @pytest.mark.parametrize("n,k,m", [(128, 256, 1), (100, 2560, 2), (256, 512, 4), (1001, 512, 8), (64, 4096, 1),
                                    (512, 2048, 9), (96, 1024, 32)])
 def test_gguf_gemv(cuda, ggml_type, n, k, m):

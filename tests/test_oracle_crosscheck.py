@@ -12,7 +12,8 @@ from oxydllm_b200 import formats as F
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "gguf_blocks.npz")
 
 
-@pytest.mark.parametrize("ggml_type", [F.GGML_Q4_0, F.GGML_Q8_0, F.GGML_Q4_K, F.GGML_Q6_K, F.GGML_Q4_1, F.GGML_Q5_0, F.GGML_Q5_1, F.GGML_Q5_K])
+@pytest.mark.parametrize("ggml_type", [F.GGML_Q4_0, F.GGML_Q8_0, F.GGML_Q4_K, F.GGML_Q6_K, F.GGML_Q4_1, F.GGML_Q5_0, F.GGML_Q5_1, F.GGML_Q5_K,
+                                       F.GGML_Q2_K, F.GGML_Q3_K])
 def test_gguf_dequant_bit_exact_against_gguf_py_fixture(ggml_type):
     z = np.load(GOLDEN)
     rows, cols = (int(v) for v in z[f"shape_{ggml_type}"])
@@ -22,7 +23,7 @@ def test_gguf_dequant_bit_exact_against_gguf_py_fixture(ggml_type):
 
 @pytest.mark.parametrize("ggml_type,max_rel", [(F.GGML_Q4_0, 0.12), (F.GGML_Q8_0, 0.01), (F.GGML_Q4_K, 0.11),
                                                (F.GGML_Q6_K, 0.03), (F.GGML_Q4_1, 0.11), (F.GGML_Q5_0, 0.06),
-                                               (F.GGML_Q5_1, 0.05), (F.GGML_Q5_K, 0.05)])
+                                               (F.GGML_Q5_1, 0.05), (F.GGML_Q5_K, 0.05), (F.GGML_Q2_K, 0.45), (F.GGML_Q3_K, 0.25)])
 def test_encoders_emit_valid_blocks(ggml_type, max_rel):
     w = (np.random.default_rng(3).standard_normal((8, 512)) * 0.02).astype(np.float32)
     data = F.GGML_QUANTIZE[ggml_type](w)
