@@ -185,6 +185,12 @@ int oxq_w8a16_dequant(const uint32_t *qweight, const uint32_t *qzeros, const voi
 
 size_t oxq_gemm_workspace_bytes(int n, int k);
 
+/* Self-test of the bounded waits (no counterpart in the reference): one thread waits, with a 50 ms limit, on a
+ * barrier that nothing arrives on; the wait gives up, stores `code` (> 0) in the flag word of `workspace`
+ * and the kernel ends normally, so the next oxq_gemm_check reports OXQ_ERR_DEVICE_FLAG and the workspace
+ * stays usable. */
+int oxq_selftest_wait_expiry(void *workspace, int code, void *stream);
+
 /* Zeroes the 256-byte header (flag word) of a fresh workspace on `stream`. */
 int oxq_gemm_workspace_init(void *workspace, void *stream);
 

@@ -4,6 +4,7 @@ Usage: ``python -m oxydllm_b200.build [--force] [--verbose]``.
 """
 from __future__ import annotations
 
+import fcntl
 import glob
 import os
 import subprocess
@@ -37,12 +38,22 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     extra = os.environ.get("OXQ_NVCC_FLAGS", "").split()  # extra defines for experiments
-    cmd = [nvcc, *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if verbose else []), "-o", LIB, *sources()]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or res.returncode:
-        sys.stderr.write(res.stdout + res.stderr)
-    if res.returncode:
-        raise RuntimeError("nvcc failed building liboxq.so")
+    # One builder at a time, and the library appears under its name only when complete: processes that start
+    # together (test workers, ranks of a multi-GPU launch) never load a half-written file.
+    with open(LIB + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and not _stale():
+            return LIB  # another process built it while this one waited
+        tmp = f"{LIB}.{os.getpid()}.tmp"
+        cmd = [nvcc, *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if verbose else []), "-o", tmp, *sources()]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose or res.returncode:
+            sys.stderr.write(res.stdout + res.stderr)
+        if res.returncode:
+            if os.path.exists(tmp):
+                os.remove(tmp)
+            raise RuntimeError("nvcc failed building liboxq.so")
+        os.replace(tmp, LIB)
     return LIB
 
 

@@ -632,7 +632,7 @@ __global__ void __launch_bounds__(GT_KW * 32, MINB)
 {
     constexpr int KW = GT_KW, V = 2;
     constexpr int NACC = V * 4 * MT * 4;
-    extern __shared__ __align__(1024) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem_ring[]; // TMA destinations want 128-byte alignment
 
     GV_CTA(0);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -654,10 +654,10 @@ __global__ void __launch_bounds__(GT_KW * 32, MINB)
     const int step_beg = (rank * KW + warp) * steps;
 
     // shared memory: rings | barriers | x | zeros | totals
-    unsigned char *ring = smem + (size_t)warp * S * GT_STAGE_BYTES;
+    unsigned char *ring = smem_ring + (size_t)warp * S * GT_STAGE_BYTES;
     const uint32_t ring_addr = smem_u32(ring);
-    const uint32_t bar0 = smem_u32(smem + (size_t)KW * S * GT_STAGE_BYTES) + warp * GT_MAX_STAGES * 8;
-    unsigned char *rest = smem + (size_t)KW * S * GT_STAGE_BYTES + KW * GT_MAX_STAGES * 8;
+    const uint32_t bar0 = smem_u32(smem_ring + (size_t)KW * S * GT_STAGE_BYTES) + warp * GT_MAX_STAGES * 8;
+    unsigned char *rest = smem_ring + (size_t)KW * S * GT_STAGE_BYTES + KW * GT_MAX_STAGES * 8;
 
     // The next launch on the stream may start its own weight boxes while this one drains; nothing
     // that another kernel may have produced (x) or may still read (y) is touched before the wait below.

@@ -529,6 +529,7 @@ __global__ void __launch_bounds__(DT_THREADS, 1) awq_decode_tc_kernel(const Deco
         __syncwarp();
         for (int u = u0 + uw; u < u1 && ok; u += S) {
             const int it = u - u0;
+            (void)it; // only the trace of tuning builds reads it
             ok = mbar_wait_warp(ebar, ph, p.flag, 1);
             ph ^= 1u;
             if (lane == 0 && uw == 0) DT_TRACE(5, it);

@@ -771,3 +771,26 @@ int gemm_grouped(const void *a, int a_rows, const void *w, int slab_experts, int
 }
 
 } // namespace oxq
+
+// One thread waits on an mbarrier that nothing ever arrives on, with a 50 ms limit: the wait must give up, record
+// its code in the flag word and let the kernel end normally.
+namespace oxq {
+__global__ void wait_expiry_selftest_kernel(int *flag, int code)
+{
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t b = smem_u32(&bar);
+    mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait(b, 0, flag, code, 50000000ull);
+}
+} // namespace oxq
+
+OXQ_EXPORT int oxq_selftest_wait_expiry(void *workspace, int code, void *stream)
+{
+    oxq::clear_error();
+    OXQ_REQUIRE(workspace, OXQ_ERR_NULL, "oxq_selftest_wait_expiry: null workspace");
+    OXQ_REQUIRE(code > 0, OXQ_ERR_BAD_SHAPE, "oxq_selftest_wait_expiry: code must be positive");
+    oxq::wait_expiry_selftest_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(reinterpret_cast<int *>(workspace), code);
+    OXQ_CUDA(cudaGetLastError());
+    return OXQ_OK;
+}

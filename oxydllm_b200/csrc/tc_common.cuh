@@ -50,7 +50,8 @@ __device__ __forceinline__ bool mbar_test_parked(uint32_t bar, uint32_t parity, 
 }
 // Bounded wait: false (and `code` recorded) when the barrier did not flip within the limit. The wall clock
 // (slow to read) is only consulted after a good number of parked polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *flag, int code)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *flag, int code,
+                                          unsigned long long limit_ns = TC_WAIT_LIMIT_NS)
 {
     if (mbar_test(bar, parity)) return true;
 #ifndef OXQ_WAIT_MODE
@@ -71,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *fl
 #pragma unroll 1
         for (int i = 0; i < 64; i++)
             if (OXQ_POLL()) return true;
-        if (global_ns() - t0 > TC_WAIT_LIMIT_NS) {
+        if (global_ns() - t0 > limit_ns) {
             atomicCAS(flag, 0, code);
             return false;
         }

@@ -2,6 +2,8 @@
 weights first rounded to bf16 (what the tensor cores are fed; the reference's GPU paths round the
 dequantized weight to the activation dtype too, linear.rs:143, mpp_gemm.metal:143). Tolerance:
 max|err| <= 2e-2 * ||row||_inf."""
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -119,3 +121,23 @@ def test_gated_ffn_gate_up_matches_oracle(cuda, activation, m, k, inter, g):
     # products of two projections: tolerance relative to the row's largest |gate| * |up| scale
     row_inf = np.abs(ref).max(axis=1, keepdims=True)
     assert (np.abs(got - ref) <= 3e-2 * row_inf + 1e-4).all(), float(np.abs(got - ref).max())
+
+
+def test_bounded_wait_expiry_is_reported_and_the_workspace_stays_usable(cuda):
+    # A wait that nothing satisfies gives up after its limit (50 ms in the self-test), records its code and the
+    # kernel ends; the check reports it once, and the same workspace then serves a normal call.
+    from oxydllm_b200 import _lib
+    k, n, m = 512, 256, 70
+    ws = gemm.workspace(n, k, "cuda")
+    gemm.check(ws)
+    _lib.call("oxq_selftest_wait_expiry", ctypes.c_void_p(ws.data_ptr()), 9, None)
+    with pytest.raises(_lib.OxqError, match="bounded wait 9") as e:
+        gemm.check(ws)
+    assert e.value.status < 0
+    gemm.check(ws)  # reported once, clean again
+    qw, qz, sc = synth.awq_layer(k, n, 128, seed=3)
+    lin = L.PackedQuantLinear(L.QuantWeight.new_awq(4, words(qw), words(qz), dev(sc)))
+    x = synth.activations(m, k, seed=4)
+    y = lin.forward(dev(x, torch.bfloat16))
+    check(y, oracle.linear(x, synth.bf16_round(oracle.awq_dequant(qw, qz, sc))), "after an expired wait")
+    gemm.check(ws)
