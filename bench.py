@@ -44,9 +44,9 @@ def algo_bytes(m: int) -> int:
 
 BYTES_PER_STEP = LAYERS * sum(algo_bytes(m) for m in M_SWEEP)
 LAUNCHES_PER_STEP = LAYERS * len(M_SWEEP)
-# dram__bytes_read.sum + dram__bytes_write.sum of one m = 1 launch of awq_gemv_group_kernel on this layer shape,
-# recorded from an ncu capture (not measured by this script; algorithmic bytes of that launch: algo_bytes(1)).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 30_547_712 + 72_192
+# dram__bytes_read.sum + dram__bytes_write.sum of one m = 2 launch of awq_gemv_tma_kernel on this layer shape,
+# recorded from an ncu capture (not measured by this script; algorithmic bytes of that launch: algo_bytes(2)).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 30_560_768
 
 
 def measured_peak():
@@ -257,7 +257,7 @@ def run_gpu(args):
                 "d2h_bytes_per_step": LAYERS * sum(m * N * 2 for m in M_SWEEP)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                     "traffic_source": "recorded ncu capture of one m = 1 launch (dram read + write bytes)",
+                     "traffic_source": "recorded ncu capture of one m = 2 launch of awq_gemv_tma_kernel (dram read + write bytes)",
                      "kernel": "awq_gemv_tma_kernel (m <= 8), awq_gemv_group_kernel (m = 16), awq_fused_tc_kernel (m = 32)",
                      "peak_kind": f"{peak_kind} copy bandwidth", "per_m": per_m},
         "clocks": clocks,
