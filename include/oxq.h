@@ -200,8 +200,13 @@ int oxq_gemm_workspace_init(void *workspace, void *stream);
  * to be trusted). */
 int oxq_gemm_check(const void *workspace, void *stream);
 
-/* PackedQuantLinear::forward prefill branch: maybe_mpp_quant_matmul, else
- * dequantize_w4 + matmul (linear.rs:494-524, metal_ops.rs:2771-2797). */
+/* PackedQuantLinear::forward beyond the decode GEMV: maybe_mpp_quant_matmul, else
+ * dequantize_w4 + matmul (linear.rs:494-524, metal_ops.rs:2771-2797). Up to 256
+ * tokens, when n % 128 == 0, k % 128 == 0, group_size is a power of two >= 64 and
+ * the scales are f16 or bf16, one kernel unpacks the words into its shared-memory
+ * operand and multiplies on tcgen05 (same bf16 weights, no slab written); all
+ * other calls dequantize slabs into the workspace. The workspace is required
+ * (and its flag word used) either way. */
 int oxq_awq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
                  int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
                  int group_size, void *workspace, size_t workspace_bytes, void *stream);

@@ -909,16 +909,10 @@ template <int MT, int MINB>
 static int launch_awq_gemv_tma(AwqGemvParams p, int nranks, cudaStream_t stream)
 {
     constexpr int NACC = 2 * 4 * MT * 4;
-    EncodeTiledFn fn = encode_tiled_fn();
-    OXQ_REQUIRE(fn != nullptr, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     CUtensorMap wmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)p.packed_out, (cuuint64_t)p.k};
-    const cuuint64_t strides[1] = {(cuuint64_t)p.packed_out * 4};
-    const cuuint32_t box[2] = {16, GT_ROWS};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t *>(p.qweight), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, p.qweight, (uint64_t)p.packed_out, (uint64_t)p.k,
+                                       (uint64_t)p.packed_out * 4, 16, GT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
 
     const int m_cta = p.m < 8 * MT ? p.m : 8 * MT;

@@ -349,8 +349,6 @@ int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qze
                      int bias_dtype, void *y, int y_dtype, int m, int k, int n, int group_size, int col_base, int ldy,
                      int *flag, cudaStream_t st)
 {
-    EncodeTiledFn fn = encode_tiled_fn();
-    OXQ_REQUIRE(fn != nullptr, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     FusedParams p;
     p.qzeros = qzeros; p.scales = scales; p.scales_dtype = scales_dtype; p.bias = bias; p.y = y;
     p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
@@ -372,26 +370,12 @@ int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qze
     const size_t smem = (size_t)p.stages * p.stage_bytes + (size_t)p.raw_slots * FT_RAW_BYTES + fixed;
 
     CUtensorMap wmap, xmap;
-    {
-        const cuuint64_t dims[2] = {(cuuint64_t)p.packed_out, (cuuint64_t)k};
-        const cuuint64_t strides[1] = {(cuuint64_t)p.packed_out * 4};
-        const cuuint32_t box[2] = {16, FT_BK};
-        const cuuint32_t estr[2] = {1, 1};
-        CUresult r = fn(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint32_t *>(qweight), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", (int)r);
-    }
-    {
-        const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)m};
-        const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-        const cuuint32_t box[2] = {FT_BK, (cuuint32_t)p.mpad};
-        const cuuint32_t estr[2] = {1, 1};
-        CUresult r = fn(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled (x) failed with CUresult %d", (int)r);
-    }
+    CUresult r = encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, qweight, (uint64_t)p.packed_out, (uint64_t)k,
+                                 (uint64_t)p.packed_out * 4, 16, FT_BK, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", (int)r);
+    r = encode_tiled_2d(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, (uint64_t)k, (uint64_t)m, (uint64_t)k * 2, FT_BK, (uint32_t)p.mpad,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled (x) failed with CUresult %d", (int)r);
 
     static size_t configured[64] = {};
     int device = 0;

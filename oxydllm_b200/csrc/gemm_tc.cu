@@ -629,15 +629,8 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // 2-D bf16 row-major [rows, cols] tensor, box [box_rows, 64 cols], 128-byte swizzle, zero fill.
 static int make_map_bf16(CUtensorMap *map, const void *ptr, uint64_t rows, uint64_t cols, uint32_t box_rows)
 {
-    EncodeTiledFn fn = encode_tiled_fn();
-    OXQ_REQUIRE(fn != nullptr, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = encode_tiled_2d(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ptr, cols, rows, cols * 2, (uint32_t)TC_BK, box_rows,
+                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return OXQ_OK;
 }

@@ -184,4 +184,41 @@ inline EncodeTiledFn encode_tiled_fn()
 }
 
 
+// 2-D tiled tensor map through a small per-thread cache. A tensor map is a pure function of these arguments, and
+// the driver call that encodes one costs several microseconds, which a decode call cannot afford on every launch.
+inline CUresult encode_tiled_2d(CUtensorMap *out, CUtensorMapDataType dtype, const void *ptr, uint64_t dim0, uint64_t dim1,
+                                uint64_t stride1_bytes, uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle,
+                                CUtensorMapL2promotion promo)
+{
+    struct Entry {
+        const void *ptr;
+        uint64_t dim0, dim1, stride;
+        uint32_t box0, box1;
+        int dtype, swizzle, promo, valid;
+        CUtensorMap map;
+    };
+    constexpr int SLOTS = 256;
+    static thread_local Entry cache[SLOTS];
+    const uintptr_t a = reinterpret_cast<uintptr_t>(ptr);
+    Entry &e = cache[((a >> 8) ^ (a >> 20) ^ box1 ^ (dim1 << 3)) & (SLOTS - 1)];
+    if (e.valid && e.ptr == ptr && e.dim0 == dim0 && e.dim1 == dim1 && e.stride == stride1_bytes && e.box0 == box0 &&
+        e.box1 == box1 && e.dtype == (int)dtype && e.swizzle == (int)swizzle && e.promo == (int)promo) {
+        *out = e.map;
+        return CUDA_SUCCESS;
+    }
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
+    const cuuint64_t dims[2] = {dim0, dim1};
+    const cuuint64_t strides[1] = {stride1_bytes};
+    const cuuint32_t box[2] = {box0, box1};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(out, dtype, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                          promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+        e.ptr = ptr; e.dim0 = dim0; e.dim1 = dim1; e.stride = stride1_bytes; e.box0 = box0; e.box1 = box1;
+        e.dtype = (int)dtype; e.swizzle = (int)swizzle; e.promo = (int)promo; e.map = *out; e.valid = 1;
+    }
+    return r;
+}
+
 } // namespace oxq
