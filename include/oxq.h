@@ -230,7 +230,9 @@ int oxq_w8a16_gemm(const void *x, int x_dtype, const uint32_t *qweight, const ui
                    int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
                    int group_size, void *workspace, size_t workspace_bytes, void *stream);
 
-/* Same branch for GPTQ-packed weights (dequantize_gptq_packed + matmul, linear.rs:509-520). */
+/* Same branch for GPTQ-packed weights (dequantize_gptq_packed + matmul, linear.rs:509-520). 4-bit weights of
+ * the shapes named above take the fused unpack + tcgen05 kernel up to 256 tokens (K-major operand: a GPTQ
+ * word is eight input rows of one out feature); qzeros, where given, must then be 16-byte aligned. */
 int oxq_gptq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
                   int scales_dtype, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n,
                   int group_size, int bits, int sym, void *workspace, size_t workspace_bytes, void *stream);

@@ -61,6 +61,7 @@ struct FusedParams {
     int m, mpad, k, n, group_size, packed_out;
     int stages, raw_slots, stage_bytes, tmem_cols;
     int gshift;        // log2(stages per quantization group)
+    int sym;           // GPTQ: no stored zero points (zero + 1 = 8)
     int col_base, ldy; // y column of out feature 0 and the row pitch of y in elements
     int *flag;
 };
@@ -100,6 +101,11 @@ __device__ __forceinline__ uint32_t ft_idesc(int n)
     return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(FT_ROWS >> 4) << 24);
 }
 
+// GPTQ = false: AWQ layout (a word is eight out features of one input row; A operand MN-major).
+// GPTQ = true:  GPTQ 4-bit layout (a word is eight input rows of one out feature, nibble i = row 8 r + i; A operand
+//               K-major: the word becomes one 16-byte chunk of the out feature's 128-byte row). The box is 8 packed
+//               rows x 128 words; the zero point is the stored nibble + 1, or 8 for symmetric weights (awq.rs:540-590).
+template <bool GPTQ>
 __global__ void __launch_bounds__(FT_THREADS, 1)
     awq_fused_tc_kernel(const FusedParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap)
 {
@@ -154,11 +160,14 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 if (it >= R && !mbar_wait(rawempty_bar(r), ph ^ 1u, p.flag, 1)) break;
                 const uint32_t dst = base + raw_base + (uint32_t)r * FT_RAW_BYTES;
                 const int qg = it * FT_BK / p.group_size;
-                mbar_arrive_expect_tx(rawfull_bar(r), FT_BOX_BYTES + FT_ZERO_BYTES + FT_SCALE_BYTES);
-                tma_load_2d(dst, &wmap, rawfull_bar(r), n0 / 8, it * FT_BK);
+                const bool with_zeros = !(GPTQ && p.sym);
+                mbar_arrive_expect_tx(rawfull_bar(r), FT_BOX_BYTES + (with_zeros ? FT_ZERO_BYTES : 0) + FT_SCALE_BYTES);
+                if (GPTQ) tma_load_2d(dst, &wmap, rawfull_bar(r), n0, it * (FT_BK / 8));
+                else tma_load_2d(dst, &wmap, rawfull_bar(r), n0 / 8, it * FT_BK);
                 // the group's zero points and scales travel with the box: a plain load issued by the unpack threads
                 // would wait a full DRAM round trip per group
-                bulk_copy_g2s(dst + FT_BOX_BYTES, p.qzeros + (size_t)qg * p.packed_out + n0 / 8, FT_ZERO_BYTES, rawfull_bar(r));
+                if (with_zeros)
+                    bulk_copy_g2s(dst + FT_BOX_BYTES, p.qzeros + (size_t)qg * p.packed_out + n0 / 8, FT_ZERO_BYTES, rawfull_bar(r));
                 bulk_copy_g2s(dst + FT_BOX_BYTES + FT_ZERO_BYTES,
                               reinterpret_cast<const uint16_t *>(p.scales) + (size_t)qg * p.n + n0, FT_SCALE_BYTES, rawfull_bar(r));
                 FT_TRACE(0, it);
@@ -180,7 +189,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     } else if (warp == 1) {
         // ---- MMA issue -------------------------------------------------------------------------------
         if (elect_one()) {
-            const uint32_t idesc = ft_idesc(p.mpad);
+            const uint32_t idesc = GPTQ ? tc_idesc(FT_ROWS, p.mpad) : ft_idesc(p.mpad);
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
@@ -190,10 +199,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 FT_TRACE(1, it);
                 tc_fence_after();
                 const uint32_t slot = base + (uint32_t)s * p.stage_bytes;
-                const uint64_t da = ft_a_desc(slot), db = kmajor_sw128_desc(slot + b_off);
+                const uint64_t da = GPTQ ? kmajor_sw128_desc(slot) : ft_a_desc(slot), db = kmajor_sw128_desc(slot + b_off);
 #pragma unroll
-                for (int kk = 0; kk < FT_BK / 16; kk++) // 16 input rows: two 1 KB atoms of A, 32 bytes inside the swizzled row of B
-                    umma_bf16(tmem_base, da + (uint64_t)kk * (2048 >> 4), db + 2 * kk, idesc, (it | kk) != 0);
+                for (int kk = 0; kk < FT_BK / 16; kk++) // 16 input rows: two 1 KB atoms of an MN-major A, 32 bytes inside a swizzled K-major row
+                    umma_bf16(tmem_base, da + (uint64_t)kk * (GPTQ ? 2 : (2048 >> 4)), db + 2 * kk, idesc, (it | kk) != 0);
                 umma_commit(empty_bar(s));
                 FT_TRACE(2, it);
                 if (++s == S) { s = 0; ph ^= 1u; }
@@ -206,8 +215,9 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         // barrier sees each of its phases.
         const int team = (warp - 4) / FT_TEAM_WARPS;
         const int ut = (threadIdx.x - 128) % (FT_TEAM_WARPS * 32);
-        constexpr int ROW_STEP = FT_BK / FT_WORDS; // this thread's rows of a stage: r0, r0 + ROW_STEP, ...
-        const int j = ut & 15, r0 = ut >> 4;       // word column (8 out features) and first row
+        constexpr int ROW_STEP = (GPTQ ? FT_BK / 8 : FT_BK) / FT_WORDS; // this thread's (packed) rows of a stage: r0, r0 + ROW_STEP, ...
+        const int j = GPTQ ? (ut & 127) : (ut & 15); // AWQ: word column (8 out features); GPTQ: out feature of the tile
+        const int r0 = GPTQ ? (ut >> 7) : (ut >> 4); // first (packed) row of this thread; the others follow ROW_STEP apart
         // A scale s (f16: 11 significant bits) is used as s_hi + s_lo, two bf16 values that
         // add up to it exactly; for d = q - z (an integer of at most 4 bits) d * s_lo is exact in bf16 and
         // fma(d, s_hi, d * s_lo) rounds the exact d * s once: the bits of bf16(f32(d) * f32(s)).
@@ -229,12 +239,15 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         };
         int cur_qg = -1;
         __nv_bfloat162 zp[4], shi[4], slo[4];
-        uint32_t nib_mask, nib_magic; // in registers, opaque to constant propagation: one LOP3 per pair instead of two
-        asm volatile("mov.b32 %0, 0x000F000F;\n\tmov.b32 %1, 0x43004300;" : "=r"(nib_mask), "=r"(nib_magic));
+        uint32_t nib_mask, nib_magic, nib_lo, nib_hi16; // in registers, opaque to constant propagation: one LOP3 per use
+        asm volatile("mov.b32 %0, 0x000F000F;\n\tmov.b32 %1, 0x43004300;\n\tmov.b32 %2, 0x0000000F;\n\tmov.b32 %3, 0x000F0000;"
+                     : "=r"(nib_mask), "=r"(nib_magic), "=r"(nib_lo), "=r"(nib_hi16));
         // byte offset of this thread's first 16-byte chunk inside the A slot; rows ROW_STEP apart are ROW_STEP * 128 bytes apart
-        const uint32_t a_off = (uint32_t)(j >> 3) * 8192u + (uint32_t)(r0 >> 3) * 1024u + (uint32_t)(r0 & 7) * 128u +
-                               (uint32_t)(((j & 7) ^ (r0 & 7)) << 4);
-        const uint32_t raw_idx = raw_base + (uint32_t)(r0 * 16 + j) * 4u;
+        // (GPTQ: out feature j is a 128-byte row of a 1 KB atom of eight rows; packed row c is its 16-byte chunk c ^ (j & 7))
+        const uint32_t a_off = GPTQ ? (uint32_t)(j >> 3) * 1024u + (uint32_t)(j & 7) * 128u
+                                    : (uint32_t)(j >> 3) * 8192u + (uint32_t)(r0 >> 3) * 1024u + (uint32_t)(r0 & 7) * 128u +
+                                          (uint32_t)(((j & 7) ^ (r0 & 7)) << 4);
+        const uint32_t raw_idx = raw_base + (uint32_t)(GPTQ ? r0 * 128 + j : r0 * 16 + j) * 4u;
         // FT_ROUND consecutive stages per round: the barrier polls, the proxy fence and the arrivals, which
         // cost more than the arithmetic of one stage, are paid once per round. Shared memory
         // is addressed with 32-bit shared-space addresses throughout (no generic-pointer arithmetic in the loop).
@@ -265,16 +278,29 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 const uint32_t ring = (uint32_t)(r + h) * FT_RAW_BYTES;
                 uint32_t w[FT_WORDS];
 #pragma unroll
-                for (int i = 0; i < FT_WORDS; i++) w[i] = lds32(box_addr0 + ring + i * ROW_STEP * 64);
+                for (int i = 0; i < FT_WORDS; i++) w[i] = lds32(box_addr0 + ring + i * ROW_STEP * (GPTQ ? 512 : 64));
                 const int qg = (it0 + h) >> p.gshift;
                 if (qg != cur_qg) { // a new quantization group: its zero points and scales sit behind the box
                     cur_qg = qg;
-                    const uint32_t zw = lds32(aux_addr0 + ring + 4 * j);
-                    split_scales(lds128(aux_addr0 + ring + FT_ZERO_BYTES + 16 * j), shi, slo);
+                    if (GPTQ) { // one out feature per thread: one zero point and one scale, both halves of the pairs alike
+                        uint32_t z1 = 8u; // symmetric weights: zero 7, + 1
+                        if (!p.sym) z1 = ((lds32(aux_addr0 + ring + 4 * (j >> 3)) >> (4 * (j & 7))) & 0xFu) + 1u;
+                        const uint32_t zv = 0x43004300u | z1 | (z1 << 16); // bf16 pair (128 + z + 1, 128 + z + 1)
+                        const uint32_t sw = lds32(aux_addr0 + ring + FT_ZERO_BYTES + 4 * (j >> 1));
+                        const uint32_t s16 = (j & 1) ? (sw >> 16) : (sw & 0xFFFFu);
+                        uint4 both;
+                        both.x = both.y = both.z = both.w = s16 | (s16 << 16);
+                        split_scales(both, shi, slo);
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const uint32_t v = ((zw >> (4 * i)) & 0x000F000Fu) | 0x43004300u; // bf16 pair (128 + z, 128 + z')
-                        zp[i] = *reinterpret_cast<const __nv_bfloat162 *>(&v);
+                        for (int i = 0; i < 4; i++) zp[i] = *reinterpret_cast<const __nv_bfloat162 *>(&zv);
+                    } else {
+                        const uint32_t zw = lds32(aux_addr0 + ring + 4 * j);
+                        split_scales(lds128(aux_addr0 + ring + FT_ZERO_BYTES + 16 * j), shi, slo);
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint32_t v = ((zw >> (4 * i)) & 0x000F000Fu) | 0x43004300u; // bf16 pair (128 + z, 128 + z')
+                            zp[i] = *reinterpret_cast<const __nv_bfloat162 *>(&v);
+                        }
                     }
                 }
 #pragma unroll
@@ -282,12 +308,22 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     uint4 o;
                     uint32_t *ov = reinterpret_cast<uint32_t *>(&o);
 #pragma unroll
-                    for (int q = 0; q < 4; q++) { // nibbles q and q + 4 are out features 2q and 2q + 1 of the word
-                        const uint32_t v = ft_and_or(w[i] >> (4 * q), nib_mask, nib_magic); // bf16 pair (128 + q, 128 + q')
+                    for (int q = 0; q < 4; q++) {
+                        uint32_t v;
+                        if (GPTQ) { // byte q of the word: rows 2q (low nibble) and 2q + 1 (high nibble), neighbours in the K-major row
+                            const uint32_t t = w[i] >> (8 * q);
+                            v = ft_and_or(t << 12, nib_hi16, ft_and_or(t, nib_lo, nib_magic));
+                        } else { // nibbles q and q + 4 are out features 2q and 2q + 1 of the word
+                            v = ft_and_or(w[i] >> (4 * q), nib_mask, nib_magic); // bf16 pair (128 + q, 128 + q')
+                        }
                         const __nv_bfloat162 d = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&v), zp[q]); // q - z, exact
                         const __nv_bfloat162 b2 = __hfma2(d, shi[q], __hmul2(d, slo[q])); // s_lo is zero for bf16 scales
                         ov[q] = *reinterpret_cast<const uint32_t *>(&b2);
                     }
+                    if (GPTQ) {
+                        const uint32_t c = (uint32_t)(r0 + i * ROW_STEP);
+                        sts128(a_addr + (my_s + h) * p.stage_bytes + ((c ^ (uint32_t)(j & 7)) << 4), o);
+                    } else
                     sts128(a_addr + (my_s + h) * p.stage_bytes + i * ROW_STEP * 128, o);
                 }
             }
@@ -345,15 +381,17 @@ bool awq_fused_supported(int m, int k, int n, int group_size, int scales_dtype, 
            (scales_dtype == OXQ_F16 || scales_dtype == OXQ_BF16) && aligned(x, 16) && aligned(qweight, 16) && aligned(scales, 16);
 }
 
+// gptq: 0 = AWQ layout, 1 = GPTQ 4-bit layout (sym: no stored zero points).
 int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype, const void *bias,
                      int bias_dtype, void *y, int y_dtype, int m, int k, int n, int group_size, int col_base, int ldy,
-                     int *flag, cudaStream_t st)
+                     int *flag, cudaStream_t st, int gptq, int sym)
 {
     FusedParams p;
     p.qzeros = qzeros; p.scales = scales; p.scales_dtype = scales_dtype; p.bias = bias; p.y = y;
     p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
     p.m = m; p.mpad = (m + 15) / 16 * 16; p.k = k; p.n = n; p.group_size = group_size; p.packed_out = n / 8;
     p.col_base = col_base; p.ldy = ldy; p.flag = flag;
+    p.sym = (gptq && (sym || qzeros == nullptr)) ? 1 : 0;
     p.gshift = 0;
     while ((FT_BK << p.gshift) < group_size) p.gshift += 1;
     p.stage_bytes = FT_A_BYTES + p.mpad * 128;
@@ -370,30 +408,28 @@ int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qze
     const size_t smem = (size_t)p.stages * p.stage_bytes + (size_t)p.raw_slots * FT_RAW_BYTES + fixed;
 
     CUtensorMap wmap, xmap;
-    CUresult r = encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, qweight, (uint64_t)p.packed_out, (uint64_t)k,
-                                 (uint64_t)p.packed_out * 4, 16, FT_BK, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    CUresult r = gptq ? encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, qweight, (uint64_t)n, (uint64_t)k / 8, (uint64_t)n * 4, 128,
+                                        FT_BK / 8, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)
+                      : encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, qweight, (uint64_t)p.packed_out, (uint64_t)k,
+                                        (uint64_t)p.packed_out * 4, 16, FT_BK, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", (int)r);
     r = encode_tiled_2d(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, (uint64_t)k, (uint64_t)m, (uint64_t)k * 2, FT_BK, (uint32_t)p.mpad,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled (x) failed with CUresult %d", (int)r);
 
-    static size_t configured[64] = {};
+    static size_t configured[2][64] = {};
     int device = 0;
     OXQ_CUDA(cudaGetDevice(&device));
-    if (device >= 64 || configured[device] < smem) {
-        OXQ_CUDA(cudaFuncSetAttribute(awq_fused_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        if (device < 64) configured[device] = smem;
+    if (device >= 64 || configured[gptq ? 1 : 0][device] < smem) {
+        if (gptq) OXQ_CUDA(cudaFuncSetAttribute(awq_fused_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        else OXQ_CUDA(cudaFuncSetAttribute(awq_fused_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (device < 64) configured[gptq ? 1 : 0][device] = smem;
     }
-    awq_fused_tc_kernel<<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
+    if (gptq) awq_fused_tc_kernel<true><<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
+    else awq_fused_tc_kernel<false><<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
     OXQ_CUDA(cudaGetLastError());
     return OXQ_OK;
 }
 
 } // namespace oxq
-
-#ifdef OXQ_TUNING
-OXQ_EXPORT int oxq_ft_trace_read(long long *host_out)
-{
-    return cudaMemcpyFromSymbol(host_out, oxq::g_ft_trace, sizeof(long long) * 12 * 64) == cudaSuccess ? 0 : -6;
-}
-#endif

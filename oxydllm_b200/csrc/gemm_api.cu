@@ -26,7 +26,7 @@ bool awq_fused_supported(int m, int k, int n, int group_size, int scales_dtype, 
                          const void *scales);
 int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype, const void *bias,
                      int bias_dtype, void *y, int y_dtype, int m, int k, int n, int group_size, int col_base, int ldy,
-                     int *flag, cudaStream_t st);
+                     int *flag, cudaStream_t st, int gptq, int sym);
 
 constexpr size_t WS_HEADER = 256;                // flag word + padding, keeps the slab 256-byte aligned
 constexpr size_t SLAB_LIMIT_BYTES = 128u << 20;  // dequantized rows held at once (whole weight if it fits)
@@ -151,7 +151,8 @@ OXQ_EXPORT int oxq_awq_gemm(const void *x, int x_dtype, const uint32_t *qweight,
     if (rc) return rc;
     // Up to 256 tokens: unpack inside the tensor-core kernel, no dense copy of the weight.
     if (awq_fused_supported(m, k, n, group_size, scales_dtype, x, qweight, scales))
-        return awq_fused_matmul(x, qweight, qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n, group_size, 0, n, c.flag, c.st);
+        return awq_fused_matmul(x, qweight, qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n, group_size, 0, n, c.flag,
+                                c.st, 0, 0);
     return run_slabs(c, [&](int n_off, int cnt) {
         return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, n_off, cnt, c.st);
     });
@@ -234,6 +235,11 @@ OXQ_EXPORT int oxq_gptq_gemm(const void *x, int x_dtype, const uint32_t *qweight
     GemmCommon c;
     int rc = prepare("oxq_gptq_gemm", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n, workspace, workspace_bytes, stream);
     if (rc) return rc;
+    // 4-bit, up to 256 tokens: unpack inside the tensor-core kernel (the same kernel as AWQ with the K-major operand).
+    if (bits == 4 && (use_sym || aligned(qzeros, 16)) &&
+        awq_fused_supported(m, k, n, group_size, scales_dtype, x, qweight, scales))
+        return awq_fused_matmul(x, qweight, use_sym ? nullptr : qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n,
+                                group_size, 0, n, c.flag, c.st, 1, use_sym);
     return run_slabs(c, [&](int n_off, int cnt) {
         return gptq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, bits, use_sym,
                                       n_off, cnt, c.st);

@@ -28,6 +28,9 @@ PACKED_SIMT_GEMV_MAX_M = 8
 # group size a power of two >= 64, 16-bit scales) leave the split-k GEMV at this batch: measured on a 4096 x 14336 layer the GEMV
 # takes 24 us at 16 tokens and 47 us at 32, the fused kernel 28 to 31 us for any batch up to 128.
 AWQ_FUSED_MIN_M = 17
+# GPTQ 4-bit layers of such shapes: the GEMV takes 25 / 28 / 35 / 48 us at 1 / 2 / 4 / 8 tokens on the same layer, the fused
+# kernel 30 us for any batch up to 64.
+GPTQ_FUSED_MIN_M = 3
 
 
 def _dt(t: torch.dtype) -> int:
@@ -267,12 +270,13 @@ class PackedQuantLinear:
     def gemv_max_m(self) -> int:
         """Largest batch the decode kernels take before the tensor-core GEMM is the better tool: 32 for the
         4-bit AWQ tensor-core GEMV (16 where the fused unpack + tcgen05 kernel takes over), 8 (one chunk of the
-        reference's batched GEMV) for GPTQ and 8-bit."""
+        reference's batched GEMV) for GPTQ and 8-bit (2 for 4-bit GPTQ shapes the fused kernel serves)."""
+        fused = (self.bits == 4 and self.out_features % 128 == 0 and self.in_features % 128 == 0 and self.group_size % 64 == 0
+                 and self.group_size & (self.group_size - 1) == 0 and self.scales.dtype in (torch.float16, torch.bfloat16))
         if self.pack_dim == "out" and self.bits == 4:
-            fused = (self.out_features % 128 == 0 and self.in_features % 128 == 0 and self.group_size % 64 == 0
-                     and self.group_size & (self.group_size - 1) == 0
-                     and self.scales.dtype in (torch.float16, torch.bfloat16))
             return AWQ_FUSED_MIN_M - 1 if fused else GEMV_MAX_M
+        if fused:
+            return GPTQ_FUSED_MIN_M - 1
         return PACKED_SIMT_GEMV_MAX_M
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -94,3 +94,44 @@ def test_shapes_outside_the_fused_kernel_keep_their_paths(cuda):
     for m in (20, 40):
         x = synth.activations(m, 512, seed=m)
         close(lin.forward(dev(x, torch.bfloat16)), oracle.linear(x, synth.bf16_round(w)))
+
+
+# ------------------------------------------------------------------ GPTQ 4-bit through the same kernel (K-major operand)
+def gptq_layer(k, n, g, seed, sym=False, scale_dtype="f16"):
+    rng = np.random.default_rng(seed)
+    qw = rng.integers(0, 2**32, size=(k // 8, n), dtype=np.uint64).astype(np.uint32)
+    qz = None if sym else rng.integers(0, 2**32, size=(k // g, n // 8), dtype=np.uint64).astype(np.uint32)
+    sc = (np.abs(rng.standard_normal((k // g, n)) * 0.02) / 7 + 1e-4).astype(np.float16)
+    if scale_dtype == "bf16":
+        sc_np = synth.bf16_round(sc.astype(np.float32))
+        sc_t = dev(sc_np, torch.bfloat16)
+    else:
+        sc_np, sc_t = sc, dev(sc)
+    raw = L.QuantWeight.new_gptq(4, sym, dev(qw.view(np.int32)), None if sym else dev(qz.view(np.int32)), sc_t)
+    return L.PackedQuantLinear(raw), oracle.gptq_dequant(qw, qz, sc_np, 4, sym)
+
+
+@pytest.mark.parametrize("k,n,g,sym,scale_dtype", [(256, 128, 64, False, "f16"), (512, 384, 128, True, "f16"),
+                                                  (1024, 256, 256, False, "bf16")])
+def test_gptq_fused_weight_tile_bit_exact_with_one_hot_rows(cuda, k, n, g, sym, scale_dtype):
+    lin, w = gptq_layer(k, n, g, seed=k + n, sym=sym, scale_dtype=scale_dtype)
+    assert lin.gemv_max_m() == L.GPTQ_FUSED_MIN_M - 1
+    want = oracle.to_bf16_bits(w)
+    for k0 in range(0, k, 256):
+        m = min(256, k - k0)
+        x = np.zeros((m, k), np.float32)
+        x[np.arange(m), k0 + np.arange(m)] = 1.0
+        y = lin.forward(dev(x, torch.bfloat16))
+        got = y.cpu().view(torch.int16).numpy().view(np.uint16)
+        assert np.array_equal(got, want[:, k0:k0 + m].T)
+    gemm.check(gemm.workspace(n, k, "cuda"))
+
+
+@pytest.mark.parametrize("m", [3, 8, 17, 64, 200, 256])
+@pytest.mark.parametrize("k,n,g,sym", [(512, 256, 128, False), (2048, 640, 64, True), (4096, 1792, 128, False)])
+def test_gptq_fused_matmul_matches_oracle(cuda, m, k, n, g, sym):
+    lin, w = gptq_layer(k, n, g, seed=m + n, sym=sym)
+    x = synth.activations(m, k, seed=m)
+    y = lin.forward(dev(x, torch.bfloat16))
+    close(y, oracle.linear(x, synth.bf16_round(w)))
+    gemm.check(gemm.workspace(n, k, "cuda"))
