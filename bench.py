@@ -505,12 +505,12 @@ def run_extras(args, world, rank, c1_layer):
         base = dev(q)
         lins = [L.Fp8Linear(base, dev(s_))] + [L.Fp8Linear(torch.roll(base, 4096 * (i + 1), 0), dev(s_)) for i in range(3)]
         res = {}
-        for m in (1, 32):
+        for m in (1, 16, 32, 128):  # through the operator: GEMV up to 16 tokens, fused widen + tcgen05 kernel up to 256
             x = dev(synth.activations(m, K, seed=m), torch.bfloat16)
             us = graph_us(lambda: [lin.forward(x) for lin in lins], len(lins))
             b = n * K + (n // 128) * (K // 128) * 4 + m * (2 * K + 2 * n)
-            res[f"gemv_m{m}"] = {"us_per_launch": round(us, 2), "gbs": round(b / us / 1e3, 1),
-                                 "frac_of_hbm_peak": round(b / us / 1e3 / hbm, 4)}
+            res[f"gemv_m{m}" if m <= 16 else f"operator_m{m}"] = {"us_per_launch": round(us, 2), "gbs": round(b / us / 1e3, 1),
+                                                                  "frac_of_hbm_peak": round(b / us / 1e3 / hbm, 4)}
         x = dev(synth.activations(2048, K, seed=5), torch.bfloat16)
         for _ in range(3):
             lins[0].forward(x)

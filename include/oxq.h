@@ -241,7 +241,9 @@ int oxq_gptq_gemm(const void *x, int x_dtype, const uint32_t *qweight, const uin
 int oxq_gguf_gemm(int ggml_type, const void *x, int x_dtype, const void *blocks, const void *bias, int bias_dtype,
                   void *y, int y_dtype, int m, int k, int n, void *workspace, size_t workspace_bytes, void *stream);
 
-/* Fp8Linear::forward for m beyond the GEMV range (linear.rs:96-145). */
+/* Fp8Linear::forward for m beyond the GEMV range (linear.rs:96-145). Up to 256 tokens, when n % 128 == 0,
+ * k % 128 == 0 and the scale blocks are multiples of 128 rows and 64 columns, the bytes are widened inside the
+ * tensor-core kernel (same bf16 weights as the dequantization kernel); otherwise slabs are dequantized. */
 int oxq_fp8_gemm(const void *x, int x_dtype, const uint8_t *weight, const float *scale_inv, int s_out, int s_in,
                  const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, void *workspace,
                  size_t workspace_bytes, void *stream);

@@ -35,7 +35,6 @@ constexpr int FT_ROUND_SLOTS = 2;                // rounds of operand slots: S =
 constexpr int FT_THREADS = (4 + FT_UNPACK_WARPS) * 32;
 constexpr int FT_BOX_BYTES = FT_BK * 16 * 4;      // 64 input rows x 16 packed words
 constexpr int FT_ZERO_BYTES = 64, FT_SCALE_BYTES = 256; // the box's group: 16 zero-point words, 128 16-bit scales
-constexpr int FT_RAW_BYTES = FT_BOX_BYTES + 384;  // ring slot: box | zero points | scales | pad to 128 bytes
 constexpr int FT_A_BYTES = FT_ROWS * FT_BK * 2;
 constexpr int FT_MAX_STAGES = FT_ROUND * FT_ROUND_SLOTS; // operand slots (A tile + x tile)
 constexpr int FT_MAX_RAW = 32;                   // ring slots of packed boxes: what is in flight from HBM
@@ -62,6 +61,8 @@ struct FusedParams {
     int stages, raw_slots, stage_bytes, tmem_cols;
     int gshift;        // log2(stages per quantization group)
     int sym;           // GPTQ: no stored zero points (zero + 1 = 8)
+    const float *scale_inv; // FP8: scale grid [s_out, s_in] or null
+    int s_in, block_out, block_in;
     int col_base, ldy; // y column of out feature 0 and the row pitch of y in elements
     int *flag;
 };
@@ -105,24 +106,32 @@ __device__ __forceinline__ uint32_t ft_idesc(int n)
 // GPTQ = true:  GPTQ 4-bit layout (a word is eight input rows of one out feature, nibble i = row 8 r + i; A operand
 //               K-major: the word becomes one 16-byte chunk of the out feature's 128-byte row). The box is 8 packed
 //               rows x 128 words; the zero point is the stored nibble + 1, or 8 for symmetric weights (awq.rs:540-590).
-template <bool GPTQ>
+// LAYOUT 2: FP8 E4M3 [n, k] row-major with an f32 scale grid (Fp8Linear, linear.rs:96-145). The box is 128 rows x
+//               64 bytes, already K-major; every thread widens 32 bytes of one row (e4m3 -> f16 exactly in hardware,
+//               -> f32, times the block's scale, one rounding to bf16: the bits of the dequantization kernel). The
+//               tile's row of the scale grid is copied to shared memory once.
+template <int LAYOUT>
 __global__ void __launch_bounds__(FT_THREADS, 1)
     awq_fused_tc_kernel(const FusedParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap)
 {
+    constexpr bool GPTQ = LAYOUT == 1, FP8 = LAYOUT == 2;
+    constexpr int BOX_BYTES = FP8 ? FT_ROWS * FT_BK : FT_BOX_BYTES; // one stage of packed weights
+    constexpr int RAW_BYTES = BOX_BYTES + (FP8 ? 0 : 384);          // ring slot: box | zero points | scales | pad
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u; // operand slots want 1 KB alignment
     unsigned char *base_ptr = smem_raw + (base - smem_u32(smem_raw));
     // operand slots (A tile + x tile) | ring of packed boxes | barriers | tensor-memory address
     const int S = p.stages, R = p.raw_slots;
     const uint32_t raw_base = (uint32_t)S * p.stage_bytes;
-    const uint32_t bars = base + raw_base + (uint32_t)R * FT_RAW_BYTES;
+    const uint32_t bars = base + raw_base + (uint32_t)R * RAW_BYTES;
     auto rawfull_bar = [&](int r) { return bars + 8u * r; };
     auto rawempty_bar = [&](int r) { return bars + 8u * (FT_MAX_RAW + r); };
     auto xfull_bar = [&](int s) { return bars + 8u * (2 * FT_MAX_RAW + s); };
     auto ready_bar = [&](int s) { return bars + 8u * (2 * FT_MAX_RAW + FT_MAX_STAGES + s); };
     auto empty_bar = [&](int s) { return bars + 8u * (2 * FT_MAX_RAW + 2 * FT_MAX_STAGES + s); };
     const uint32_t acc_bar = bars + 8u * (2 * FT_MAX_RAW + 3 * FT_MAX_STAGES);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + raw_base + (size_t)R * FT_RAW_BYTES + 8 * FT_NUM_BARS);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + raw_base + (size_t)R * RAW_BYTES + 8 * FT_NUM_BARS);
+    float *fp8_scales = reinterpret_cast<float *>(tmem_slot + 4); // FP8: the tile's row of the scale grid, one float per k block
     const uint32_t b_off = FT_A_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -146,6 +155,11 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         tmem_alloc(smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
         tmem_relinquish();
     }
+    if (FP8 && warp == 3) {
+        const int cnt = p.k / p.block_in;
+        for (int i = lane; i < cnt; i += 32)
+            fp8_scales[i] = p.scale_inv ? __ldg(p.scale_inv + (size_t)(n0 / p.block_out) * p.s_in + i) : 1.0f;
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -158,17 +172,24 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             uint32_t ph = 0;
             for (int it = 0; it < nk; it++) {
                 if (it >= R && !mbar_wait(rawempty_bar(r), ph ^ 1u, p.flag, 1)) break;
-                const uint32_t dst = base + raw_base + (uint32_t)r * FT_RAW_BYTES;
+                const uint32_t dst = base + raw_base + (uint32_t)r * RAW_BYTES;
                 const int qg = it * FT_BK / p.group_size;
+                if (FP8) { // the box alone
+                    mbar_arrive_expect_tx(rawfull_bar(r), BOX_BYTES);
+                    tma_load_2d(dst, &wmap, rawfull_bar(r), it * FT_BK, n0);
+                    FT_TRACE(0, it);
+                    if (++r == R) { r = 0; ph ^= 1u; }
+                    continue;
+                }
                 const bool with_zeros = !(GPTQ && p.sym);
-                mbar_arrive_expect_tx(rawfull_bar(r), FT_BOX_BYTES + (with_zeros ? FT_ZERO_BYTES : 0) + FT_SCALE_BYTES);
+                mbar_arrive_expect_tx(rawfull_bar(r), BOX_BYTES + (with_zeros ? FT_ZERO_BYTES : 0) + FT_SCALE_BYTES);
                 if (GPTQ) tma_load_2d(dst, &wmap, rawfull_bar(r), n0, it * (FT_BK / 8));
                 else tma_load_2d(dst, &wmap, rawfull_bar(r), n0 / 8, it * FT_BK);
                 // the group's zero points and scales travel with the box: a plain load issued by the unpack threads
                 // would wait a full DRAM round trip per group
                 if (with_zeros)
-                    bulk_copy_g2s(dst + FT_BOX_BYTES, p.qzeros + (size_t)qg * p.packed_out + n0 / 8, FT_ZERO_BYTES, rawfull_bar(r));
-                bulk_copy_g2s(dst + FT_BOX_BYTES + FT_ZERO_BYTES,
+                    bulk_copy_g2s(dst + BOX_BYTES, p.qzeros + (size_t)qg * p.packed_out + n0 / 8, FT_ZERO_BYTES, rawfull_bar(r));
+                bulk_copy_g2s(dst + BOX_BYTES + FT_ZERO_BYTES,
                               reinterpret_cast<const uint16_t *>(p.scales) + (size_t)qg * p.n + n0, FT_SCALE_BYTES, rawfull_bar(r));
                 FT_TRACE(0, it);
                 if (++r == R) { r = 0; ph ^= 1u; }
@@ -189,7 +210,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
     } else if (warp == 1) {
         // ---- MMA issue -------------------------------------------------------------------------------
         if (elect_one()) {
-            const uint32_t idesc = GPTQ ? tc_idesc(FT_ROWS, p.mpad) : ft_idesc(p.mpad);
+            const uint32_t idesc = (GPTQ || FP8) ? tc_idesc(FT_ROWS, p.mpad) : ft_idesc(p.mpad);
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
@@ -199,10 +220,10 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 FT_TRACE(1, it);
                 tc_fence_after();
                 const uint32_t slot = base + (uint32_t)s * p.stage_bytes;
-                const uint64_t da = GPTQ ? kmajor_sw128_desc(slot) : ft_a_desc(slot), db = kmajor_sw128_desc(slot + b_off);
+                const uint64_t da = (GPTQ || FP8) ? kmajor_sw128_desc(slot) : ft_a_desc(slot), db = kmajor_sw128_desc(slot + b_off);
 #pragma unroll
                 for (int kk = 0; kk < FT_BK / 16; kk++) // 16 input rows: two 1 KB atoms of an MN-major A, 32 bytes inside a swizzled K-major row
-                    umma_bf16(tmem_base, da + (uint64_t)kk * (GPTQ ? 2 : (2048 >> 4)), db + 2 * kk, idesc, (it | kk) != 0);
+                    umma_bf16(tmem_base, da + (uint64_t)kk * ((GPTQ || FP8) ? 2 : (2048 >> 4)), db + 2 * kk, idesc, (it | kk) != 0);
                 umma_commit(empty_bar(s));
                 FT_TRACE(2, it);
                 if (++s == S) { s = 0; ph ^= 1u; }
@@ -253,7 +274,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
         // is addressed with 32-bit shared-space addresses throughout (no generic-pointer arithmetic in the loop).
         const uint32_t a_addr = base + a_off;                           // first 16-byte chunk in slot 0
         const uint32_t box_addr0 = base + raw_idx;                      // this thread's first word in ring slot 0
-        const uint32_t aux_addr0 = base + raw_base + FT_BOX_BYTES;      // zero points of ring slot 0
+        const uint32_t aux_addr0 = base + raw_base + BOX_BYTES;      // zero points of ring slot 0
         int r = FT_ROUND * team;                                       // first ring slot of the round
         uint32_t my_s = (uint32_t)(FT_ROUND * team) % (uint32_t)S;      // first operand slot of the round
         uint32_t ph = ((uint32_t)(FT_ROUND * team) / (uint32_t)S) & 1u, rph = 0; // phases of the operand-slot and ring barriers
@@ -275,7 +296,36 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             if (ut == 0) FT_TRACE(3, it0);
 #pragma unroll
             for (int h = 0; h < FT_ROUND; h++) {
-                const uint32_t ring = (uint32_t)(r + h) * FT_RAW_BYTES;
+                const uint32_t ring = (uint32_t)(r + h) * RAW_BYTES;
+                if constexpr (FP8) {
+                    // thread = (row, half): 32 bytes of the row -> 32 bf16 = four 16-byte chunks of the K-major row
+                    const int row = ut >> 1, half = ut & 1;
+                    const float sc = fp8_scales[((it0 + h) * FT_BK) / p.block_in];
+                    const uint32_t src = base + raw_base + ring + (uint32_t)row * 64u + (uint32_t)half * 32u;
+                    const uint4 lo = lds128(src), hi = lds128(src + 16);
+                    const uint32_t wv[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                    const uint32_t dst = base + (my_s + h) * p.stage_bytes + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; c4++) {
+                        uint4 o;
+                        uint32_t *ov = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+                        for (int q = 0; q < 2; q++) {
+                            uint32_t h01, h23;
+                            asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+                                "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+                                : "=r"(h01), "=r"(h23)
+                                : "r"(wv[2 * c4 + q]));
+                            const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&h01));
+                            const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&h23));
+                            const __nv_bfloat162 b01 = __floats2bfloat162_rn(__fmul_rn(sc, f01.x), __fmul_rn(sc, f01.y));
+                            const __nv_bfloat162 b23 = __floats2bfloat162_rn(__fmul_rn(sc, f23.x), __fmul_rn(sc, f23.y));
+                            ov[2 * q] = *reinterpret_cast<const uint32_t *>(&b01);
+                            ov[2 * q + 1] = *reinterpret_cast<const uint32_t *>(&b23);
+                        }
+                        sts128(dst + ((((uint32_t)(half * 4 + c4)) ^ (uint32_t)(row & 7)) << 4), o);
+                    }
+                } else {
                 uint32_t w[FT_WORDS];
 #pragma unroll
                 for (int i = 0; i < FT_WORDS; i++) w[i] = lds32(box_addr0 + ring + i * ROW_STEP * (GPTQ ? 512 : 64));
@@ -326,6 +376,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                     } else
                     sts128(a_addr + (my_s + h) * p.stage_bytes + i * ROW_STEP * 128, o);
                 }
+                } // layouts with packed words
             }
             if (ut == 0) FT_TRACE(4, it0);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // generic-proxy stores -> visible to the MMA
@@ -381,55 +432,90 @@ bool awq_fused_supported(int m, int k, int n, int group_size, int scales_dtype, 
            (scales_dtype == OXQ_F16 || scales_dtype == OXQ_BF16) && aligned(x, 16) && aligned(qweight, 16) && aligned(scales, 16);
 }
 
-// gptq: 0 = AWQ layout, 1 = GPTQ 4-bit layout (sym: no stored zero points).
-int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype, const void *bias,
-                     int bias_dtype, void *y, int y_dtype, int m, int k, int n, int group_size, int col_base, int ldy,
-                     int *flag, cudaStream_t st, int gptq, int sym)
+// layout 0 = AWQ, 1 = GPTQ 4-bit (sym: no stored zero points), 2 = FP8 E4M3 (qweight = the bytes, scale_inv / s_in /
+// block_out / block_in describe the scale grid; qzeros, scales unused).
+static int fused_launch(int layout, FusedParams p, const void *x, const void *qweight, int m, int k, int n, cudaStream_t st)
 {
-    FusedParams p;
-    p.qzeros = qzeros; p.scales = scales; p.scales_dtype = scales_dtype; p.bias = bias; p.y = y;
-    p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
-    p.m = m; p.mpad = (m + 15) / 16 * 16; p.k = k; p.n = n; p.group_size = group_size; p.packed_out = n / 8;
-    p.col_base = col_base; p.ldy = ldy; p.flag = flag;
-    p.sym = (gptq && (sym || qzeros == nullptr)) ? 1 : 0;
-    p.gshift = 0;
-    while ((FT_BK << p.gshift) < group_size) p.gshift += 1;
+    const int raw_bytes = layout == 2 ? FT_ROWS * FT_BK : FT_BOX_BYTES + 384;
+    p.mpad = (m + 15) / 16 * 16;
     p.stage_bytes = FT_A_BYTES + p.mpad * 128;
-    const int fixed = 1024 + 8 * FT_NUM_BARS + 16;
+    const int fixed = 1024 + 8 * FT_NUM_BARS + 16 + (layout == 2 ? (k / p.block_in) * 4 + 16 : 0);
     const int nk = k / FT_BK;
     // Four operand slots (two rounds of two stages); the rest of shared memory is the ring of packed boxes, a multiple of four.
     p.stages = FT_MAX_STAGES;
-    p.raw_slots = (FT_SMEM_BUDGET - fixed - p.stages * p.stage_bytes) / FT_RAW_BYTES / FT_MAX_STAGES * FT_MAX_STAGES;
+    p.raw_slots = (FT_SMEM_BUDGET - fixed - p.stages * p.stage_bytes) / raw_bytes / FT_MAX_STAGES * FT_MAX_STAGES;
     if (p.raw_slots > FT_MAX_RAW) p.raw_slots = FT_MAX_RAW;
     if (const char *env = tuning_env("OXQ_AWQ_FUSED_RAW")) p.raw_slots = atoi(env) < p.raw_slots ? atoi(env) : p.raw_slots;
-    OXQ_REQUIRE(p.raw_slots >= FT_MAX_STAGES && nk >= 1, OXQ_ERR_UNSUPPORTED, "awq_fused_matmul: no room for the ring of boxes");
+    if (p.raw_slots < FT_MAX_STAGES || nk < 1) return OXQ_ERR_UNSUPPORTED; // the caller takes the slab path
     p.tmem_cols = 32;
     while (p.tmem_cols < p.mpad) p.tmem_cols *= 2;
-    const size_t smem = (size_t)p.stages * p.stage_bytes + (size_t)p.raw_slots * FT_RAW_BYTES + fixed;
+    const size_t smem = (size_t)p.stages * p.stage_bytes + (size_t)p.raw_slots * raw_bytes + fixed;
 
     CUtensorMap wmap, xmap;
-    CUresult r = gptq ? encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, qweight, (uint64_t)n, (uint64_t)k / 8, (uint64_t)n * 4, 128,
-                                        FT_BK / 8, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)
-                      : encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, qweight, (uint64_t)p.packed_out, (uint64_t)k,
-                                        (uint64_t)p.packed_out * 4, 16, FT_BK, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    CUresult r;
+    if (layout == 1)
+        r = encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, qweight, (uint64_t)n, (uint64_t)k / 8, (uint64_t)n * 4, 128, FT_BK / 8,
+                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    else if (layout == 2)
+        r = encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, qweight, (uint64_t)k, (uint64_t)n, (uint64_t)k, FT_BK, FT_ROWS,
+                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
+    else
+        r = encode_tiled_2d(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, qweight, (uint64_t)p.packed_out, (uint64_t)k, (uint64_t)p.packed_out * 4,
+                            16, FT_BK, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", (int)r);
     r = encode_tiled_2d(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, (uint64_t)k, (uint64_t)m, (uint64_t)k * 2, FT_BK, (uint32_t)p.mpad,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     OXQ_REQUIRE(r == CUDA_SUCCESS, OXQ_ERR_CUDA, "cuTensorMapEncodeTiled (x) failed with CUresult %d", (int)r);
 
-    static size_t configured[2][64] = {};
+    static size_t configured[3][64] = {};
     int device = 0;
     OXQ_CUDA(cudaGetDevice(&device));
-    if (device >= 64 || configured[gptq ? 1 : 0][device] < smem) {
-        if (gptq) OXQ_CUDA(cudaFuncSetAttribute(awq_fused_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        else OXQ_CUDA(cudaFuncSetAttribute(awq_fused_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        if (device < 64) configured[gptq ? 1 : 0][device] = smem;
+    if (device >= 64 || configured[layout][device] < smem) {
+        if (layout == 1) OXQ_CUDA(cudaFuncSetAttribute(awq_fused_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        else if (layout == 2) OXQ_CUDA(cudaFuncSetAttribute(awq_fused_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        else OXQ_CUDA(cudaFuncSetAttribute(awq_fused_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (device < 64) configured[layout][device] = smem;
     }
-    if (gptq) awq_fused_tc_kernel<true><<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
-    else awq_fused_tc_kernel<false><<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
+    if (layout == 1) awq_fused_tc_kernel<1><<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
+    else if (layout == 2) awq_fused_tc_kernel<2><<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
+    else awq_fused_tc_kernel<0><<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
     OXQ_CUDA(cudaGetLastError());
     return OXQ_OK;
+}
+
+int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype, const void *bias,
+                     int bias_dtype, void *y, int y_dtype, int m, int k, int n, int group_size, int col_base, int ldy,
+                     int *flag, cudaStream_t st, int gptq, int sym)
+{
+    FusedParams p = {};
+    p.qzeros = qzeros; p.scales = scales; p.scales_dtype = scales_dtype; p.bias = bias; p.y = y;
+    p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
+    p.m = m; p.k = k; p.n = n; p.group_size = group_size; p.packed_out = n / 8;
+    p.col_base = col_base; p.ldy = ldy; p.flag = flag;
+    p.sym = (gptq && (sym || qzeros == nullptr)) ? 1 : 0;
+    p.gshift = 0;
+    while ((FT_BK << p.gshift) < group_size) p.gshift += 1;
+    p.block_in = FT_BK; p.block_out = FT_ROWS; p.s_in = 1;
+    return fused_launch(gptq ? 1 : 0, p, x, qweight, m, k, n, st);
+}
+
+bool fp8_fused_supported(int m, int k, int n, int block_out, int block_in, const void *x, const void *weight, const void *scale_inv)
+{
+    if (const char *env = tuning_env("OXQ_AWQ_FUSED"))
+        if (env[0] == '0') return false;
+    return m >= 1 && m <= FT_MAX_M && n % FT_ROWS == 0 && k % (FT_BK * FT_ROUND) == 0 && block_out % FT_ROWS == 0 &&
+           block_in % FT_BK == 0 && k / block_in <= 1024 && aligned(x, 16) && aligned(weight, 16) && aligned(scale_inv, 4);
+}
+
+int fp8_fused_matmul(const void *x, const uint8_t *weight, const float *scale_inv, int s_in, int block_out, int block_in,
+                     const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, int *flag, cudaStream_t st)
+{
+    FusedParams p = {};
+    p.bias = bias; p.y = y; p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
+    p.m = m; p.k = k; p.n = n; p.group_size = FT_BK; p.packed_out = n / 8;
+    p.col_base = 0; p.ldy = n; p.flag = flag;
+    p.scale_inv = scale_inv; p.s_in = s_in; p.block_out = block_out; p.block_in = block_in;
+    return fused_launch(2, p, x, weight, m, k, n, st);
 }
 
 } // namespace oxq

@@ -24,6 +24,9 @@ int mxfp4_dequant_rows_bf16(const uint8_t *blocks, const uint8_t *scales, __nv_b
 bool gguf_block_layout_host(int ggml_type, int &bel, int &bby);
 bool awq_fused_supported(int m, int k, int n, int group_size, int scales_dtype, const void *x, const void *qweight,
                          const void *scales);
+bool fp8_fused_supported(int m, int k, int n, int block_out, int block_in, const void *x, const void *weight, const void *scale_inv);
+int fp8_fused_matmul(const void *x, const uint8_t *weight, const float *scale_inv, int s_in, int block_out, int block_in,
+                     const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, int *flag, cudaStream_t st);
 int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype, const void *bias,
                      int bias_dtype, void *y, int y_dtype, int m, int k, int n, int group_size, int col_base, int ldy,
                      int *flag, cudaStream_t st, int gptq, int sym);
@@ -151,8 +154,11 @@ OXQ_EXPORT int oxq_awq_gemm(const void *x, int x_dtype, const uint32_t *qweight,
     if (rc) return rc;
     // Up to 256 tokens: unpack inside the tensor-core kernel, no dense copy of the weight.
     if (awq_fused_supported(m, k, n, group_size, scales_dtype, x, qweight, scales))
-        return awq_fused_matmul(x, qweight, qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n, group_size, 0, n, c.flag,
-                                c.st, 0, 0);
+    {
+        rc = awq_fused_matmul(x, qweight, qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n, group_size, 0, n, c.flag,
+                              c.st, 0, 0);
+        if (rc != OXQ_ERR_UNSUPPORTED) return rc;
+    }
     return run_slabs(c, [&](int n_off, int cnt) {
         return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, n_off, cnt, c.st);
     });
@@ -238,8 +244,11 @@ OXQ_EXPORT int oxq_gptq_gemm(const void *x, int x_dtype, const uint32_t *qweight
     // 4-bit, up to 256 tokens: unpack inside the tensor-core kernel (the same kernel as AWQ with the K-major operand).
     if (bits == 4 && (use_sym || aligned(qzeros, 16)) &&
         awq_fused_supported(m, k, n, group_size, scales_dtype, x, qweight, scales))
-        return awq_fused_matmul(x, qweight, use_sym ? nullptr : qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n,
-                                group_size, 0, n, c.flag, c.st, 1, use_sym);
+    {
+        rc = awq_fused_matmul(x, qweight, use_sym ? nullptr : qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n,
+                              group_size, 0, n, c.flag, c.st, 1, use_sym);
+        if (rc != OXQ_ERR_UNSUPPORTED) return rc;
+    }
     return run_slabs(c, [&](int n_off, int cnt) {
         return gptq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n, group_size, bits, use_sym,
                                       n_off, cnt, c.st);
@@ -300,6 +309,11 @@ OXQ_EXPORT int oxq_fp8_gemm(const void *x, int x_dtype, const uint8_t *weight, c
     GemmCommon c;
     int rc = prepare("oxq_fp8_gemm", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n, workspace, workspace_bytes, stream);
     if (rc) return rc;
+    // Up to 256 tokens: widen the bytes inside the tensor-core kernel, no dense copy of the weight.
+    if (fp8_fused_supported(m, k, n, bo, bi, x, weight, scale_inv)) {
+        rc = fp8_fused_matmul(x, weight, scale_inv, scale_inv ? s_in : 1, bo, bi, bias, bias_dtype, y, y_dtype, m, k, n, c.flag, c.st);
+        if (rc != OXQ_ERR_UNSUPPORTED) return rc;
+    }
     return run_slabs(c, [&](int n_off, int cnt) {
         return fp8_dequant_rows_bf16(weight, scale_inv, scale_inv ? s_in : 1, bo, bi, c.slab, k, n_off, cnt, c.st);
     });

@@ -135,3 +135,36 @@ def test_gptq_fused_matmul_matches_oracle(cuda, m, k, n, g, sym):
     y = lin.forward(dev(x, torch.bfloat16))
     close(y, oracle.linear(x, synth.bf16_round(w)))
     gemm.check(gemm.workspace(n, k, "cuda"))
+
+
+# ------------------------------------------------------------------ FP8 E4M3 block-scaled through the same kernel
+@pytest.mark.parametrize("k,n,block", [(256, 128, 128), (1024, 384, 128), (512, 256, None)])
+def test_fp8_fused_weight_tile_bit_exact_with_one_hot_rows(cuda, k, n, block):
+    w8, sinv = synth.fp8_layer(n, k, seed=k + n)
+    if block is None:
+        sinv = None  # unscaled weight
+    lin = L.Fp8Linear(dev(w8), None if sinv is None else dev(sinv))
+    want = oracle.to_bf16_bits(oracle.fp8_dequant(w8, sinv)).copy()
+    want[want == 0x8000] = 0  # a -0 weight leaves the sum of +0 products at +0
+    for k0 in range(0, k, 256):
+        m = min(256, k - k0)
+        x = np.zeros((m, k), np.float32)
+        x[np.arange(m), k0 + np.arange(m)] = 1.0
+        y = lin.forward(dev(x, torch.bfloat16))
+        got = y.cpu().view(torch.int16).numpy().view(np.uint16)
+        assert np.array_equal(got, want[:, k0:k0 + m].T)
+    gemm.check(gemm.workspace(n, k, "cuda"))
+
+
+@pytest.mark.parametrize("m", [17, 32, 64, 130, 256])
+@pytest.mark.parametrize("k,n,bias", [(512, 256, True), (2048, 640, False), (4096, 1792, False)])
+def test_fp8_fused_matmul_matches_oracle(cuda, m, k, n, bias):
+    w8, sinv = synth.fp8_layer(n, k, seed=m + n)
+    b = synth.bf16_round(np.random.default_rng(m).standard_normal(n).astype(np.float32)) if bias else None
+    lin = L.Fp8Linear(dev(w8), dev(sinv), dev(b, torch.bfloat16) if bias else None)
+    s, s_out, s_in = lin._grid()
+    assert lin.gemv_max_m(s_out, s_in) == L.AWQ_FUSED_MIN_M - 1
+    x = synth.activations(m, k, seed=m)
+    y = lin.forward(dev(x, torch.bfloat16))
+    close(y, oracle.linear(x, synth.bf16_round(oracle.fp8_dequant(w8, sinv)), b))
+    gemm.check(gemm.workspace(n, k, "cuda"))
