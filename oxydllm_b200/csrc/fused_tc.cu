@@ -31,7 +31,7 @@ constexpr int FT_TEAMS = 2;                      // teams of unpack warps take r
 constexpr int FT_TEAM_WARPS = FT_UNPACK_WARPS / FT_TEAMS;
 constexpr int FT_WORDS = FT_BK * 16 / (FT_TEAM_WARPS * 32); // packed words per thread and stage
 constexpr int FT_ROUND = 2;                      // stages per round: polls, proxy fence and arrivals are paid once per round
-constexpr int FT_ROUND_SLOTS = 2;                // rounds of operand slots: S = FT_ROUND * FT_ROUND_SLOTS, a multiple of the teams' rounds
+constexpr int FT_ROUND_SLOTS = 4;                // most rounds of operand slots (S = FT_ROUND * 2 or FT_ROUND * 4: multiples of the teams' rounds)
 constexpr int FT_THREADS = (4 + FT_UNPACK_WARPS) * 32;
 constexpr int FT_BOX_BYTES = FT_BK * 16 * 4;      // 64 input rows x 16 packed words
 constexpr int FT_ZERO_BYTES = 64, FT_SCALE_BYTES = 256; // the box's group: 16 zero-point words, 128 16-bit scales
@@ -441,12 +441,17 @@ static int fused_launch(int layout, FusedParams p, const void *x, const void *qw
     p.stage_bytes = FT_A_BYTES + p.mpad * 128;
     const int fixed = 1024 + 8 * FT_NUM_BARS + 16 + (layout == 2 ? (k / p.block_in) * 4 + 16 : 0);
     const int nk = k / FT_BK;
-    // Four operand slots (two rounds of two stages); the rest of shared memory is the ring of packed boxes, a multiple of four.
-    p.stages = FT_MAX_STAGES;
-    p.raw_slots = (FT_SMEM_BUDGET - fixed - p.stages * p.stage_bytes) / raw_bytes / FT_MAX_STAGES * FT_MAX_STAGES;
+    // FP8: eight operand slots (each team two rounds ahead of the MMAs) when that leaves at least eight boxes in flight,
+    // else four; the rest of shared memory is the ring of packed boxes, a multiple of four. (FP8, 32 tokens on a
+    // 14336 x 4096 layer: 29.2 us with four slots, 24.3 us with eight; AWQ, bound by its unpack arithmetic: no change.)
+    constexpr int UNIT = FT_ROUND * FT_TEAMS;
+    p.stages = layout == 2 ? 2 * UNIT : UNIT; // the 4-bit layouts lose a little to the shallower ring (GPTQ, 64 tokens: 31.4 -> 33.3 us)
+    if ((FT_SMEM_BUDGET - fixed - p.stages * p.stage_bytes) / raw_bytes < 8) p.stages = UNIT;
+    if (const char *env = tuning_env("OXQ_AWQ_FUSED_STAGES")) p.stages = atoi(env) == UNIT ? UNIT : p.stages;
+    p.raw_slots = (FT_SMEM_BUDGET - fixed - p.stages * p.stage_bytes) / raw_bytes / UNIT * UNIT;
     if (p.raw_slots > FT_MAX_RAW) p.raw_slots = FT_MAX_RAW;
     if (const char *env = tuning_env("OXQ_AWQ_FUSED_RAW")) p.raw_slots = atoi(env) < p.raw_slots ? atoi(env) : p.raw_slots;
-    if (p.raw_slots < FT_MAX_STAGES || nk < 1) return OXQ_ERR_UNSUPPORTED; // the caller takes the slab path
+    if (p.raw_slots < UNIT || nk < 1) return OXQ_ERR_UNSUPPORTED; // the caller takes the slab path
     p.tmem_cols = 32;
     while (p.tmem_cols < p.mpad) p.tmem_cols *= 2;
     const size_t smem = (size_t)p.stages * p.stage_bytes + (size_t)p.raw_slots * raw_bytes + fixed;

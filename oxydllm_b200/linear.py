@@ -417,8 +417,8 @@ class Fp8Linear:
 
     def gemv_max_m(self, s_out: int, s_in: int) -> int:
         """Largest batch for the decode GEMV: 16 where the fused widen + tcgen05 kernel serves the layer (out_features % 128,
-        in_features % 128, scale blocks of a multiple of 128 rows and 64 columns; 28 us for up to 64 tokens on a
-        14336 x 4096 layer against 45 us for the GEMV at 32), else 32."""
+        in_features % 128, scale blocks of a multiple of 128 rows and 64 columns; 24 us for up to 32 tokens on a
+        14336 x 4096 layer against 25 / 45 us for the GEMV at 16 / 32), else 32."""
         n, k = self.out_features, self.in_features
         bo, bi = (n // s_out, k // s_in) if s_out and s_in else (n, k)
         fused = n % 128 == 0 and k % 128 == 0 and bo % 128 == 0 and bi % 64 == 0
