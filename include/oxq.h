@@ -177,9 +177,10 @@ int oxq_w8a16_dequant(const uint32_t *qweight, const uint32_t *qzeros, const voi
  * oxq_gemm_workspace_bytes(n, k) bytes; its first word is a flag that a
  * kernel sets if one of its bounded waits ran out. The flag is sticky: no
  * call clears it, it keeps the code of the FIRST wait that ran out in any call
- * on this workspace until oxq_gemm_check reports and clears it. Fresh
- * workspace memory must start with a zero flag: allocate it zero-filled or
- * call oxq_gemm_workspace_init once. Calls sharing a workspace must be
+ * on this workspace until oxq_gemm_check reports and clears it. The rest of
+ * the 256-byte header holds arrival tickets of the fused kernel's k splits
+ * (zero between calls). Fresh workspace memory must start with a zeroed
+ * header: allocate it zero-filled or call oxq_gemm_workspace_init once. Calls sharing a workspace must be
  * stream-ordered. The same holds for the workspaces of
  * oxq_awq_decode_matmul and oxq_gptoss_moe_forward. */
 

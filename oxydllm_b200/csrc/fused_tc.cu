@@ -65,6 +65,9 @@ struct FusedParams {
     int s_in, block_out, block_in;
     int col_base, ldy; // y column of out feature 0 and the row pitch of y in elements
     int *flag;
+    int sk;              // k splits per tile (grid y); > 1: partial tiles meet in `partials`, the last CTA of a tile adds them
+    float *partials;     // [tile][split][mpad][128] f32
+    unsigned int *tickets; // 16-bit arrival counters, two per word, zero between calls
 };
 
 // A operand: 16-bit, MN-major, 128-byte swizzle. An atom is 8 input rows x 64 out features (1 KB); atoms of
@@ -136,7 +139,8 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * FT_ROWS;
-    const int nk = p.k / FT_BK;
+    const int nk = p.k / FT_BK / p.sk;        // stages of this CTA: split sk of the tile takes stages [sbase, sbase + nk)
+    const int sbase = (int)blockIdx.y * nk;
 
     if (threadIdx.x == 0) {
         for (int r = 0; r < R; r++) {
@@ -173,18 +177,18 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             for (int it = 0; it < nk; it++) {
                 if (it >= R && !mbar_wait(rawempty_bar(r), ph ^ 1u, p.flag, 1)) break;
                 const uint32_t dst = base + raw_base + (uint32_t)r * RAW_BYTES;
-                const int qg = it * FT_BK / p.group_size;
+                const int qg = (sbase + it) * FT_BK / p.group_size;
                 if (FP8) { // the box alone
                     mbar_arrive_expect_tx(rawfull_bar(r), BOX_BYTES);
-                    tma_load_2d(dst, &wmap, rawfull_bar(r), it * FT_BK, n0);
+                    tma_load_2d(dst, &wmap, rawfull_bar(r), (sbase + it) * FT_BK, n0);
                     FT_TRACE(0, it);
                     if (++r == R) { r = 0; ph ^= 1u; }
                     continue;
                 }
                 const bool with_zeros = !(GPTQ && p.sym);
                 mbar_arrive_expect_tx(rawfull_bar(r), BOX_BYTES + (with_zeros ? FT_ZERO_BYTES : 0) + FT_SCALE_BYTES);
-                if (GPTQ) tma_load_2d(dst, &wmap, rawfull_bar(r), n0, it * (FT_BK / 8));
-                else tma_load_2d(dst, &wmap, rawfull_bar(r), n0 / 8, it * FT_BK);
+                if (GPTQ) tma_load_2d(dst, &wmap, rawfull_bar(r), n0, (sbase + it) * (FT_BK / 8));
+                else tma_load_2d(dst, &wmap, rawfull_bar(r), n0 / 8, (sbase + it) * FT_BK);
                 // the group's zero points and scales travel with the box: a plain load issued by the unpack threads
                 // would wait a full DRAM round trip per group
                 if (with_zeros)
@@ -203,7 +207,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
             for (int it = 0; it < nk; it++) {
                 if (it >= S && !mbar_wait(empty_bar(s), ph ^ 1u, p.flag, 5)) break;
                 mbar_arrive_expect_tx(xfull_bar(s), (uint32_t)p.mpad * 128u);
-                tma_load_2d(base + (uint32_t)s * p.stage_bytes + b_off, &xmap, xfull_bar(s), it * FT_BK, 0);
+                tma_load_2d(base + (uint32_t)s * p.stage_bytes + b_off, &xmap, xfull_bar(s), (sbase + it) * FT_BK, 0);
                 if (++s == S) { s = 0; ph ^= 1u; }
             }
         }
@@ -300,7 +304,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 if constexpr (FP8) {
                     // thread = (row, half): 32 bytes of the row -> 32 bf16 = four 16-byte chunks of the K-major row
                     const int row = ut >> 1, half = ut & 1;
-                    const float sc = fp8_scales[((it0 + h) * FT_BK) / p.block_in];
+                    const float sc = fp8_scales[((sbase + it0 + h) * FT_BK) / p.block_in];
                     const uint32_t src = base + raw_base + ring + (uint32_t)row * 64u + (uint32_t)half * 32u;
                     const uint4 lo = lds128(src), hi = lds128(src + 16);
                     const uint32_t wv[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
@@ -329,7 +333,7 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
                 uint32_t w[FT_WORDS];
 #pragma unroll
                 for (int i = 0; i < FT_WORDS; i++) w[i] = lds32(box_addr0 + ring + i * ROW_STEP * (GPTQ ? 512 : 64));
-                const int qg = (it0 + h) >> p.gshift;
+                const int qg = (sbase + it0 + h) >> p.gshift;
                 if (qg != cur_qg) { // a new quantization group: its zero points and scales sit behind the box
                     cur_qg = qg;
                     if (GPTQ) { // one out feature per thread: one zero point and one scale, both halves of the pairs alike
@@ -397,19 +401,70 @@ __global__ void __launch_bounds__(FT_THREADS, 1)
 
         // ---- epilogue: lane = out feature inside this warp's quarter of the accumulator rows -----------------
         if (ok) ok = mbar_wait(acc_bar, 0, p.flag, 4);
-        if (ok) {
-            tc_fence_after();
-            const int quad = warp & 3, turn = (warp - 4) >> 2; // the warps of a quarter take 32-token chunks in turn
-            const int ncol = n0 + quad * 32 + lane;
-            const float bv = p.bias ? load_as_f32(p.bias, p.bias_dtype, (size_t)p.col_base + ncol) : 0.0f;
-            for (int c0 = 32 * turn; c0 < p.mpad; c0 += 32 * (FT_UNPACK_WARPS / 4)) {
-                uint32_t rr[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, rr);
-                tmem_ld_wait();
+        if (ok) tc_fence_after();
+        const int quad = warp & 3, turn = (warp - 4) >> 2; // the warps of a quarter take 32-token chunks in turn
+        const int ncol = n0 + quad * 32 + lane;
+        if (p.sk == 1) {
+            if (ok) {
+                const float bv = p.bias ? load_as_f32(p.bias, p.bias_dtype, (size_t)p.col_base + ncol) : 0.0f;
+                for (int c0 = 32 * turn; c0 < p.mpad; c0 += 32 * (FT_UNPACK_WARPS / 4)) {
+                    uint32_t rr[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, rr);
+                    tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 32; c++)
-                    if (c0 + c < p.m)
-                        store_as(p.y, p.y_dtype, (size_t)(c0 + c) * p.ldy + p.col_base + ncol, __uint_as_float(rr[c]) + bv);
+                    for (int c = 0; c < 32; c++)
+                        if (c0 + c < p.m)
+                            store_as(p.y, p.y_dtype, (size_t)(c0 + c) * p.ldy + p.col_base + ncol, __uint_as_float(rr[c]) + bv);
+                }
+            }
+        } else {
+            // Split k: this CTA's partial tile goes to the scratch area; the CTA that arrives last at the tile's ticket
+            // adds the partial tiles in split order (ascending k) and stores y. No CTA waits for another; the two
+            // barriers below are among this CTA's unpack warps, which all get here whether or not a wait gave up
+            // (in that case the flag word is set and the output is not to be trusted).
+            if (ok) {
+                float *part = p.partials + (size_t)(blockIdx.x * p.sk + blockIdx.y) * p.mpad * FT_ROWS;
+                for (int c0 = 32 * turn; c0 < p.mpad; c0 += 32 * (FT_UNPACK_WARPS / 4)) {
+                    uint32_t rr[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, rr);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; c++)
+                        if (c0 + c < p.m) part[(size_t)(c0 + c) * FT_ROWS + quad * 32 + lane] = __uint_as_float(rr[c]);
+                }
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"n"(FT_UNPACK_WARPS * 32) : "memory");
+            const int et = threadIdx.x - 128; // 0 .. 511
+            const unsigned shift = (blockIdx.x & 1u) * 16u;
+            if (et == 0) tmem_slot[1] = (atomicAdd(p.tickets + (blockIdx.x >> 1), 1u << shift) >> shift) & 0xFFFFu;
+            asm volatile("bar.sync 1, %0;" ::"n"(FT_UNPACK_WARPS * 32) : "memory");
+            if (tmem_slot[1] == (uint32_t)(p.sk - 1)) {
+                __threadfence();
+                const float *tile_parts = p.partials + (size_t)blockIdx.x * p.sk * p.mpad * FT_ROWS;
+                // a thread keeps its out feature (512 threads = four tokens x 128 features per pass) and takes eight
+                // tokens per batch: all loads of a batch are issued before the first sum is stored
+                const int nn = et % FT_ROWS;
+                const float bv = p.bias ? load_as_f32(p.bias, p.bias_dtype, (size_t)p.col_base + n0 + nn) : 0.0f;
+                constexpr int TOK_STEP = FT_UNPACK_WARPS * 32 / FT_ROWS, BATCH = 8;
+                for (int tok0 = et / FT_ROWS; tok0 < p.m; tok0 += TOK_STEP * BATCH) {
+                    float sum[BATCH];
+#pragma unroll
+                    for (int b = 0; b < BATCH; b++) sum[b] = 0.0f;
+                    for (int sp = 0; sp < p.sk; sp++) { // ascending k
+#pragma unroll
+                        for (int b = 0; b < BATCH; b++) {
+                            const int tok = tok0 + b * TOK_STEP;
+                            if (tok < p.m) sum[b] += __ldcg(tile_parts + ((size_t)sp * p.mpad + tok) * FT_ROWS + nn);
+                        }
+                    }
+#pragma unroll
+                    for (int b = 0; b < BATCH; b++) {
+                        const int tok = tok0 + b * TOK_STEP;
+                        if (tok < p.m) store_as(p.y, p.y_dtype, (size_t)tok * p.ldy + p.col_base + n0 + nn, sum[b] + bv);
+                    }
+                }
+                if (et == 0) atomicAnd(p.tickets + (blockIdx.x >> 1), ~(0xFFFFu << shift)); // zero again for the next call
             }
         }
     }
@@ -434,7 +489,8 @@ bool awq_fused_supported(int m, int k, int n, int group_size, int scales_dtype, 
 
 // layout 0 = AWQ, 1 = GPTQ 4-bit (sym: no stored zero points), 2 = FP8 E4M3 (qweight = the bytes, scale_inv / s_in /
 // block_out / block_in describe the scale grid; qzeros, scales unused).
-static int fused_launch(int layout, FusedParams p, const void *x, const void *qweight, int m, int k, int n, cudaStream_t st)
+static int fused_launch(int layout, FusedParams p, const void *x, const void *qweight, int m, int k, int n, cudaStream_t st,
+                        void *scratch, size_t scratch_bytes)
 {
     const int raw_bytes = layout == 2 ? FT_ROWS * FT_BK : FT_BOX_BYTES + 384;
     p.mpad = (m + 15) / 16 * 16;
@@ -454,6 +510,22 @@ static int fused_launch(int layout, FusedParams p, const void *x, const void *qw
     if (p.raw_slots < UNIT || nk < 1) return OXQ_ERR_UNSUPPORTED; // the caller takes the slab path
     p.tmem_cols = 32;
     while (p.tmem_cols < p.mpad) p.tmem_cols *= 2;
+    // Few out-feature tiles (narrow layers: attention and down projections): split k over grid y so that about every SM has a
+    // CTA. Splits are whole rounds, at least eight stages each; at most 126 tiles (the 16-bit tickets share the workspace header
+    // with the flag word) and only while the partial tiles fit the scratch area.
+    const int tiles = n / FT_ROWS, rounds = nk / FT_ROUND;
+    p.sk = 1;
+    p.partials = reinterpret_cast<float *>(scratch);
+    p.tickets = reinterpret_cast<unsigned int *>(p.flag) + 1;
+    if (tiles <= 126 && scratch != nullptr) {
+        for (int cand = sm_count() / tiles; cand >= 2; cand--) {
+            if (rounds % cand != 0 || nk / cand < 8) continue;
+            if ((size_t)tiles * cand * p.mpad * FT_ROWS * sizeof(float) > scratch_bytes) continue;
+            p.sk = cand;
+            break;
+        }
+    }
+    if (const char *env = tuning_env("OXQ_AWQ_FUSED_SK")) p.sk = atoi(env) >= 1 && rounds % atoi(env) == 0 && tiles <= 126 ? atoi(env) : p.sk;
     const size_t smem = (size_t)p.stages * p.stage_bytes + (size_t)p.raw_slots * raw_bytes + fixed;
 
     CUtensorMap wmap, xmap;
@@ -481,16 +553,17 @@ static int fused_launch(int layout, FusedParams p, const void *x, const void *qw
         else OXQ_CUDA(cudaFuncSetAttribute(awq_fused_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (device < 64) configured[layout][device] = smem;
     }
-    if (layout == 1) awq_fused_tc_kernel<1><<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
-    else if (layout == 2) awq_fused_tc_kernel<2><<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
-    else awq_fused_tc_kernel<0><<<n / FT_ROWS, FT_THREADS, smem, st>>>(p, wmap, xmap);
+    const dim3 grid(tiles, p.sk, 1);
+    if (layout == 1) awq_fused_tc_kernel<1><<<grid, FT_THREADS, smem, st>>>(p, wmap, xmap);
+    else if (layout == 2) awq_fused_tc_kernel<2><<<grid, FT_THREADS, smem, st>>>(p, wmap, xmap);
+    else awq_fused_tc_kernel<0><<<grid, FT_THREADS, smem, st>>>(p, wmap, xmap);
     OXQ_CUDA(cudaGetLastError());
     return OXQ_OK;
 }
 
 int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype, const void *bias,
                      int bias_dtype, void *y, int y_dtype, int m, int k, int n, int group_size, int col_base, int ldy,
-                     int *flag, cudaStream_t st, int gptq, int sym)
+                     int *flag, cudaStream_t st, int gptq, int sym, void *scratch, size_t scratch_bytes)
 {
     FusedParams p = {};
     p.qzeros = qzeros; p.scales = scales; p.scales_dtype = scales_dtype; p.bias = bias; p.y = y;
@@ -501,7 +574,7 @@ int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qze
     p.gshift = 0;
     while ((FT_BK << p.gshift) < group_size) p.gshift += 1;
     p.block_in = FT_BK; p.block_out = FT_ROWS; p.s_in = 1;
-    return fused_launch(gptq ? 1 : 0, p, x, qweight, m, k, n, st);
+    return fused_launch(gptq ? 1 : 0, p, x, qweight, m, k, n, st, scratch, scratch_bytes);
 }
 
 bool fp8_fused_supported(int m, int k, int n, int block_out, int block_in, const void *x, const void *weight, const void *scale_inv)
@@ -513,14 +586,15 @@ bool fp8_fused_supported(int m, int k, int n, int block_out, int block_in, const
 }
 
 int fp8_fused_matmul(const void *x, const uint8_t *weight, const float *scale_inv, int s_in, int block_out, int block_in,
-                     const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, int *flag, cudaStream_t st)
+                     const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, int *flag, cudaStream_t st,
+                     void *scratch, size_t scratch_bytes)
 {
     FusedParams p = {};
     p.bias = bias; p.y = y; p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
     p.m = m; p.k = k; p.n = n; p.group_size = FT_BK; p.packed_out = n / 8;
     p.col_base = 0; p.ldy = n; p.flag = flag;
     p.scale_inv = scale_inv; p.s_in = s_in; p.block_out = block_out; p.block_in = block_in;
-    return fused_launch(2, p, x, weight, m, k, n, st);
+    return fused_launch(2, p, x, weight, m, k, n, st, scratch, scratch_bytes);
 }
 
 } // namespace oxq

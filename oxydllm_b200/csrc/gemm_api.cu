@@ -26,10 +26,11 @@ bool awq_fused_supported(int m, int k, int n, int group_size, int scales_dtype, 
                          const void *scales);
 bool fp8_fused_supported(int m, int k, int n, int block_out, int block_in, const void *x, const void *weight, const void *scale_inv);
 int fp8_fused_matmul(const void *x, const uint8_t *weight, const float *scale_inv, int s_in, int block_out, int block_in,
-                     const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, int *flag, cudaStream_t st);
+                     const void *bias, int bias_dtype, void *y, int y_dtype, int m, int k, int n, int *flag, cudaStream_t st,
+                     void *scratch, size_t scratch_bytes);
 int awq_fused_matmul(const void *x, const uint32_t *qweight, const uint32_t *qzeros, const void *scales, int scales_dtype, const void *bias,
                      int bias_dtype, void *y, int y_dtype, int m, int k, int n, int group_size, int col_base, int ldy,
-                     int *flag, cudaStream_t st, int gptq, int sym);
+                     int *flag, cudaStream_t st, int gptq, int sym, void *scratch, size_t scratch_bytes);
 
 constexpr size_t WS_HEADER = 256;                // flag word + padding, keeps the slab 256-byte aligned
 constexpr size_t SLAB_LIMIT_BYTES = 128u << 20;  // dequantized rows held at once (whole weight if it fits)
@@ -62,6 +63,7 @@ struct GemmCommon {
     int bias_dtype, y_dtype, m, k, n;
     int *flag;
     __nv_bfloat16 *slab;
+    size_t slab_bytes = 0; // what the workspace holds behind the header
     int rows;
     cudaStream_t st;
     // tensor-parallel placement (oxq_awq_gemm_tp): this call's weight is columns [col_base, col_base + n) of an
@@ -84,6 +86,7 @@ static int prepare(const char *who, GemmCommon &c, const void *x, int x_dtype, c
     c.x = x; c.bias = bias; c.y = y; c.bias_dtype = bias_dtype; c.y_dtype = y_dtype; c.m = m; c.k = k; c.n = n;
     c.flag = reinterpret_cast<int *>(workspace);
     c.slab = reinterpret_cast<__nv_bfloat16 *>(reinterpret_cast<unsigned char *>(workspace) + WS_HEADER);
+    c.slab_bytes = workspace_bytes - WS_HEADER;
     c.rows = slab_rows_for_m(slab_rows(n, k), n, m);
     c.st = (cudaStream_t)stream;
     return OXQ_OK; // the flag word is sticky: only oxq_gemm_check / oxq_gemm_workspace_init clear it
@@ -121,7 +124,7 @@ OXQ_EXPORT int oxq_gemm_check(const void *workspace, void *stream)
     OXQ_CUDA(cudaMemcpyAsync(&flag, workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     OXQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (flag != 0) { // report once, then the workspace is clean again
-        OXQ_CUDA(cudaMemsetAsync(const_cast<void *>(workspace), 0, sizeof(int), (cudaStream_t)stream));
+        OXQ_CUDA(cudaMemsetAsync(const_cast<void *>(workspace), 0, WS_HEADER, (cudaStream_t)stream)); // flag and split-k tickets
         OXQ_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     }
     OXQ_REQUIRE(flag == 0, OXQ_ERR_DEVICE_FLAG,
@@ -156,7 +159,7 @@ OXQ_EXPORT int oxq_awq_gemm(const void *x, int x_dtype, const uint32_t *qweight,
     if (awq_fused_supported(m, k, n, group_size, scales_dtype, x, qweight, scales))
     {
         rc = awq_fused_matmul(x, qweight, qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n, group_size, 0, n, c.flag,
-                              c.st, 0, 0);
+                              c.st, 0, 0, c.slab, c.slab_bytes);
         if (rc != OXQ_ERR_UNSUPPORTED) return rc;
     }
     return run_slabs(c, [&](int n_off, int cnt) {
@@ -246,7 +249,7 @@ OXQ_EXPORT int oxq_gptq_gemm(const void *x, int x_dtype, const uint32_t *qweight
         awq_fused_supported(m, k, n, group_size, scales_dtype, x, qweight, scales))
     {
         rc = awq_fused_matmul(x, qweight, use_sym ? nullptr : qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n,
-                              group_size, 0, n, c.flag, c.st, 1, use_sym);
+                              group_size, 0, n, c.flag, c.st, 1, use_sym, c.slab, c.slab_bytes);
         if (rc != OXQ_ERR_UNSUPPORTED) return rc;
     }
     return run_slabs(c, [&](int n_off, int cnt) {
@@ -311,7 +314,8 @@ OXQ_EXPORT int oxq_fp8_gemm(const void *x, int x_dtype, const uint8_t *weight, c
     if (rc) return rc;
     // Up to 256 tokens: widen the bytes inside the tensor-core kernel, no dense copy of the weight.
     if (fp8_fused_supported(m, k, n, bo, bi, x, weight, scale_inv)) {
-        rc = fp8_fused_matmul(x, weight, scale_inv, scale_inv ? s_in : 1, bo, bi, bias, bias_dtype, y, y_dtype, m, k, n, c.flag, c.st);
+        rc = fp8_fused_matmul(x, weight, scale_inv, scale_inv ? s_in : 1, bo, bi, bias, bias_dtype, y, y_dtype, m, k, n, c.flag, c.st,
+                              c.slab, c.slab_bytes);
         if (rc != OXQ_ERR_UNSUPPORTED) return rc;
     }
     return run_slabs(c, [&](int n_off, int cnt) {

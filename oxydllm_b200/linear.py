@@ -28,6 +28,7 @@ PACKED_SIMT_GEMV_MAX_M = 8
 # group size a power of two >= 64, 16-bit scales) leave the split-k GEMV at this batch: measured on a 4096 x 14336 layer the GEMV
 # takes 24 us at 16 tokens and 47 us at 32, the fused kernel 28 to 31 us for any batch up to 128.
 AWQ_FUSED_MIN_M = 17
+AWQ_FUSED_SPLIT_K_TILES = 74  # at most this many 128-row tiles: the fused kernel runs two or more k splits per tile
 # GPTQ 4-bit layers of such shapes: the GEMV takes 25 / 28 / 35 / 48 us at 1 / 2 / 4 / 8 tokens on the same layer, the fused
 # kernel 30 us for any batch up to 64.
 GPTQ_FUSED_MIN_M = 3
@@ -274,6 +275,8 @@ class PackedQuantLinear:
         fused = (self.bits == 4 and self.out_features % 128 == 0 and self.in_features % 128 == 0 and self.group_size % 64 == 0
                  and self.group_size & (self.group_size - 1) == 0 and self.scales.dtype in (torch.float16, torch.bfloat16))
         if self.pack_dim == "out" and self.bits == 4:
+            if fused and self.out_features // 128 <= AWQ_FUSED_SPLIT_K_TILES:
+                return 8  # narrow layer: the fused kernel splits k over the SMs (4096 x 4096: 14 us at 16 tokens, GEMV 23 us)
             return AWQ_FUSED_MIN_M - 1 if fused else GEMV_MAX_M
         if fused:
             return GPTQ_FUSED_MIN_M - 1

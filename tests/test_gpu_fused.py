@@ -46,7 +46,7 @@ def close(y, ref):
 @pytest.mark.parametrize("k,n,g", [(256, 128, 64), (512, 384, 128), (1024, 256, 256)])
 def test_fused_weight_tile_bit_exact_with_one_hot_rows(cuda, k, n, g, scale_dtype):
     lin, w, _ = layer(k, n, g, seed=k + n, scale_dtype=scale_dtype)
-    assert lin.gemv_max_m() == L.AWQ_FUSED_MIN_M - 1  # these shapes take the fused kernel above 16 tokens
+    assert lin.gemv_max_m() == 8  # narrow layers of these shapes take the fused kernel (with k splits) from 9 tokens on
     want = oracle.to_bf16_bits(w)  # [n, k]
     for k0 in range(0, k, 256):
         m = min(256, k - k0)
@@ -168,3 +168,28 @@ def test_fp8_fused_matmul_matches_oracle(cuda, m, k, n, bias):
     y = lin.forward(dev(x, torch.bfloat16))
     close(y, oracle.linear(x, synth.bf16_round(oracle.fp8_dequant(w8, sinv)), b))
     gemm.check(gemm.workspace(n, k, "cuda"))
+
+
+# ------------------------------------------------------------------ narrow layers: k split over grid y, ticketed reduction
+@pytest.mark.parametrize("m,k,n,g,bias", [(9, 4096, 4096, 128, True), (64, 14336, 4096, 128, False), (17, 1024, 128, 128, False),
+                                          (200, 2048, 1024, 64, True), (256, 4096, 1024, 128, False), (40, 1024, 8064, 128, False)])
+def test_fused_split_k_matches_oracle_and_is_reproducible(cuda, m, k, n, g, bias):
+    lin, w, b = layer(k, n, g, seed=m + n, bias=bias)
+    x = synth.activations(m, k, seed=m)
+    xd = dev(x, torch.bfloat16)
+    ys = [lin.forward(xd) for _ in range(3)]
+    close(ys[0], oracle.linear(x, synth.bf16_round(w), b))
+    assert torch.equal(ys[0], ys[1]) and torch.equal(ys[1], ys[2])  # partial tiles are added in split order
+    ws = gemm.workspace(n, k, "cuda")
+    gemm.check(ws)
+    assert not ws[:256].view(torch.int32).any()  # the tickets in the workspace header are back at zero
+
+
+def test_fused_split_k_other_layouts(cuda):
+    w8, sinv = synth.fp8_layer(1024, 4096, seed=5)
+    lin = L.Fp8Linear(dev(w8), dev(sinv))
+    x = synth.activations(32, 4096, seed=6)
+    close(lin.forward(dev(x, torch.bfloat16)), oracle.linear(x, synth.bf16_round(oracle.fp8_dequant(w8, sinv))))
+    glin, gw = gptq_layer(4096, 1024, 128, seed=8)
+    close(glin.forward(dev(x, torch.bfloat16)), oracle.linear(x, synth.bf16_round(gw)))
+    gemm.check(gemm.workspace(1024, 4096, "cuda"))
