@@ -487,6 +487,26 @@ def run_extras(args, world, rank, c1_layer):
                     del ps, y_ps
                 except Exception as e:
                     sharded[f"tp{world}_c2_awq_gemm_n{n}_peer_store"] = {"error": str(e)[:200]}
+                if n == 14336:  # the same split at a decode batch: the fused unpack + tcgen05 kernel on the shard, then the peer stores
+                    try:
+                        for md in (32, 256):
+                            xdec = x[:md].contiguous()
+                            y1 = torch.empty((md, n), dtype=torch.bfloat16, device="cuda")
+                            for _ in range(3):
+                                gemm.awq_matmul(lin_full, xdec, y1)
+                            ms1 = _timed_ms(torch, dist, world, lambda: gemm.awq_matmul(lin_full, xdec, y1), 20)
+                            psd = parallel.PeerStoreColumnLinear(shard, n, m_max=md)
+                            for _ in range(3):
+                                y_pd = psd.forward(xdec)
+                            msd = _timed_ms(torch, dist, world, lambda: psd.forward(xdec), 20)
+                            refd = y1.float()
+                            okd = bool(((y_pd.float() - refd).abs() <= 2e-2 * refd.abs().amax(dim=1, keepdim=True) + 1e-6).all().item())
+                            sharded[f"tp{world}_c1_awq_m{md}_peer_store"] = {
+                                "ms": round(msd, 4), "ms_1gpu": round(ms1, 4), "speedup_vs_1gpu": round(ms1 / msd, 3), "parity_ok": okd,
+                                "stored_to_peers_bytes_per_rank": int(md * (b_ - a) * 2 * (world - 1))}
+                            del psd, y_pd
+                    except Exception as e:
+                        sharded[f"tp{world}_c1_awq_decode_peer_store"] = {"error": str(e)[:200]}
                 del tp, shard
             del lin_c, lin_big_c, big_c, common, y_c
         del lin_big, y_big, big

@@ -206,9 +206,14 @@ OXQ_EXPORT int oxq_awq_gemm_tp(const void *x, int x_dtype, const uint32_t *qweig
     int rc = prepare("oxq_awq_gemm_tp", c, x, x_dtype, bias, bias_dtype, y, y_dtype, m, k, n_local, workspace, workspace_bytes, stream);
     if (rc) return rc;
     c.col_base = col_base; c.ldy = n_full;
-    rc = run_slabs(c, [&](int n_off, int cnt) {
-        return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n_local, group_size, n_off, cnt, c.st);
-    });
+    rc = OXQ_ERR_UNSUPPORTED;
+    if (awq_fused_supported(m, k, n_local, group_size, scales_dtype, x, qweight, scales)) // decode-sized batches: no slab
+        rc = awq_fused_matmul(x, qweight, qzeros, scales, scales_dtype, bias, bias_dtype, y, y_dtype, m, k, n_local, group_size,
+                              col_base, n_full, c.flag, c.st, 0, 0, c.slab, c.slab_bytes);
+    if (rc == OXQ_ERR_UNSUPPORTED)
+        rc = run_slabs(c, [&](int n_off, int cnt) {
+            return awq_dequant_rows_bf16(qweight, qzeros, scales, scales_dtype, c.slab, k, n_local, group_size, n_off, cnt, c.st);
+        });
     if (rc || n_peers == 0) return rc;
     // The finished column block goes to the same place in every peer's output: long contiguous runs (a row of the
     // block) in 16-byte stores. Stores from the GEMM's epilogue (64-byte pieces per thread) were tried first and

@@ -41,8 +41,8 @@ def main():
         assert err <= tol, f"TP m={m}: {err} > {tol}"
 
     # --- the same split with direct placement: each rank's GEMM stores its tile into every rank's output
-    ps = parallel.PeerStoreColumnLinear(shard, n, m_max=256)
-    for m in (200, 64, 200):
+    ps = parallel.PeerStoreColumnLinear(shard, n, m_max=320)
+    for m in (200, 64, 300, 200):  # fused kernel on the shard up to 256 rows, dequantized slab + GEMM above
         x = dev(synth.activations(m, k, seed=m + 7), torch.bfloat16)
         y = ps.forward(x)
         ref = full.forward(x)
