@@ -396,6 +396,20 @@ def run_extras(args, world, rank, c1_layer):
             us = graph_us(lambda: [lin.forward(x) for lin in glins], len(glins), reps=10)
             res[f"gptq4_operator_m{m}"] = {"us_per_call": round(us, 2), "gbs": round(algo_bytes(m) / us / 1e3, 1),
                                            "frac_of_hbm_peak": round(algo_bytes(m) / us / 1e3 / hbm, 4)}
+        # narrow layers of the same model family (attention projection 4096 x 4096, down projection 14336 -> 4096): the fused
+        # kernel splits k over the SMs
+        for (kk, nn, tag) in ((4096, 4096, "attn_4096x4096"), (14336, 4096, "down_4096x14336")):
+            nl = []
+            for i in range(6):
+                nqw, nqz, nsc = synth.awq_layer(kk, nn, G, seed=700 + i)
+                nl.append(L.PackedQuantLinear(L.QuantWeight.new_awq(4, dev(nqw.view(np.int32)), dev(nqz.view(np.int32)), dev(nsc))))
+            for m in (1, 32, 128):
+                x = dev(synth.activations(m, kk, seed=m), torch.bfloat16)
+                us = graph_us(lambda: [lin.forward(x) for lin in nl], len(nl), reps=10)
+                nb = kk * nn // 2 + (kk // G) * (nn // 2) + (kk // G) * nn * 2 + m * (2 * kk + 2 * nn)
+                res[f"{tag}_operator_m{m}"] = {"us_per_call": round(us, 2), "gbs": round(nb / us / 1e3, 1),
+                                               "frac_of_hbm_peak": round(nb / us / 1e3 / hbm, 4)}
+            del nl
         out["c1_shape_other_batches_and_layouts"] = res
         del lins, glins
     except _NotSelected:

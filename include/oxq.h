@@ -192,6 +192,12 @@ size_t oxq_gemm_workspace_bytes(int n, int k);
  * stays usable. */
 int oxq_selftest_wait_expiry(void *workspace, int code, void *stream);
 
+/* The same through the dense tensor-core GEMM itself (one-CTA kernel for m <= 128, two-CTA kernel above, m <= 256): its
+ * TMA producer issues no loads, the MMA issuer's wait for tile data runs out after the regular 2 s limit, every role
+ * falls through, tensor memory is freed and the kernel ends with code 2 in the flag word. Operands and output are
+ * scratch inside `workspace` (256-byte aligned, at least 1 MiB). */
+int oxq_selftest_gemm_wait_expiry(void *workspace, size_t workspace_bytes, int m, void *stream);
+
 /* Zeroes the 256-byte header (flag word) of a fresh workspace on `stream`. */
 int oxq_gemm_workspace_init(void *workspace, void *stream);
 

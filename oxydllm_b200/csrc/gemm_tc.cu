@@ -43,6 +43,7 @@ struct GemmParams {
     int m, n, k;      // n = rows of W in this call (a slab); y columns [n_off, n_off + n)
     int n_off, ldy;   // ldy = full out_features
     int tiles_m, tiles_n, bn; // tile grid of this call; bn = tile width (multiple of 32, <= 256)
+    int test_skip_loads; // self-test only: the TMA producer issues nothing, so the waits of the other roles run out
     int epi; // 0: y = acc (+ bias). 1 / 2: W rows interleave (gate j, up j); y[:, j] = SiLU / GeLU-tanh(gate) * up, bf16 [m, n/2]
 };
 
@@ -163,7 +164,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (elect_one()) {
             uint32_t it = 0; // k blocks issued so far by this CTA, across tiles
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = blockIdx.x; tile < num_tiles && ok && !p.test_skip_loads; tile += gridDim.x) {
                 const int m0 = (tile % p.tiles_m) * TC_BM, n0 = (tile / p.tiles_m) * p.bn;
                 for (int kb = 0; kb < k_iters; kb++, it++) {
                     const int s = it % TC_STAGES;
@@ -338,7 +339,7 @@ gemm_bf16_tn_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (elect_one()) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+            for (int tile = cluster_id; tile < num_tiles && ok && !p.test_skip_loads; tile += num_clusters) {
                 const int m0 = ((tile % pair_m) * 2 + (int)rank) * TC_BM;                  // this CTA's 128 rows
                 const int n0 = (tile / pair_m) * p.bn + (int)rank * (p.bn / 2);           // this CTA's half of the W rows
                 for (int kb = 0; kb < k_iters; kb++, it++) {
@@ -666,6 +667,8 @@ int gemm_pick_bn_2cta(int m, int n)
 }
 
 // y[:, n_off : n_off + n] = x[m, k] . w[n, k]^T (+ bias) with x, w bf16 row-major.
+static thread_local int g_selftest_skip_loads = 0; // set only inside oxq_selftest_gemm_wait_expiry
+
 int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype, void *y, int y_dtype, int m, int n,
                  int k, int n_off, int ldy, int *flag, cudaStream_t stream, int epi)
 {
@@ -690,6 +693,7 @@ int gemm_bf16_tn(const void *x, const void *w, const void *bias, int bias_dtype,
         if (device < 64) configured[device] = true;
     }
     GemmParams p;
+    p.test_skip_loads = g_selftest_skip_loads;
     p.bias = bias; p.y = y; p.flag = flag; p.bias_dtype = bias_dtype; p.y_dtype = y_dtype;
     p.m = m; p.n = n; p.k = k; p.n_off = n_off; p.ldy = ldy; p.epi = epi;
     p.tiles_m = ceil_div(m, TC_BM); p.tiles_n = ceil_div(n, bn); p.bn = bn;
@@ -786,4 +790,23 @@ OXQ_EXPORT int oxq_selftest_wait_expiry(void *workspace, int code, void *stream)
     oxq::wait_expiry_selftest_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(reinterpret_cast<int *>(workspace), code);
     OXQ_CUDA(cudaGetLastError());
     return OXQ_OK;
+}
+
+// The dense tensor-core GEMM (one-CTA kernel for m <= 128, two-CTA kernel above) with a producer that issues no
+// loads: the MMA issuer's wait for the first tile data runs out (2 s), the roles fall through, tensor memory is freed
+// and the kernel ends with code 2 in the flag word. Operands and output are scratch inside `workspace` (>= 1 MiB).
+OXQ_EXPORT int oxq_selftest_gemm_wait_expiry(void *workspace, size_t workspace_bytes, int m, void *stream)
+{
+    oxq::clear_error();
+    OXQ_REQUIRE(workspace && workspace_bytes >= (1u << 20) && oxq::aligned(workspace, 256), OXQ_ERR_WORKSPACE,
+                "oxq_selftest_gemm_wait_expiry: 256-byte aligned workspace of at least 1 MiB needed");
+    OXQ_REQUIRE(m >= 1 && m <= 256, OXQ_ERR_BAD_SHAPE, "oxq_selftest_gemm_wait_expiry: m in 1..256");
+    unsigned char *b = reinterpret_cast<unsigned char *>(workspace);
+    const int k = 64, n = 256;
+    void *x = b + 4096, *w = b + 4096 + 256 * 64 * 2, *y = b + 4096 + 2 * 256 * 64 * 2; // x [256, 64], w [256, 64], y [256, 256] bf16
+    oxq::g_selftest_skip_loads = 1;
+    const int rc = oxq::gemm_bf16_tn(x, w, nullptr, 0, y, OXQ_BF16, m, n, k, 0, n, reinterpret_cast<int *>(workspace),
+                                     (cudaStream_t)stream, 0);
+    oxq::g_selftest_skip_loads = 0;
+    return rc;
 }

@@ -141,3 +141,22 @@ def test_bounded_wait_expiry_is_reported_and_the_workspace_stays_usable(cuda):
     y = lin.forward(dev(x, torch.bfloat16))
     check(y, oracle.linear(x, synth.bf16_round(oracle.awq_dequant(qw, qz, sc))), "after an expired wait")
     gemm.check(ws)
+
+
+@pytest.mark.parametrize("m", [100, 200])  # one-CTA kernel, two-CTA kernel
+def test_gemm_kernel_survives_a_producer_that_never_loads(cuda, m):
+    # The kernel's own roles: with no tile data ever arriving the MMA issuer gives up after the 2 s limit, everybody
+    # falls through, tensor memory is freed, the kernel returns, the check reports code 2 and the workspace still works.
+    from oxydllm_b200 import _lib
+    k, n = 1024, 1024
+    ws = gemm.workspace(n, k, "cuda")
+    gemm.check(ws)
+    _lib.call("oxq_selftest_gemm_wait_expiry", ctypes.c_void_p(ws.data_ptr()), ws.numel(), m, None)
+    with pytest.raises(_lib.OxqError, match=r"bounded wait [23]"):  # the issuer (2) or an epilogue warp (3) gives up first
+        gemm.check(ws)
+    gemm.check(ws)
+    qw, qz, sc = synth.awq_layer(k, n, 128, seed=9)
+    lin = L.PackedQuantLinear(L.QuantWeight.new_awq(4, words(qw), words(qz), dev(sc.astype(np.float32))))  # f32 scales: slab path
+    x = synth.activations(300, k, seed=10)
+    y = lin.forward(dev(x, torch.bfloat16))
+    check(y, oracle.linear(x, synth.bf16_round(oracle.awq_dequant(qw, qz, sc.astype(np.float32)))), "after an aborted GEMM")
