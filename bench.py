@@ -410,6 +410,18 @@ def run_extras(args, world, rank, c1_layer):
                 res[f"{tag}_operator_m{m}"] = {"us_per_call": round(us, 2), "gbs": round(nb / us / 1e3, 1),
                                                "frac_of_hbm_peak": round(nb / us / 1e3 / hbm, 4)}
             del nl
+        # gated FFN projection of the same family at decode batches: fused [gate | up] weight 4096 -> 2 x 14336, SiLU
+        fqw, fqz, fsc = synth.awq_layer(K, 2 * N, G, seed=770)
+        fq = dev(fqw.view(np.int32))
+        fl = [L.GatedFfnProjection(L.PackedQuantLinear(L.QuantWeight.new_awq(4, torch.roll(fq, 64 * i, 0), dev(fqz.view(np.int32)),
+                                                                              dev(fsc))), "silu") for i in range(3)]
+        for m in (1, 32, 128):
+            x = dev(synth.activations(m, K, seed=m), torch.bfloat16)
+            us = graph_us(lambda: [f.forward(x) for f in fl], len(fl), reps=10)
+            nb = K * N + (K // G) * N + (K // G) * 2 * N * 2 + m * (2 * K + 2 * N)
+            res[f"ffn_gate_up_silu_i14336_m{m}"] = {"us_per_call": round(us, 2), "gbs": round(nb / us / 1e3, 1),
+                                                    "frac_of_hbm_peak": round(nb / us / 1e3 / hbm, 4)}
+        del fl, fq
         out["c1_shape_other_batches_and_layouts"] = res
         del lins, glins
     except _NotSelected:

@@ -389,15 +389,29 @@ OXQ_EXPORT int oxq_awq_ffn_gate_up(const void *x, int x_dtype, const uint32_t *q
     GemmCommon c;
     int rc = prepare("oxq_awq_ffn_gate_up", c, x, x_dtype, nullptr, 0, y, OXQ_BF16, m, k, n, workspace, workspace_bytes, stream);
     if (rc) return rc;
-    if (m <= 32) {
-        // Decode: the GEMV into a scratch row block [m, 2 * inter] (the workspace slab), then the activation.
-        rc = oxq_awq_gemv(x, x_dtype, qweight, qzeros, scales, scales_dtype, nullptr, 0, c.slab, OXQ_BF16, m, k, n, group_size,
-                          stream);
-        if (rc) return rc;
+    const size_t gu_bytes = ((size_t)m * n * 2 + 255) / 256 * 256; // scratch row block [m, 2 * inter] at the head of the slab
+    auto activate = [&]() -> int {
         const int blocks = (int)(((size_t)m * inter + 255) / 256);
         gated_act_rows_kernel<<<blocks < 2368 ? blocks : 2368, 256, 0, c.st>>>(c.slab, (__nv_bfloat16 *)y, m, inter, activation);
         OXQ_LAUNCH_CHECK("gated_act_rows_kernel");
         return OXQ_OK;
+    };
+    if (m > 16 && gu_bytes <= c.slab_bytes && awq_fused_supported(m, k, n, group_size, scales_dtype, x, qweight, scales)) {
+        // Decode batches of 17 .. 256 tokens: the kernel that unpacks inside the tensor-core loop writes the
+        // row block (no dense copy of the weight); what the slab holds behind the block is its scratch.
+        rc = awq_fused_matmul(x, qweight, qzeros, scales, scales_dtype, nullptr, 0, c.slab, OXQ_BF16, m, k, n, group_size, 0, n,
+                              c.flag, c.st, 0, 0, (unsigned char *)c.slab + gu_bytes, c.slab_bytes - gu_bytes);
+        if (rc == OXQ_OK) return activate();
+        if (rc != OXQ_ERR_UNSUPPORTED) return rc;
+    }
+    if (m <= 32) {
+        // Decode: the GEMV into the scratch row block, then the activation.
+        OXQ_REQUIRE(gu_bytes <= c.slab_bytes, OXQ_ERR_WORKSPACE, "oxq_awq_ffn_gate_up: workspace slab of %zu bytes, %zu needed",
+                    c.slab_bytes, gu_bytes);
+        rc = oxq_awq_gemv(x, x_dtype, qweight, qzeros, scales, scales_dtype, nullptr, 0, c.slab, OXQ_BF16, m, k, n, group_size,
+                          stream);
+        if (rc) return rc;
+        return activate();
     }
     // Prefill: gate row j and up row j of the dequantized weight are written next to each other, so that
     // every accumulator tile holds (gate, up) pairs and the activation runs in the GEMM's epilogue.

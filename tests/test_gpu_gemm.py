@@ -102,17 +102,19 @@ def test_workspace_too_small_is_rejected(cuda):
 
 @pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
 @pytest.mark.parametrize("m,k,inter,g", [(1, 256, 64, 64), (7, 512, 200, 128), (33, 256, 64, 32), (300, 1024, 1000, 128),
-                                         (2048, 512, 1024, 128), (64, 4096, 9216, 128)])  # the last needs two slabs
+                                         (2048, 512, 1024, 128), (64, 4096, 9216, 128),  # the last needs two slabs
+                                         (24, 512, 256, 128), (200, 1024, 1024, 64), (256, 2048, 9216, 128)])
 def test_gated_ffn_gate_up_matches_oracle(cuda, activation, m, k, inter, g):
-    """act(gate) * up on the fused [gate | up] AWQ weight: GEMV route for m <= 32, fused GEMM epilogue above."""
+    """act(gate) * up on the fused [gate | up] AWQ weight: GEMV route for m <= 16, the kernel that unpacks inside the
+    tensor-core loop for 17 .. 256 tokens on the shapes it takes (GEMV up to 32 elsewhere), GEMM epilogue above."""
     from oxydllm_b200 import gemm
     qw, qz, sc = synth.awq_layer(k, 2 * inter, g, seed=m + inter)
     sc = (sc.astype(np.float32) * 8.0).astype(sc.dtype)  # larger pre-activations: both tails of the activations
     lin = L.PackedQuantLinear(L.QuantWeight.new_awq(4, words(qw), words(qz), dev(sc)))
     x = synth.activations(m, k, seed=3)
     w = oracle.awq_dequant(qw, qz, sc)
-    if m > 32:
-        w = oracle.round_bf16(w)  # the tensor-core path multiplies the bf16-rounded dense weight
+    if m > 32 or (m > 16 and g >= 64 and inter % 64 == 0 and k % 128 == 0):
+        w = oracle.round_bf16(w)  # the tensor-core paths multiplies the bf16-rounded dense weight
     ref = oracle.gated_ffn(x, w, activation)
     y = L.GatedFfnProjection(lin, activation).forward(dev(x, torch.bfloat16))
     gemm.check(gemm.workspace(1, 8, "cuda"))
