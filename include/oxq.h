@@ -93,8 +93,9 @@ int oxq_awq_gemv_check(void *stream);
  * up_proj, ffn.rs:235-254): y[m, inter] = act(x . W_gate^T) * (x . W_up^T), act = 1 SiLU, 2 GeLU-tanh
  * (FeedForward::forward, ffn.rs:385-470; gated_silu_fused / gated_gelu_tanh_fused, metal_ops.rs:1243-1277).
  * x, y bf16. qweight u32 [k, 2*inter/8], qzeros u32 [k/g, 2*inter/8], scales [k/g, 2*inter].
- * m <= 32 runs the GEMV and a small activation kernel; larger m dequantizes the weight with gate row j
- * and up row j side by side and applies the activation in the tensor-core GEMM's epilogue (no
+ * m <= 16 runs the GEMV and a small activation kernel; 17 .. 256 tokens run the kernel that unpacks inside
+ * the tensor-core loop (on the shapes oxq_awq_gemm takes it for; the GEMV up to 32 tokens elsewhere) and the
+ * same activation kernel; larger m dequantizes the weight with gate row j and up row j side by side and applies the activation in the tensor-core GEMM's epilogue (no
  * [m, 2*inter] round trip). Workspace as for oxq_awq_gemm with n = 2*inter; oxq_gemm_check applies. */
 int oxq_awq_ffn_gate_up(const void *x, int x_dtype, const uint32_t *qweight, const uint32_t *qzeros, const void *scales,
                         int scales_dtype, int activation, void *y, int m, int k, int inter, int group_size,
