@@ -14,6 +14,12 @@ int gemm_grouped(const void *a, int a_rows, const void *w, int slab_experts, int
                  const int4 *entries, const int *grp_beg, int group, const void *bias, int bias_dtype, void *out,
                  int ldo, int epi, float limit, int *flag, cudaStream_t stream);
 
+int moe_fused_block_rows();
+bool moe_fused_supported(int n, int k, const void *blocks, const void *scales, const void *a, const void *out, int ldo);
+int moe_fused_grouped(const void *a, int a_rows, const uint8_t *blocks, const uint8_t *scales, int experts, int n, int k,
+                      const int4 *entries, const int *n_blocks, const void *bias, int bias_dtype, void *out, int ldo, int epi,
+                      float limit, int *flag, cudaStream_t st);
+
 bool mxfp4_gemv_batched_supported(int k, const void *blocks);
 int mxfp4_gemv_batched(const void *x, int x_div, const uint8_t *blocks, const uint8_t *scales, const void *bias,
                        int bias_dtype, const int *pair_expert, int pairs, int e_lo, int e_hi, void *y, int y_dtype, int k,
@@ -124,6 +130,27 @@ __global__ void moe_plan_kernel(const int *__restrict__ counts, int n_exp, int e
     }
     offsets[n_exp] = off;
     grp_beg[g] = mt;
+}
+
+// The same offsets; token blocks for the kernel that unpacks MXFP4 inside the tensor-core loop: every expert's rows cut into
+// the fewest blocks of at most max_rows rows, of equal size rounded up to 16. n_blocks[0] = how many.
+__global__ void moe_plan_blocks_kernel(const int *__restrict__ counts, int n_exp, int e_lo, int max_rows, int *__restrict__ offsets,
+                                       int4 *__restrict__ entries, int *__restrict__ n_blocks)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int off = 0, nb = 0;
+    for (int i = 0; i < n_exp; i++) {
+        offsets[i] = off;
+        const int c = counts[i];
+        if (c > 0) {
+            const int parts = (c + max_rows - 1) / max_rows;
+            const int size = ((c + parts - 1) / parts + 15) / 16 * 16;
+            for (int r = 0; r < c; r += size) entries[nb++] = make_int4(off + r, min(size, c - r), e_lo + i, 0);
+        }
+        off += c;
+    }
+    offsets[n_exp] = off;
+    n_blocks[0] = nb;
 }
 
 // Stable partition: position of pair i among the pairs of its expert, in pair (= token) order.
@@ -351,13 +378,30 @@ static int moe_forward_impl(const void *x, int x_dtype, const float *router_logi
         OXQ_LAUNCH_CHECK("moe_combine_kernel");
         return OXQ_OK;
     }
+    const int a_rows = pairs + 128;
+    // Both projections through the kernel that unpacks the MXFP4 blocks inside the tensor-core loop, where it takes the shapes:
+    // no dequantized slab, one launch per projection over all experts.
+    const bool fused = moe_fused_supported(2 * inter, hidden, gu_blocks, gu_scales, xs, h, inter) &&
+                       moe_fused_supported(hidden, inter, dn_blocks, dn_scales, h, xs, hidden);
     moe_count_kernel<<<n_exp, 256, 0, st>>>(top_idx, pairs, expert_lo, counts);
-    moe_plan_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, L.group_experts, offsets, entries, grp_beg);
+    if (fused) moe_plan_blocks_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, moe_fused_block_rows(), offsets, entries, grp_beg);
+    else moe_plan_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, L.group_experts, offsets, entries, grp_beg);
     moe_scatter_kernel<<<n_exp, 1024, 0, st>>>(top_idx, pairs, expert_lo, offsets, perm, inv);
     moe_gather_kernel<<<sm_count() * 8, 256, 0, st>>>((const __nv_bfloat16 *)x, perm, offsets + n_exp, top_k, hidden, xs);
     OXQ_LAUNCH_CHECK("moe routing kernels");
 
-    const int a_rows = pairs + 128;
+    if (fused) {
+        int rc = moe_fused_grouped(xs, a_rows, gu_blocks, gu_scales, num_experts, 2 * inter, hidden, entries, grp_beg, gu_bias,
+                                   bias_dtype, h, inter, 1, limit, flag, st);
+        if (rc) return rc;
+        rc = moe_fused_grouped(h, a_rows, dn_blocks, dn_scales, num_experts, hidden, inter, entries, grp_beg, dn_bias, bias_dtype,
+                               xs, hidden, 0, limit, flag, st);
+        if (rc) return rc;
+        moe_combine_kernel<<<sm_count() * 8, 256, 0, st>>>(xs, top_idx, top_w, inv, tokens, top_k, hidden, expert_lo, expert_hi,
+                                                         out, out_dtype);
+        OXQ_LAUNCH_CHECK("moe_combine_kernel");
+        return OXQ_OK;
+    }
     const size_t gu_rows = (size_t)2 * inter, nbh = hidden / 32, nbi = inter / 32;
     for (int g = 0; g < L.n_groups; g++) { // gate_up + SwiGLU: h = act(xs . W_gu^T + b_gu)
         const int e0 = expert_lo + g * L.group_experts;
