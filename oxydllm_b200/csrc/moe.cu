@@ -96,21 +96,27 @@ moe_route_kernel(const float *__restrict__ logits, int tokens, int experts, int 
 }
 
 // counts[e - e_lo] = number of (token, slot) pairs routed to expert e, for e in [e_lo, e_hi).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 moe_count_kernel(const int *__restrict__ top_idx, int pairs, int e_lo, int *__restrict__ counts)
 {
-    __shared__ int part[8];
+    __shared__ int part[32];
     const int e = e_lo + blockIdx.x;
     int c = 0;
-    for (int i = threadIdx.x; i < pairs; i += blockDim.x) c += top_idx[i] == e;
+    const int quads = pairs / 4; // top_idx sits on a 256-byte boundary of the workspace
+    for (int i = threadIdx.x; i < quads; i += blockDim.x) {
+        const int4 v = __ldg(reinterpret_cast<const int4 *>(top_idx) + i);
+        c += (v.x == e) + (v.y == e) + (v.z == e) + (v.w == e);
+    }
+    for (int i = quads * 4 + threadIdx.x; i < pairs; i += blockDim.x) c += top_idx[i] == e;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = c;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int t = 0;
-        for (int w = 0; w < 8; w++) t += part[w];
-        counts[blockIdx.x] = t;
+    if (threadIdx.x < 32) {
+        int t = part[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+        if (threadIdx.x == 0) counts[blockIdx.x] = t;
     }
 }
 
@@ -154,36 +160,58 @@ __global__ void moe_plan_blocks_kernel(const int *__restrict__ counts, int n_exp
 }
 
 // Stable partition: position of pair i among the pairs of its expert, in pair (= token) order.
-// One CTA per expert; a block-wide ballot scan keeps the order deterministic.
+// One CTA per expert walks the pairs 4096 at a time (four neighbours per thread); a scan over the threads'
+// hit counts keeps the order deterministic.
 __global__ void __launch_bounds__(1024)
 moe_scatter_kernel(const int *__restrict__ top_idx, int pairs, int e_lo, const int *__restrict__ offsets,
                    int *__restrict__ perm, int *__restrict__ inv)
 {
-    __shared__ int warp_cnt[32];
-    __shared__ int base_s;
+    __shared__ int warp_cnt[32], warp_off[32];
+    __shared__ int total_s;
     const int e = e_lo + blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) base_s = offsets[blockIdx.x];
-    __syncthreads();
-    for (int start = 0; start < pairs; start += 1024) {
-        const int i = start + threadIdx.x;
-        const bool hit = i < pairs && top_idx[i] == e;
-        const unsigned ballot = __ballot_sync(0xFFFFFFFFu, hit);
-        if (lane == 0) warp_cnt[warp] = __popc(ballot);
-        __syncthreads();
-        int before = 0, total = 0;
-        for (int w = 0; w < 32; w++) {
-            const int c = warp_cnt[w];
-            if (w < warp) before += c;
-            total += c;
+    int base = offsets[blockIdx.x];
+    for (int start = 0; start < pairs; start += 4096) {
+        const int i0 = start + 4 * (int)threadIdx.x;
+        int id[4] = {-1, -1, -1, -1};
+        if (i0 + 3 < pairs) {
+            const int4 v = __ldg(reinterpret_cast<const int4 *>(top_idx + i0)); // top_idx sits on a 256-byte boundary
+            id[0] = v.x; id[1] = v.y; id[2] = v.z; id[3] = v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (i0 + j < pairs) id[j] = top_idx[i0 + j];
         }
-        if (hit) {
-            const int pos = base_s + before + __popc(ballot & ((1u << lane) - 1u));
-            perm[pos] = i;
-            inv[i] = pos;
+        const int cnt = (id[0] == e) + (id[1] == e) + (id[2] == e) + (id[3] == e);
+        int incl = cnt; // inclusive scan of the hit counts over the warp
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) warp_cnt[warp] = incl;
+        __syncthreads();
+        if (warp == 0) { // exclusive scan of the warps' totals
+            const int c = warp_cnt[lane];
+            int inc2 = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(0xFFFFFFFFu, inc2, o);
+                if (lane >= o) inc2 += t;
+            }
+            warp_off[lane] = inc2 - c;
+            if (lane == 31) total_s = inc2;
         }
         __syncthreads();
-        if (threadIdx.x == 0) base_s += total;
-        __syncthreads();
+        int pos = base + warp_off[warp] + incl - cnt;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (id[j] == e) {
+                perm[pos] = i0 + j;
+                inv[i0 + j] = pos;
+                pos += 1;
+            }
+        base += total_s;
+        __syncthreads(); // warp_cnt, warp_off and total_s are rewritten by the next pass
     }
 }
 
@@ -212,19 +240,29 @@ moe_combine_kernel(const __nv_bfloat16 *__restrict__ yp, const int *__restrict__
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < (size_t)tokens * chunks;
          idx += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(idx / chunks), c = (int)(idx % chunks);
-        int order[MOE_MAX_TOPK];
-        for (int s = 0; s < top_k; s++) order[s] = s;
-        for (int a = 1; a < top_k; a++) // insertion sort by expert id (k <= 8)
-            for (int b = a; b > 0 && top_idx[(size_t)t * top_k + order[b]] < top_idx[(size_t)t * top_k + order[b - 1]]; b--) {
-                const int tmp = order[b]; order[b] = order[b - 1]; order[b - 1] = tmp;
-            }
+        int order[MOE_MAX_TOPK], ids[MOE_MAX_TOPK];
+#pragma unroll
+        for (int s = 0; s < MOE_MAX_TOPK; s++) {
+            order[s] = s;
+            ids[s] = s < top_k ? __ldg(top_idx + (size_t)t * top_k + s) : 0x7FFFFFFF;
+        }
+#pragma unroll
+        for (int a = 1; a < MOE_MAX_TOPK; a++) // insertion sort by expert id (k <= 8), in registers
+#pragma unroll
+            for (int b = a; b > 0; b--)
+                if (ids[b] < ids[b - 1]) {
+                    const int ti = ids[b]; ids[b] = ids[b - 1]; ids[b - 1] = ti;
+                    const int to = order[b]; order[b] = order[b - 1]; order[b - 1] = to;
+                }
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int s = 0; s < top_k; s++) {
-            const size_t pair = (size_t)t * top_k + order[s];
-            const int e = top_idx[pair];
+#pragma unroll
+        for (int s = 0; s < MOE_MAX_TOPK; s++) {
+            if (s >= top_k) break;
+            const int e = ids[s];
             if (e < e_lo || e >= e_hi) continue;
-            const float w = top_w[pair];
-            const uint4 v = reinterpret_cast<const uint4 *>(yp + (size_t)inv[pair] * hidden)[c];
+            const size_t pair = (size_t)t * top_k + order[s];
+            const float w = __ldg(top_w + pair);
+            const uint4 v = reinterpret_cast<const uint4 *>(yp + (size_t)__ldg(inv + pair) * hidden)[c];
             const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int q = 0; q < 4; q++) {
@@ -383,7 +421,7 @@ static int moe_forward_impl(const void *x, int x_dtype, const float *router_logi
     // no dequantized slab, one launch per projection over all experts.
     const bool fused = moe_fused_supported(2 * inter, hidden, gu_blocks, gu_scales, xs, h, inter) &&
                        moe_fused_supported(hidden, inter, dn_blocks, dn_scales, h, xs, hidden);
-    moe_count_kernel<<<n_exp, 256, 0, st>>>(top_idx, pairs, expert_lo, counts);
+    moe_count_kernel<<<n_exp, 1024, 0, st>>>(top_idx, pairs, expert_lo, counts);
     if (fused) moe_plan_blocks_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, moe_fused_block_rows(), offsets, entries, grp_beg);
     else moe_plan_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, L.group_experts, offsets, entries, grp_beg);
     moe_scatter_kernel<<<n_exp, 1024, 0, st>>>(top_idx, pairs, expert_lo, offsets, perm, inv);

@@ -3,16 +3,16 @@
 // Mirrors the expert half of MoeFeedForward::forward (moe.rs:466-499, dispatch_sparse 563-607) with the
 // experts' Mxfp4Linear weights (linear.rs, [experts, out, in / 32, 16] blocks + [experts, out, in / 32] scales).
 //
-// A unit of work is (token block of one expert: up to 192 expert-sorted rows) x (128 out features). The grid is
+// A unit of work is (token block of one expert: up to 256 expert-sorted rows) x (128 out features). The grid is
 // persistent: CTA b takes units b, b + grid, ... of a device-side table, feature tiles fastest, so that CTAs
 // running at the same time share their token block in L2. Per CTA:
 //   warp 0 (one lane)   TMA: boxes of packed nibbles (128 out features x 32 bytes = 64 input columns) into a
-//                       ring of eight slots;
+//                       ring of six slots;
 //   warp 2 (one lane)   TMA: the stage's tile of the activations ([rows, 64] bf16 in boxes of 64 rows, 128-byte swizzle)
 //                       into one of four slots;
-//   warps 4..19         unpack, two teams of eight warps taking rounds of two stages in turn: a thread turns
+//   warps 4..19         unpack, two teams of eight warps taking stages in turn: a thread turns
 //                       one 16-byte block (32 weights; its E8M0 scale byte read through L1/L2) into 32 bf16 weights, the bits the
-//                       dequantization kernel writes, as four 16-byte chunks of the K-major operand row;
+//                       dequantization kernel writes, as four 16-byte chunks of the K-major operand row (128-byte swizzle) in one of four slots;
 //   warp 1 (one lane)   tcgen05.mma kind::f16, A = weights [128, 64], B = activations, D[128, rows] f32 in one of
 //                       two tensor-memory buffers for the whole of k; commits free the slots;
 //   warps 20..23        epilogue of the previous unit while the next one accumulates: accumulator rows (out
@@ -39,7 +39,7 @@ constexpr int MF_BK = 64;                      // input columns per stage
 constexpr int MF_UNPACK_WARPS = 16, MF_TEAMS = 2, MF_TEAM_WARPS = 8, MF_ROUND = 1;
 constexpr int MF_EPI_WARPS = 4;
 constexpr int MF_THREADS = (4 + MF_UNPACK_WARPS + MF_EPI_WARPS) * 32;
-constexpr int MF_A_SLOTS = 4;                  // three rounds of unpacked weights between the teams and the MMAs
+constexpr int MF_A_SLOTS = 4;                  // unpacked weight tiles between the teams and the MMAs
 constexpr int MF_X_SLOTS = 4;
 constexpr int MF_RAW_SLOTS = 6;
 constexpr int MF_MAX_TOK = 256;                // rows of a token block
@@ -52,30 +52,18 @@ static_assert(MF_RAW_SLOTS % MF_ROUND == 0 && MF_A_SLOTS % MF_ROUND == 0, "a rou
 constexpr int MF_SMEM_BUDGET = 227 * 1024;
 
 struct MoeFusedParams {
-    const int4 *entries;   // token blocks: {first row in the expert-sorted matrix, rows (<= 192), expert, -}
+    const int4 *entries;   // token blocks: {first row in the expert-sorted matrix, rows (<= 256), expert, -}
     const int *n_blocks;   // how many
     const uint8_t *scales; // [experts, n, k / 32]
     const void *bias;      // [experts, n] or null
     void *out;
     int *flag;
-    int n, k, nkb, nk2;    // out features per expert, in features, scale bytes per row, stages per unit (even)
+    int n, k, nkb, nk2;    // out features per expert, in features, scale bytes per row, stages per unit (whole rounds)
     int tiles_n, bias_dtype, ldo, epi;
     float limit;
     int dbg;               // tuning builds: parts of the pipeline switched off for timing
 };
 
-__device__ __forceinline__ uint32_t mf_lds32(uint32_t addr)
-{
-    uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint32_t mf_lds8(uint32_t addr)
-{
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
 __device__ __forceinline__ uint4 mf_lds128(uint32_t addr)
 {
     uint4 v;
