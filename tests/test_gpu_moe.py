@@ -140,3 +140,46 @@ def test_device_combine_matches_host_combine(cuda):
     ref = parallel.combine_rows(torch.from_numpy(rows), send_order, torch.from_numpy(top_idx), torch.from_numpy(top_w))
     got = moe.combine(dev(rows, torch.bfloat16), dev(top_idx), dev(top_w), pos.cuda(), e, torch.float32)
     assert torch.allclose(got.cpu(), ref, rtol=1e-6, atol=1e-6)
+
+
+def test_moe_skewed_routing_many_blocks_and_empty_experts(cuda):
+    """One expert takes most rows (several token blocks of the grouped kernel), others take none or a handful."""
+    tokens, experts, hidden, inter = 700, 8, 128, 128
+    d = synth.gptoss_moe(experts, hidden, inter, tokens, seed=21)
+    lg = np.full((tokens, experts), -30.0, dtype=np.float32)
+    lg[:, 0] = 5.0                                  # every token picks expert 0 first
+    lg[:, 1:4] = np.random.default_rng(3).standard_normal((tokens, 3)).astype(np.float32)
+    lg[:5, 6] = 9.0                                 # five rows for expert 6; experts 4, 5, 7 get nothing or ties only
+    d["logits"] = lg
+    layer = build(d)
+    y = layer.forward_with_logits(dev(d["x"], torch.bfloat16), dev(lg))
+    layer.check()
+    idx, w = oracle.moe_route(lg, 4, True)
+    counts = np.bincount(idx.reshape(-1), minlength=experts)
+    assert counts[0] == tokens and counts.min() == 0  # more than two blocks of 256 rows, and an empty expert
+    ref = oracle.gptoss_moe(d["x"], idx, w, d["gu_blocks"], d["gu_scales"], d["gu_bias"], d["dn_blocks"], d["dn_scales"],
+                            d["dn_bias"], hidden, inter, 7.0)
+    got = y.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert (np.abs(got - ref) <= 2e-2 * np.abs(ref).max(axis=1, keepdims=True) + 1e-5).all()
+
+
+def test_moe_tiny_block_scales_take_the_f32_route(cuda):
+    """E8M0 bytes below 4 (2^-127 .. 2^-124: products leave the normal bf16 range) in a tenth of the blocks."""
+    tokens, experts, hidden, inter = 300, 4, 256, 192
+    d = synth.gptoss_moe(experts, hidden, inter, tokens, seed=33)
+    rng = np.random.default_rng(8)
+    for key in ("gu_scales", "dn_scales"):
+        sc = d[key].copy()
+        mask = rng.random(sc.shape) < 0.1
+        sc[mask] = rng.integers(0, 4, size=int(mask.sum()), dtype=np.uint8)
+        d[key] = sc
+    layer = build(d)
+    y = layer.forward_with_logits(dev(d["x"], torch.bfloat16), dev(d["logits"]))
+    layer.check()
+    idx, w = oracle.moe_route(d["logits"], 4, True)
+    ref = oracle.gptoss_moe(d["x"], idx, w, d["gu_blocks"], d["gu_scales"], d["gu_bias"], d["dn_blocks"], d["dn_scales"],
+                            d["dn_bias"], hidden, inter, 7.0)
+    got = y.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert (np.abs(got - ref) <= 2e-2 * np.abs(ref).max(axis=1, keepdims=True) + 1e-5).all()
