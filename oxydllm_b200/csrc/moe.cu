@@ -143,11 +143,14 @@ __global__ void moe_plan_kernel(const int *__restrict__ counts, int n_exp, int e
 __global__ void moe_plan_blocks_kernel(const int *__restrict__ counts, int n_exp, int e_lo, int max_rows, int *__restrict__ offsets,
                                        int4 *__restrict__ entries, int *__restrict__ n_blocks)
 {
+    __shared__ int cnt_s[MOE_MAX_EXPERTS];
+    for (int i = threadIdx.x; i < n_exp; i += blockDim.x) cnt_s[i] = counts[i]; // one round trip for all counts
+    __syncthreads();
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     int off = 0, nb = 0;
     for (int i = 0; i < n_exp; i++) {
         offsets[i] = off;
-        const int c = counts[i];
+        const int c = cnt_s[i];
         if (c > 0) {
             const int parts = (c + max_rows - 1) / max_rows;
             const int size = ((c + parts - 1) / parts + 15) / 16 * 16;
@@ -254,16 +257,28 @@ moe_combine_kernel(const __nv_bfloat16 *__restrict__ yp, const int *__restrict__
                     const int ti = ids[b]; ids[b] = ids[b - 1]; ids[b - 1] = ti;
                     const int to = order[b]; order[b] = order[b - 1]; order[b - 1] = to;
                 }
+        // all index loads first, then all row loads, then the sums in ascending expert order: the loads of a token's
+        // slots do not wait for one another
+        int pos[MOE_MAX_TOPK];
+        float wv[MOE_MAX_TOPK];
+        bool use[MOE_MAX_TOPK];
+#pragma unroll
+        for (int s = 0; s < MOE_MAX_TOPK; s++) {
+            use[s] = s < top_k && ids[s] >= e_lo && ids[s] < e_hi;
+            const size_t pair = (size_t)t * top_k + order[s];
+            pos[s] = use[s] ? __ldg(inv + pair) : 0;
+            wv[s] = use[s] ? __ldg(top_w + pair) : 0.0f;
+        }
+        uint4 rows[MOE_MAX_TOPK];
+#pragma unroll
+        for (int s = 0; s < MOE_MAX_TOPK; s++)
+            rows[s] = use[s] ? reinterpret_cast<const uint4 *>(yp + (size_t)pos[s] * hidden)[c] : make_uint4(0u, 0u, 0u, 0u);
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
         for (int s = 0; s < MOE_MAX_TOPK; s++) {
-            if (s >= top_k) break;
-            const int e = ids[s];
-            if (e < e_lo || e >= e_hi) continue;
-            const size_t pair = (size_t)t * top_k + order[s];
-            const float w = __ldg(top_w + pair);
-            const uint4 v = reinterpret_cast<const uint4 *>(yp + (size_t)__ldg(inv + pair) * hidden)[c];
-            const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
+            if (!use[s]) continue;
+            const float w = wv[s];
+            const uint32_t vv[4] = {rows[s].x, rows[s].y, rows[s].z, rows[s].w};
 #pragma unroll
             for (int q = 0; q < 4; q++) {
                 acc[2 * q] = fmaf(w, __uint_as_float(vv[q] << 16), acc[2 * q]);
