@@ -14,7 +14,8 @@
 //                       one 16-byte block (32 weights; its E8M0 scale byte read through L1/L2) into 32 bf16 weights, the bits the
 //                       dequantization kernel writes, as four 16-byte chunks of the K-major operand row (128-byte swizzle) in one of four slots;
 //   warp 1 (one lane)   tcgen05.mma kind::f16, A = weights [128, 64], B = activations, D[128, rows] f32 in one of
-//                       two tensor-memory buffers for the whole of k; commits free the slots;
+//                       two tensor-memory buffers for the whole of k; one commit per stage frees the slot (weights and
+//                       activations share a full / empty barrier pair per slot, so the issuer polls once per stage);
 //   warps 20..23        epilogue of the previous unit while the next one accumulates: accumulator rows (out
 //                       features) -> + bias -> bf16 out[row, feature], or the clamped SwiGLU of GPT-OSS on
 //                       interleaved (gate, up) features -> out[row, feature / 2].
@@ -27,7 +28,7 @@ namespace oxq {
 
 #ifdef OXQ_TUNING
 #define MF_DBG(bit) (p.dbg & (bit))
-__device__ long long g_mf_trace[8][256]; // clock stamps of CTA 0, per role and stage (tuning builds only)
+__device__ long long g_mf_trace[10][256]; // clock stamps of CTA 0, per role and stage (tuning builds only)
 #define MF_TRACE(role, it) do { if (blockIdx.x == 0 && (it) < 256) g_mf_trace[role][it] = clock64(); } while (0)
 #else
 #define MF_DBG(bit) 0
@@ -39,15 +40,15 @@ constexpr int MF_BK = 64;                      // input columns per stage
 constexpr int MF_UNPACK_WARPS = 16, MF_TEAMS = 2, MF_TEAM_WARPS = 8, MF_ROUND = 1;
 constexpr int MF_EPI_WARPS = 4;
 constexpr int MF_THREADS = (4 + MF_UNPACK_WARPS + MF_EPI_WARPS) * 32;
-constexpr int MF_A_SLOTS = 4;                  // unpacked weight tiles between the teams and the MMAs
-constexpr int MF_X_SLOTS = 4;
+constexpr int MF_SLOTS = 4;                    // operand slots: an unpacked weight tile and an activation tile each, one pair of barriers
+constexpr int MF_A_SLOTS = MF_SLOTS, MF_X_SLOTS = MF_SLOTS;
 constexpr int MF_RAW_SLOTS = 6;
 constexpr int MF_MAX_TOK = 256;                // rows of a token block
 constexpr int MF_TMEM_BUF = 256;               // accumulator columns per buffer
 constexpr int MF_A_BYTES = MF_ROWS * MF_BK * 2;
 constexpr int MF_XBOX_ROWS = 64, MF_XBOX_BYTES = MF_XBOX_ROWS * MF_BK * 2, MF_X_BYTES = MF_MAX_TOK * MF_BK * 2; // activation rows travel in boxes of 64
 constexpr int MF_RAW_BYTES = MF_ROWS * MF_BK / 2;
-constexpr int MF_NUM_BARS = 2 * MF_RAW_SLOTS + 2 * MF_X_SLOTS + 2 * MF_A_SLOTS + 4;
+constexpr int MF_NUM_BARS = 2 * MF_RAW_SLOTS + 2 * MF_SLOTS + 4;
 static_assert(MF_RAW_SLOTS % MF_ROUND == 0 && MF_A_SLOTS % MF_ROUND == 0, "a round's slots are neighbours");
 constexpr int MF_SMEM_BUDGET = 227 * 1024;
 
@@ -91,11 +92,11 @@ __global__ void __launch_bounds__(MF_THREADS, 1)
     const uint32_t bars = raw_base + MF_RAW_SLOTS * MF_RAW_BYTES;
     auto rawfull_bar = [&](int r) { return bars + 8u * r; };
     auto rawempty_bar = [&](int r) { return bars + 8u * (MF_RAW_SLOTS + r); };
-    auto xfull_bar = [&](int s) { return bars + 8u * (2 * MF_RAW_SLOTS + s); };
-    auto xempty_bar = [&](int s) { return bars + 8u * (2 * MF_RAW_SLOTS + MF_X_SLOTS + s); };
-    auto ready_bar = [&](int s) { return bars + 8u * (2 * MF_RAW_SLOTS + 2 * MF_X_SLOTS + s); };
-    auto aempty_bar = [&](int s) { return bars + 8u * (2 * MF_RAW_SLOTS + 2 * MF_X_SLOTS + MF_A_SLOTS + s); };
-    const uint32_t misc = bars + 8u * (2 * MF_RAW_SLOTS + 2 * MF_X_SLOTS + 2 * MF_A_SLOTS);
+    // full: the slot's weight tile is unpacked (one arrival per warp of the team) and its activation tile has landed (the
+    // producer's arrival with the byte count); empty: the MMAs that read the slot have completed (one commit)
+    auto full_bar = [&](int s) { return bars + 8u * (2 * MF_RAW_SLOTS + s); };
+    auto empty_bar = [&](int s) { return bars + 8u * (2 * MF_RAW_SLOTS + MF_SLOTS + s); };
+    const uint32_t misc = bars + 8u * (2 * MF_RAW_SLOTS + 2 * MF_SLOTS);
     auto tfull_bar = [&](int b) { return misc + 8u * b; };
     auto tempty_bar = [&](int b) { return misc + 8u * (2 + b); };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + (bars - base) + 8 * MF_NUM_BARS);
@@ -109,13 +110,9 @@ __global__ void __launch_bounds__(MF_THREADS, 1)
             mbar_init(rawfull_bar(r), 1);
             mbar_init(rawempty_bar(r), MF_TEAM_WARPS);
         }
-        for (int s = 0; s < MF_X_SLOTS; s++) {
-            mbar_init(xfull_bar(s), 1);
-            mbar_init(xempty_bar(s), 1);
-        }
-        for (int s = 0; s < MF_A_SLOTS; s++) {
-            mbar_init(ready_bar(s), MF_TEAM_WARPS);
-            mbar_init(aempty_bar(s), 1);
+        for (int s = 0; s < MF_SLOTS; s++) {
+            mbar_init(full_bar(s), MF_TEAM_WARPS + 1);
+            mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(tfull_bar(b), 1);
@@ -161,14 +158,14 @@ __global__ void __launch_bounds__(MF_THREADS, 1)
                 const int4 en = __ldg(p.entries + u / p.tiles_n);
                 const int boxes = (en.y + MF_XBOX_ROWS - 1) / MF_XBOX_ROWS;
                 for (int it = 0; it < nk2; it++, gx++) {
-                    if (gx >= MF_X_SLOTS && !mbar_wait(xempty_bar(xs), xph ^ 1u, p.flag, 5)) { ok = false; break; }
+                    if (gx >= MF_SLOTS && !mbar_wait(empty_bar(xs), xph ^ 1u, p.flag, 5)) { ok = false; break; }
                     const uint32_t dst = x_base + (uint32_t)xs * MF_X_BYTES;
                     MF_TRACE(1, gx);
-                    if (MF_DBG(2)) mf_arrive(xfull_bar(xs));
+                    if (MF_DBG(2)) mf_arrive(full_bar(xs));
                     else {
-                    mbar_arrive_expect_tx(xfull_bar(xs), (uint32_t)boxes * MF_XBOX_BYTES);
+                    mbar_arrive_expect_tx(full_bar(xs), (uint32_t)boxes * MF_XBOX_BYTES);
                     for (int b = 0; b < boxes; b++)
-                        tma_load_2d(dst + (uint32_t)b * MF_XBOX_BYTES, &xmap, xfull_bar(xs), it * MF_BK, en.x + b * MF_XBOX_ROWS);
+                        tma_load_2d(dst + (uint32_t)b * MF_XBOX_BYTES, &xmap, full_bar(xs), it * MF_BK, en.x + b * MF_XBOX_ROWS);
                     }
                     if (++xs == MF_X_SLOTS) { xs = 0; xph ^= 1u; }
                 }
@@ -177,36 +174,47 @@ __global__ void __launch_bounds__(MF_THREADS, 1)
     } else if (warp == 1) {
         // ---- MMA issue ----------------------------------------------------------------------------------
         if (elect_one()) {
-            int xs = 0;
-            uint32_t xph = 0, gs = 0, ul = 0;
+            // One thread issues every MMA of the CTA, so its instruction count per stage is on the critical path: the loop
+            // runs over all stages of all this CTA's units, four at a time, so that slot, barrier and descriptor addresses are
+            // constants of the unrolled body; one poll (full) and one commit (empty) per stage.
+            int my_units = 0;
+            if ((int)blockIdx.x < n_units) my_units = (n_units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1;
+            const uint32_t total = (uint32_t)my_units * (uint32_t)nk2;
+            const uint64_t da0 = kmajor_sw128_desc(base), db0 = kmajor_sw128_desc(x_base);
+            const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
+            uint32_t ul = 0, idesc = 0, d_tmem = tmem_base, buf = 0;
+            int it = 0;
             bool ok = true;
-            for (int u = blockIdx.x; ok && u < n_units; u += gridDim.x, ul++) {
-                const int4 en = __ldg(p.entries + u / p.tiles_n);
-                const int mpad = (en.y + 15) & ~15;
-                const uint32_t idesc = tc_idesc(MF_ROWS, mpad);
-                const uint32_t buf = ul & 1u;
-                if (ul >= 2 && !mbar_wait(tempty_bar(buf), ((ul >> 1) & 1u) ^ 1u, p.flag, 8)) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * MF_TMEM_BUF;
-                for (int it = 0; it < nk2; it++, gs++) {
-                    const uint32_t s = gs % MF_A_SLOTS;
-                    const bool ta = mbar_test(ready_bar(s), (gs / MF_A_SLOTS) & 1u), tx = mbar_test(xfull_bar(xs), xph); // both polls in flight
-                    if (!ta) ok = mbar_wait(ready_bar(s), (gs / MF_A_SLOTS) & 1u, p.flag, 2);
-                    if (ok && !tx) ok = mbar_wait(xfull_bar(xs), xph, p.flag, 6);
-                    if (!ok) break;
-                    MF_TRACE(2, gs);
-                    tc_fence_after();
-                    const uint64_t da = kmajor_sw128_desc(base + s * MF_A_BYTES), db = kmajor_sw128_desc(x_base + (uint32_t)xs * MF_X_BYTES);
-                    if (!MF_DBG(4))
-#pragma unroll
-                    for (int kk = 0; kk < MF_BK / 16; kk++) // 16 input columns: 32 bytes inside a swizzled K-major row
-                        umma_bf16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (it | kk) != 0);
-                    umma_commit(aempty_bar(s));
-                    umma_commit(xempty_bar(xs));
-                    MF_TRACE(3, gs);
-                    if (++xs == MF_X_SLOTS) { xs = 0; xph ^= 1u; }
+            auto stage = [&](const uint32_t gs, const int j) { // j = gs % MF_SLOTS, a constant after unrolling
+                if (it == 0) { // first stage of a unit
+                    const int u = (int)blockIdx.x + (int)ul * (int)gridDim.x;
+                    const int rows = __ldg(p.entries + u / p.tiles_n).y;
+                    idesc = tc_idesc(MF_ROWS, (rows + 15) & ~15);
+                    buf = ul & 1u;
+                    if (ul >= 2 && !mbar_wait(tempty_bar(buf), ((ul >> 1) & 1u) ^ 1u, p.flag, 8)) { ok = false; return; }
+                    d_tmem = tmem_base + buf * MF_TMEM_BUF;
                 }
-                if (ok) umma_commit(tfull_bar(buf));
+                MF_TRACE(7, gs);
+                if (!mbar_wait(full0 + 8u * j, (gs / MF_SLOTS) & 1u, p.flag, 2)) { ok = false; return; }
+                MF_TRACE(2, gs);
+                tc_fence_after();
+                const uint64_t da = da0 + (uint64_t)(j * (MF_A_BYTES >> 4)), db = db0 + (uint64_t)(j * (MF_X_BYTES >> 4));
+                if (!MF_DBG(4))
+#pragma unroll
+                for (int kk = 0; kk < MF_BK / 16; kk++) // 16 input columns: 32 bytes inside a swizzled K-major row
+                    umma_bf16(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (it | kk) != 0);
+                umma_commit(empty0 + 8u * j);
+                MF_TRACE(3, gs);
+                if (++it == nk2) { // last stage of the unit: the accumulator is complete once these MMAs are
+                    umma_commit(tfull_bar(buf));
+                    it = 0;
+                    ul += 1;
+                }
+            };
+            for (uint32_t g = 0; ok && g < total; g += MF_SLOTS) {
+#pragma unroll
+                for (int j = 0; j < MF_SLOTS; j++)
+                    if (ok && g + j < total) stage(g + j, j);
             }
         }
     } else if (warp >= 4 && warp < 4 + MF_UNPACK_WARPS) {
@@ -250,12 +258,12 @@ __global__ void __launch_bounds__(MF_THREADS, 1)
 #pragma unroll
             for (int h = 0; h < MF_ROUND; h++) {
                 tr[h] = mbar_test(rawfull_bar(r0 + h), rph);
-                ta[h] = gs0 < MF_A_SLOTS || mbar_test(aempty_bar(s0 + h), aph ^ 1u);
+                ta[h] = gs0 < MF_SLOTS || mbar_test(empty_bar(s0 + h), aph ^ 1u);
             }
 #pragma unroll
             for (int h = 0; h < MF_ROUND; h++) {
                 if (ok && !tr[h]) ok = mbar_wait(rawfull_bar(r0 + h), rph, p.flag, 3);
-                if (ok && !ta[h]) ok = mbar_wait(aempty_bar(s0 + h), aph ^ 1u, p.flag, 7);
+                if (ok && !ta[h]) ok = mbar_wait(empty_bar(s0 + h), aph ^ 1u, p.flag, 7);
             }
             if (!ok) break;
             if (ut == 0) MF_TRACE(4, gs0);
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(MF_THREADS, 1)
             if (lane == 0) {
 #pragma unroll
                 for (int h = 0; h < MF_ROUND; h++) {
-                    mf_arrive(ready_bar(s0 + h));
+                    mf_arrive(full_bar(s0 + h));
                     mf_arrive(rawempty_bar(r0 + h));
                 }
             }
