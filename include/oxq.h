@@ -199,6 +199,13 @@ int oxq_selftest_wait_expiry(void *workspace, int code, void *stream);
  * scratch inside `workspace` (256-byte aligned, at least 1 MiB). */
 int oxq_selftest_gemm_wait_expiry(void *workspace, size_t workspace_bytes, int m, void *stream);
 
+/* The same for the grouped kernel of the MoE expert layer (the one that unpacks MXFP4 inside its tensor-core
+ * loop): one unit of work whose weight producer never loads, so every other role gives up on its bounded
+ * wait (about two seconds), the flag word takes a code, tensor memory is freed and the kernel returns.
+ * workspace: at least 1 MiB, 256-byte aligned; oxq_gemm_check(workspace) afterwards returns
+ * OXQ_ERR_DEVICE_FLAG once. No counterpart in the reference. */
+int oxq_selftest_moe_wait_expiry(void *workspace, size_t workspace_bytes, void *stream);
+
 /* Zeroes the 256-byte header (flag word) of a fresh workspace on `stream`. */
 int oxq_gemm_workspace_init(void *workspace, void *stream);
 

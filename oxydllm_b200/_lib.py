@@ -40,6 +40,7 @@ SIGNATURES = {
     "oxq_gemm_check": [_vp, _vp],
     "oxq_selftest_wait_expiry": [_vp, ctypes.c_int, _vp],
     "oxq_selftest_gemm_wait_expiry": [_vp, ctypes.c_size_t, ctypes.c_int, _vp],
+    "oxq_selftest_moe_wait_expiry": [_vp, ctypes.c_size_t, _vp],
     "oxq_awq_gemv_check": [_vp],
     "oxq_gemm_workspace_init": [_vp, _vp],
     "oxq_awq_gemm": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp, _sz, _vp],

@@ -63,6 +63,7 @@ struct MoeFusedParams {
     int tiles_n, bias_dtype, ldo, epi;
     float limit;
     int dbg;               // tuning builds: parts of the pipeline switched off for timing
+    int test_skip_loads;   // self-test only: the weight producer issues nothing, so the waits of the other roles run out
 };
 
 __device__ __forceinline__ uint4 mf_lds128(uint32_t addr)
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(MF_THREADS, 1)
         if (elect_one()) {
             uint32_t gs = 0, ul = 0;
             bool ok = true;
-            for (int u = blockIdx.x; ok && u < n_units; u += gridDim.x, ul++) {
+            for (int u = blockIdx.x; ok && u < n_units && !p.test_skip_loads; u += gridDim.x, ul++) {
                 const int tb = u / p.tiles_n, f = u - tb * p.tiles_n;
                 const int4 en = __ldg(p.entries + tb);
                 const int rowbase = en.z * p.n + f * MF_ROWS;
@@ -384,6 +385,8 @@ __global__ void __launch_bounds__(MF_THREADS, 1)
     }
 }
 
+static thread_local int g_moe_selftest_skip_loads = 0; // set only inside oxq_selftest_moe_wait_expiry
+
 // Rows of a token block (the plan kernel cuts every expert's rows into blocks of at most this many).
 int moe_fused_block_rows() { return MF_MAX_TOK; }
 
@@ -412,6 +415,7 @@ int moe_fused_grouped(const void *a, int a_rows, const uint8_t *blocks, const ui
     p.nk2 = (nk + MF_ROUND - 1) / MF_ROUND * MF_ROUND;
     p.tiles_n = (n + MF_ROWS - 1) / MF_ROWS;
     p.bias_dtype = bias_dtype; p.ldo = ldo; p.epi = epi; p.limit = limit;
+    p.test_skip_loads = g_moe_selftest_skip_loads;
     if (const char *env = tuning_env("OXQ_MF_DBG")) p.dbg = atoi(env);
     constexpr size_t smem = 1024 + MF_A_SLOTS * MF_A_BYTES + MF_X_SLOTS * MF_X_BYTES + MF_RAW_SLOTS * MF_RAW_BYTES + 8 * MF_NUM_BARS + 16;
     static_assert(smem <= (size_t)MF_SMEM_BUDGET, "operand slots and the ring must fit one CTA's shared memory");
@@ -435,6 +439,36 @@ int moe_fused_grouped(const void *a, int a_rows, const uint8_t *blocks, const ui
 }
 
 } // namespace oxq
+
+// Self-test of the grouped kernel's abort path: one unit (one expert, 128 out features, 64 in features, 16 rows) whose
+// weight producer never loads. The unpack teams, the MMA issuer, the activation producer and the epilogue warps each give
+// up on their bounded wait (about two seconds, side by side), the flag word of the workspace takes the first code,
+// tensor memory is freed and the kernel returns; oxq_gemm_check(workspace) then reports it. Nothing faults or hangs.
+OXQ_EXPORT int oxq_selftest_moe_wait_expiry(void *workspace, size_t workspace_bytes, void *stream)
+{
+    oxq::clear_error();
+    OXQ_REQUIRE(workspace && workspace_bytes >= (1u << 20) && oxq::aligned(workspace, 256), OXQ_ERR_WORKSPACE,
+                "oxq_selftest_moe_wait_expiry: 256-byte aligned workspace of at least 1 MiB needed");
+    unsigned char *b = reinterpret_cast<unsigned char *>(workspace);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int n = 128, k = 64, rows = 16;
+    // table | rows [256 + 128, 64] bf16 | blocks [128, 32] | scales [128, 2] | out [256, 128] bf16
+    int4 *entries = reinterpret_cast<int4 *>(b + 4096);
+    int *n_blocks = reinterpret_cast<int *>(b + 4096 + 64);
+    void *a = b + 8192;
+    uint8_t *blocks = b + 8192 + 384 * 64 * 2, *scales = blocks + 128 * 32;
+    void *out = b + 131072;
+    const int4 en = make_int4(0, rows, 0, 0);
+    const int one = 1;
+    OXQ_CUDA(cudaMemcpyAsync(entries, &en, sizeof(en), cudaMemcpyHostToDevice, st));
+    OXQ_CUDA(cudaMemcpyAsync(n_blocks, &one, sizeof(one), cudaMemcpyHostToDevice, st));
+    OXQ_CUDA(cudaStreamSynchronize(st)); // the two host words above live on this stack frame
+    oxq::g_moe_selftest_skip_loads = 1;
+    const int rc = oxq::moe_fused_grouped(a, 384, blocks, scales, 1, n, k, entries, n_blocks, nullptr, 0, out, n, 0, 0.0f,
+                                          reinterpret_cast<int *>(workspace), st);
+    oxq::g_moe_selftest_skip_loads = 0;
+    return rc;
+}
 
 #ifdef OXQ_TUNING
 OXQ_EXPORT int oxq_mf_trace_read(long long *out)

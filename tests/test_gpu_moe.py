@@ -183,3 +183,25 @@ def test_moe_tiny_block_scales_take_the_f32_route(cuda):
     got = y.float().cpu().numpy()
     assert np.isfinite(got).all()
     assert (np.abs(got - ref) <= 2e-2 * np.abs(ref).max(axis=1, keepdims=True) + 1e-5).all()
+
+
+def test_grouped_kernel_survives_a_weight_producer_that_never_loads(cuda):
+    # With no packed box ever arriving, the unpack teams, the MMA issuer and the epilogue warps of the grouped kernel each
+    # give up after the 2 s limit, tensor memory is freed, the kernel returns, the check reports a code once, and the layer
+    # still works afterwards.
+    import ctypes
+    from oxydllm_b200 import _lib, gemm
+    ws = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    _lib.call("oxq_selftest_moe_wait_expiry", ctypes.c_void_p(ws.data_ptr()), ws.numel(), None)
+    with pytest.raises(_lib.OxqError, match=r"bounded wait \d+"):
+        gemm.check(ws)
+    gemm.check(ws)
+    d = synth.gptoss_moe(4, 128, 128, 200, seed=2)
+    layer = build(d)
+    y = layer.forward_with_logits(dev(d["x"], torch.bfloat16), dev(d["logits"]))
+    layer.check()
+    idx, w = oracle.moe_route(d["logits"], 4, True)
+    ref = oracle.gptoss_moe(d["x"], idx, w, d["gu_blocks"], d["gu_scales"], d["gu_bias"], d["dn_blocks"], d["dn_scales"],
+                            d["dn_bias"], 128, 128, 7.0)
+    got = y.float().cpu().numpy()
+    assert (np.abs(got - ref) <= 2e-2 * np.abs(ref).max(axis=1, keepdims=True) + 1e-5).all()
