@@ -303,6 +303,21 @@ int oxq_gptoss_experts_forward(const void *rows, int x_dtype, const int32_t *exp
 int oxq_moe_combine(const void *rows, const int32_t *top_idx, const float *top_w, const int32_t *pos, int tokens,
                     int top_k, int hidden, int num_experts, void *out, int out_dtype, void *stream);
 
+/* Expert parallelism, sender and owner side bookkeeping on the device (no counterpart in the reference, whose
+ * dispatch_sparse, moe.rs:563-607, keeps all experts local): pairs (token, slot) sorted by expert id with the
+ * pair order kept inside an expert. counts i32 [num_experts], offsets i32 [num_experts + 1], perm i32 [pairs]
+ * (perm[i] = the pair sent i-th), inv i32 [pairs] (inv[pair] = its position; the `pos` of oxq_moe_combine).
+ * top_idx i32 [pairs], 16-byte aligned. */
+int oxq_moe_dispatch_plan(const int32_t *top_idx, int pairs, int num_experts, int32_t *counts, int32_t *offsets,
+                          int32_t *perm, int32_t *inv, void *stream);
+
+/* out[i, :] = x[perm[i] / top_k, :], i < rows: the rows of a dispatch in send order. bf16, hidden % 8 == 0. */
+int oxq_moe_gather_rows(const void *x, const int32_t *perm, int rows, int top_k, int hidden, void *out, void *stream);
+
+/* Expert ids of rows received in groups, source rank major and local expert minor: group g holds counts[g] rows
+ * of expert lo + g % n_local. counts i32 [groups], ids i32 [sum of counts]. */
+int oxq_moe_expand_ids(const int32_t *counts, int groups, int n_local, int lo, int32_t *ids, void *stream);
+
 /* Routing alone: softmax over all experts, top-k (ties: lower index), optional
  * renormalisation (moe.rs:472-487). top_idx i32 [tokens, top_k], top_w f32. */
 int oxq_moe_route(const float *router_logits, int tokens, int num_experts, int top_k, int norm_topk, int32_t *top_idx,

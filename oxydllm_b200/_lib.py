@@ -55,6 +55,9 @@ SIGNATURES = {
     "oxq_gptoss_experts_forward": [_vp, _i, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, ctypes.c_float, _i, _i,
                                    _vp, _i, _vp, _sz, _vp],
     "oxq_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _i, _vp],
+    "oxq_moe_dispatch_plan": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp],
+    "oxq_moe_gather_rows": [_vp, _vp, _i, _i, _i, _vp, _vp],
+    "oxq_moe_expand_ids": [_vp, _i, _i, _i, _vp, _vp],
     "oxq_moe_route": [_vp, _i, _i, _i, _i, _vp, _vp, _vp],
     "oxq_awq_gemm_noalloc_max_k": [],
     "oxq_awq_gemm_noalloc": [_vp, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],

@@ -221,9 +221,9 @@ moe_scatter_kernel(const int *__restrict__ top_idx, int pairs, int e_lo, const i
 // xs[pos, :] = x[perm[pos] / top_k, :]  (one warp per row, 16-byte copies)
 __global__ void __launch_bounds__(256)
 moe_gather_kernel(const __nv_bfloat16 *__restrict__ x, const int *__restrict__ perm, const int *__restrict__ total_rows,
-                  int top_k, int hidden, __nv_bfloat16 *__restrict__ xs)
+                  int top_k, int hidden, __nv_bfloat16 *__restrict__ xs, int rows_by_value = 0)
 {
-    const int rows = *total_rows;
+    const int rows = total_rows ? *total_rows : rows_by_value;
     const int lane = threadIdx.x & 31;
     for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < rows; row += (gridDim.x * blockDim.x) >> 5) {
         const uint4 *src = reinterpret_cast<const uint4 *>(x + (size_t)(perm[row] / top_k) * hidden);
@@ -302,6 +302,37 @@ moe_swiglu_kernel(const float *__restrict__ gu, int pairs, int inter, float limi
         const float sig = __fdividef(1.0f, __expf(-1.702f * gate) + 1.0f);
         h[idx] = __float2bfloat16_rn((up + 1.0f) * (gate * sig));
         if (idx < (size_t)pairs) inv[idx] = (int)idx;
+    }
+}
+
+// offsets = exclusive scan of counts (one warp; at most MOE_MAX_EXPERTS entries).
+__global__ void moe_offsets_kernel(const int *__restrict__ counts, int n, int *__restrict__ offsets)
+{
+    __shared__ int cnt_s[MOE_MAX_EXPERTS];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) cnt_s[i] = counts[i];
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    int off = 0;
+    for (int i = 0; i < n; i++) { offsets[i] = off; off += cnt_s[i]; }
+    offsets[n] = off;
+}
+
+// ids of rows that arrive grouped: group g (source rank g / n_local, local expert g % n_local) holds counts[g] rows of
+// expert lo + g % n_local. One CTA: scan of the group sizes in shared memory, then every thread fills whole groups.
+__global__ void __launch_bounds__(1024)
+moe_expand_ids_kernel(const int *__restrict__ counts, int groups, int n_local, int lo, int *__restrict__ ids)
+{
+    __shared__ int start_s[2049];
+    if (threadIdx.x == 0) {
+        int off = 0;
+        for (int g = 0; g < groups; g++) { start_s[g] = off; off += counts[g]; }
+        start_s[groups] = off;
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int g = warp; g < groups; g += 32) {
+        const int a = start_s[g], b = start_s[g + 1], e = lo + g % n_local;
+        for (int i = a + lane; i < b; i += 32) ids[i] = e;
     }
 }
 
@@ -540,5 +571,50 @@ OXQ_EXPORT int oxq_moe_route(const float *router_logits, int tokens, int num_exp
     moe_route_kernel<<<ceil_div(tokens * 32, 256), 256, 0, (cudaStream_t)stream>>>(router_logits, tokens, num_experts,
                                                                                     top_k, norm_topk, top_idx, top_w);
     OXQ_LAUNCH_CHECK("moe_route_kernel");
+    return OXQ_OK;
+}
+
+// Dispatch plan of expert parallelism on the device (the sender side of dispatch_sparse, moe.rs:563-607, when experts live on
+// other ranks): pairs (token, slot) sorted by expert id, pair order kept inside an expert. counts [E], offsets [E + 1],
+// perm [pairs] (perm[i] = pair sent i-th), inv [pairs] (inv[pair] = its position). No counterpart in the reference.
+OXQ_EXPORT int oxq_moe_dispatch_plan(const int32_t *top_idx, int pairs, int num_experts, int32_t *counts, int32_t *offsets,
+                                     int32_t *perm, int32_t *inv, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(top_idx && counts && offsets && perm && inv, OXQ_ERR_NULL, "oxq_moe_dispatch_plan: null pointer");
+    OXQ_REQUIRE(pairs > 0 && num_experts > 0 && num_experts <= MOE_MAX_EXPERTS, OXQ_ERR_BAD_SHAPE,
+                "oxq_moe_dispatch_plan: pairs %d, experts %d (max %d)", pairs, num_experts, MOE_MAX_EXPERTS);
+    OXQ_REQUIRE(aligned(top_idx, 16), OXQ_ERR_BAD_ALIGN, "oxq_moe_dispatch_plan: top_idx must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    moe_count_kernel<<<num_experts, 1024, 0, st>>>(top_idx, pairs, 0, counts);
+    moe_offsets_kernel<<<1, 32, 0, st>>>(counts, num_experts, offsets);
+    moe_scatter_kernel<<<num_experts, 1024, 0, st>>>(top_idx, pairs, 0, offsets, perm, inv);
+    OXQ_LAUNCH_CHECK("moe dispatch plan kernels");
+    return OXQ_OK;
+}
+
+// out[i, :] = x[perm[i] / top_k, :] for i < rows (bf16 rows, hidden a multiple of 8): the rows of a dispatch in send order.
+OXQ_EXPORT int oxq_moe_gather_rows(const void *x, const int32_t *perm, int rows, int top_k, int hidden, void *out, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(x && perm && out, OXQ_ERR_NULL, "oxq_moe_gather_rows: null pointer");
+    OXQ_REQUIRE(rows > 0 && top_k > 0 && hidden > 0 && hidden % 8 == 0, OXQ_ERR_BAD_SHAPE,
+                "oxq_moe_gather_rows: rows %d, top_k %d, hidden %d (multiple of 8)", rows, top_k, hidden);
+    OXQ_REQUIRE(aligned(x, 16) && aligned(out, 16), OXQ_ERR_BAD_ALIGN, "oxq_moe_gather_rows: rows must be 16-byte aligned");
+    moe_gather_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)x, perm, nullptr, top_k, hidden,
+                                                                         (__nv_bfloat16 *)out, rows);
+    OXQ_LAUNCH_CHECK("moe_gather_kernel");
+    return OXQ_OK;
+}
+
+// Expert ids of rows received in groups (source rank major, local expert minor): counts [world * n_local] -> ids [total].
+OXQ_EXPORT int oxq_moe_expand_ids(const int32_t *counts, int groups, int n_local, int lo, int32_t *ids, void *stream)
+{
+    clear_error();
+    OXQ_REQUIRE(counts && ids, OXQ_ERR_NULL, "oxq_moe_expand_ids: null pointer");
+    OXQ_REQUIRE(groups > 0 && groups <= 2048 && n_local > 0 && groups % n_local == 0, OXQ_ERR_BAD_SHAPE,
+                "oxq_moe_expand_ids: groups %d (at most 2048, a multiple of n_local %d)", groups, n_local);
+    moe_expand_ids_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(counts, groups, n_local, lo, ids);
+    OXQ_LAUNCH_CHECK("moe_expand_ids_kernel");
     return OXQ_OK;
 }

@@ -51,6 +51,34 @@ def combine(rows: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor, pos:
     return out
 
 
+def dispatch_plan(top_idx: torch.Tensor, num_experts: int):
+    """Pairs sorted by expert id (stable) on the device: ``(counts i32 [E], perm i32 [pairs], inv i32 [pairs])``."""
+    idx = top_idx.to(torch.int32).contiguous()
+    pairs = idx.numel()
+    counts = torch.empty(num_experts, dtype=torch.int32, device=idx.device)
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=idx.device)
+    perm = torch.empty(pairs, dtype=torch.int32, device=idx.device)
+    inv = torch.empty(pairs, dtype=torch.int32, device=idx.device)
+    _lib.call("oxq_moe_dispatch_plan", _p(idx), pairs, num_experts, _p(counts), _p(offsets), _p(perm), _p(inv), _stream())
+    return counts, perm, inv
+
+
+def gather_rows(x: torch.Tensor, perm: torch.Tensor, top_k: int) -> torch.Tensor:
+    """``out[i] = x[perm[i] // top_k]``: the rows of a dispatch in send order (bf16, on the device)."""
+    out = torch.empty((perm.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    if perm.numel():
+        _lib.call("oxq_moe_gather_rows", _p(x.contiguous()), _p(perm), perm.numel(), top_k, x.shape[1], _p(out), _stream())
+    return out
+
+
+def expand_ids(counts: torch.Tensor, n_local: int, lo: int, total: int) -> torch.Tensor:
+    """Expert ids of rows received in groups (source rank major, local expert minor) from the groups' sizes."""
+    ids = torch.empty(total, dtype=torch.int32, device=counts.device)
+    if total:
+        _lib.call("oxq_moe_expand_ids", _p(counts), counts.numel(), n_local, lo, _p(ids), _stream())
+    return ids
+
+
 class GptOssMoe:
     """``gu_*``: fused gate/up projection (even rows gate, odd rows up), ``dn_*``: down projection, per expert."""
 

@@ -64,6 +64,17 @@ def plan_dispatch(top_idx: torch.Tensor, num_experts: int, world: int):
     return send_order, send_counts
 
 
+def plan_dispatch_by_expert(top_idx: torch.Tensor, num_experts: int):
+    """The same order refined: pairs sorted by expert id (stable), which under the contiguous :func:`expert_shard` also groups
+    them by destination rank. Returns ``(send_order, per_expert)`` with ``per_expert[e]`` the number of rows for expert ``e``:
+    exchanging these counts tells every owner how many rows of which expert arrive from whom, so the expert ids themselves
+    never travel."""
+    flat = top_idx.reshape(-1).to(torch.int64)
+    send_order = torch.sort(flat, stable=True).indices
+    per_expert = torch.bincount(flat, minlength=num_experts)
+    return send_order, per_expert
+
+
 def combine_rows(rows: torch.Tensor, send_order: torch.Tensor, top_idx: torch.Tensor, top_w: torch.Tensor) -> torch.Tensor:
     """out[t] = sum over slots, in ascending expert id, of top_w[t, s] * rows[position of pair (t, s)] (f32 accumulate)."""
     t, k = top_idx.shape
@@ -202,23 +213,44 @@ class ExpertParallelMoe:
         self.num_experts, self.route, self.local_experts, self.group = num_experts, route, local_experts, group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
+        self.bounds = [expert_shard(num_experts, self.world, r) for r in range(self.world)]
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         top_idx, top_w = self.route(logits)
         k = top_idx.shape[1]
-        send_order, send_counts = plan_dispatch(top_idx, self.num_experts, self.world)
-        recv_counts = exchange_counts(send_counts, self.group)
-        sc, rc = send_counts.tolist(), recv_counts.tolist()  # the one host read-back: buffer sizes
-        rows = x[send_order // k]
-        ids = top_idx.reshape(-1)[send_order].to(torch.int32)
+        on_device = x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+        if on_device:  # counting sort by expert id in three small kernels: counts, send order and its inverse
+            from . import moe
+            per_expert, send_order, pos = moe.dispatch_plan(top_idx, self.num_experts)
+        else:
+            send_order, per_expert = plan_dispatch_by_expert(top_idx, self.num_experts)
+            pos = None
+        sizes = [hi - lo for lo, hi in self.bounds]
+        lo, hi = self.bounds[self.rank]
+        n_local = hi - lo
+        # counts per (source rank, local expert): one small all-to-all; the expert ids of the rows follow from them
+        recv_pe = per_expert.new_empty((self.world * n_local,))
+        dist.all_to_all_single(recv_pe, per_expert, output_split_sizes=[n_local] * self.world, input_split_sizes=sizes,
+                               group=self.group)
+        if len(set(sizes)) == 1:
+            send_counts = per_expert.view(self.world, -1).sum(1)
+        else:
+            send_counts = torch.stack([per_expert[a:b].sum() for a, b in self.bounds])
+        recv_counts = recv_pe.view(self.world, n_local).sum(1)
+        both = torch.cat([send_counts, recv_counts]).tolist()  # the one host read-back: buffer sizes
+        sc, rc = both[:self.world], both[self.world:]
+        total = int(sum(rc))
+        if on_device:
+            rows = moe.gather_rows(x, send_order, k)
+            got_ids = moe.expand_ids(recv_pe, n_local, lo, total)
+        else:
+            rows = x[send_order // k]
+            local_ids = torch.arange(lo, hi, device=recv_pe.device, dtype=torch.int32).repeat(self.world)
+            got_ids = torch.repeat_interleave(local_ids, recv_pe, output_size=total)
         got_rows = all_to_all_rows(rows, sc, rc, self.group)
-        got_ids = all_to_all_rows(ids[:, None], sc, rc, self.group)[:, 0]
         y = self.local_experts(got_rows, got_ids) if got_rows.shape[0] else got_rows
         back = all_to_all_rows(y.to(x.dtype), rc, sc, self.group)
-        if back.is_cuda and back.dtype == torch.bfloat16 and back.shape[1] % 8 == 0:
-            from . import moe  # the device combine: one kernel, ascending expert order, f32 accumulation
-            pos = torch.empty_like(send_order)
-            pos[send_order] = torch.arange(send_order.numel(), device=send_order.device)
+        if on_device:  # the device combine: one kernel, ascending expert order, f32 accumulation
             return moe.combine(back, top_idx, top_w, pos, self.num_experts, x.dtype)
         return combine_rows(back, send_order, top_idx, top_w).to(x.dtype)
 

@@ -205,3 +205,24 @@ def test_grouped_kernel_survives_a_weight_producer_that_never_loads(cuda):
                             d["dn_bias"], 128, 128, 7.0)
     got = y.float().cpu().numpy()
     assert (np.abs(got - ref) <= 2e-2 * np.abs(ref).max(axis=1, keepdims=True) + 1e-5).all()
+
+
+@pytest.mark.parametrize("tokens,experts,k", [(1, 4, 4), (37, 8, 2), (1024, 32, 4), (4099, 32, 4)])
+def test_dispatch_plan_gather_and_ids_match_torch(cuda, tokens, experts, k):
+    """The expert-parallel bookkeeping kernels against their eager equivalents (bit-exact: integer work and row copies)."""
+    g = torch.Generator().manual_seed(tokens)
+    top_idx = torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(tokens)]).to(torch.int32).cuda()
+    counts, perm, inv = moe.dispatch_plan(top_idx, experts)
+    flat = top_idx.reshape(-1).to(torch.int64)
+    ref_perm = torch.sort(flat, stable=True).indices
+    assert torch.equal(counts.long(), torch.bincount(flat, minlength=experts))
+    assert torch.equal(perm.long(), ref_perm)
+    assert torch.equal(inv.long()[ref_perm], torch.arange(flat.numel(), device="cuda"))
+    x = torch.randn(tokens, 64, device="cuda").to(torch.bfloat16)
+    assert torch.equal(moe.gather_rows(x, perm, k), x[ref_perm // k])
+    world, n_local, lo = 4, experts // 4, experts // 4 * 2
+    grp = torch.randint(0, 50, (world * n_local,), generator=g).to(torch.int32).cuda()
+    grp[1] = 0
+    ids = moe.expand_ids(grp, n_local, lo, int(grp.sum()))
+    ref_ids = torch.repeat_interleave(torch.arange(lo, lo + n_local, device="cuda", dtype=torch.int32).repeat(world), grp.long())
+    assert torch.equal(ids, ref_ids)
