@@ -228,20 +228,17 @@ class ExpertParallelMoe:
         sizes = [hi - lo for lo, hi in self.bounds]
         lo, hi = self.bounds[self.rank]
         n_local = hi - lo
+        if on_device:
+            rows = moe.gather_rows(x, send_order, k)  # needs no size from the host: runs while the counts travel
         # counts per (source rank, local expert): one small all-to-all; the expert ids of the rows follow from them
         recv_pe = per_expert.new_empty((self.world * n_local,))
         dist.all_to_all_single(recv_pe, per_expert, output_split_sizes=[n_local] * self.world, input_split_sizes=sizes,
                                group=self.group)
-        if len(set(sizes)) == 1:
-            send_counts = per_expert.view(self.world, -1).sum(1)
-        else:
-            send_counts = torch.stack([per_expert[a:b].sum() for a, b in self.bounds])
-        recv_counts = recv_pe.view(self.world, n_local).sum(1)
-        both = torch.cat([send_counts, recv_counts]).tolist()  # the one host read-back: buffer sizes
-        sc, rc = both[:self.world], both[self.world:]
+        both = torch.cat([per_expert, recv_pe]).tolist()  # the one host read-back: buffer sizes (summed on the host)
+        sc = [sum(both[a:b]) for a, b in self.bounds]
+        rc = [sum(both[self.num_experts + r * n_local:self.num_experts + (r + 1) * n_local]) for r in range(self.world)]
         total = int(sum(rc))
         if on_device:
-            rows = moe.gather_rows(x, send_order, k)
             got_ids = moe.expand_ids(recv_pe, n_local, lo, total)
         else:
             rows = x[send_order // k]
