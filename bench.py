@@ -607,6 +607,14 @@ def run_extras(args, world, rank, c1_layer):
             us = graph_us(lambda: layer.forward_with_logits(xd, ld), 1)
             res[f"decode_tokens{t_dec}"] = {"us": round(us, 2), "gbs_upper_bound_distinct_experts": round(
                 t_dec * 4 * per_pair_bytes / us / 1e3, 1), "note": "bytes counted as if every (token, slot) pair hit a distinct expert"}
+        # batches between decode and the headline size: the grouped kernel reads every routed expert's packed weights once per
+        # token block, no expert is dequantized to a dense copy
+        for t_mid in (32, 128, 512):
+            xm, lm = x[:t_mid].contiguous(), lg[:t_mid].contiguous()
+            for _ in range(2):
+                layer.forward_with_logits(xm, lm)
+            ms_mid = _timed_ms(torch, dist, world, lambda: layer.forward_with_logits(xm, lm), 5)
+            res[f"tokens{t_mid}"] = {"ms": round(ms_mid, 4), "tokens_per_s": round(t_mid / ms_mid * 1e3, 0)}
         if world > 1:  # expert parallel: tokens data-parallel, all-to-all dispatch and combine
             t_local = tokens // world
             sl = slice(rank * t_local, (rank + 1) * t_local)

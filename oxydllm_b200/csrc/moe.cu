@@ -30,6 +30,7 @@ constexpr int MOE_MAX_TOPK = 8;
 // Up to this many (token, slot) pairs the layer runs as batched single-token GEMVs on the packed
 // weights of the selected experts only (decode); above, it dequantizes expert groups for the grouped GEMM.
 constexpr int MOE_DECODE_MAX_PAIRS = 64;
+constexpr int MOE_DECODE_FUSED_FROM_PAIRS = 48;
 
 // One warp per token: f32 softmax over all experts, k rounds of arg-max (ties: lower index),
 // optional renormalisation by the sum of the selected probabilities (moe.rs:472-487).
@@ -442,7 +443,14 @@ static int moe_forward_impl(const void *x, int x_dtype, const float *router_logi
     if (given_ids) moe_assign_kernel<<<ceil_div(tokens, 256), 256, 0, st>>>(given_ids, tokens, top_idx, top_w);
     else moe_route_kernel<<<ceil_div(tokens * 32, 256), 256, 0, st>>>(router_logits, tokens, num_experts, top_k, norm_topk,
                                                                       top_idx, top_w);
-    if (L.decode) {
+    const int a_rows = pairs + 128;
+    // Both projections through the kernel that unpacks the MXFP4 blocks inside the tensor-core loop, where it takes the shapes:
+    // no dequantized slab, one launch per projection over all experts.
+    const bool fused = moe_fused_supported(2 * inter, hidden, gu_blocks, gu_scales, xs, h, inter) &&
+                       moe_fused_supported(hidden, inter, dn_blocks, dn_scales, h, xs, hidden);
+    // The per-pair GEMVs cost about 6.3 us a pair on the GPT-OSS shape (201 us at 32 pairs); the grouped kernel reads every
+    // expert that has rows once, 0.32 ms at 128 pairs: it takes over from about 48 pairs.
+    if (L.decode && !(fused && pairs > MOE_DECODE_FUSED_FROM_PAIRS)) {
         OXQ_REQUIRE(aligned(gu_blocks, 16) && aligned(dn_blocks, 16), OXQ_ERR_BAD_ALIGN,
                     "oxq_gptoss_moe_forward: expert blocks must be 16-byte aligned");
         // Decode: only the selected experts' packed weights are read. gate_up (f32 out, bias folded) ->
@@ -462,11 +470,6 @@ static int moe_forward_impl(const void *x, int x_dtype, const float *router_logi
         OXQ_LAUNCH_CHECK("moe_combine_kernel");
         return OXQ_OK;
     }
-    const int a_rows = pairs + 128;
-    // Both projections through the kernel that unpacks the MXFP4 blocks inside the tensor-core loop, where it takes the shapes:
-    // no dequantized slab, one launch per projection over all experts.
-    const bool fused = moe_fused_supported(2 * inter, hidden, gu_blocks, gu_scales, xs, h, inter) &&
-                       moe_fused_supported(hidden, inter, dn_blocks, dn_scales, h, xs, hidden);
     moe_count_kernel<<<n_exp, 1024, 0, st>>>(top_idx, pairs, expert_lo, counts);
     if (fused) moe_plan_blocks_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, moe_fused_block_rows(), offsets, entries, grp_beg);
     else moe_plan_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, L.group_experts, offsets, entries, grp_beg);
