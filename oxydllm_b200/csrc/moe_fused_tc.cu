@@ -275,29 +275,37 @@ __global__ void __launch_bounds__(MF_THREADS, 1)
                 const uint4 rawv = mf_lds128(raw_base + (r0 + h) * MF_RAW_BYTES + raw_off);
                 const uint32_t v[4] = {rawv.x, rawv.y, rawv.z, rawv.w};
                 const uint32_t dst = base + (s0 + h) * MF_A_BYTES + a_row;
-                if (sb >= 4u && sb <= 250u) { // 2^(s-127) as a bf16 pair: the product is exact
+                if (sb >= 4u && sb <= 250u) { // 2^(s-127) as a bf16 pair: the products are exact
+                    // The block's eight magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 times its scale, as bf16 (four multiplies for
+                    // 32 weights), split into a table of low bytes and a table of high bytes; the byte permute unit then looks
+                    // up four nibbles at a time, and each nibble's sign bit is copied onto its element (prmt's sign-replicate
+                    // mode turns bit 7 of a byte into a mask).
                     const uint32_t s2 = (sb << 7) | (sb << 23);
+                    const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162 *>(&s2);
+                    const uint32_t mags[4] = {0x3F000000u, 0x3FC03F80u, 0x40404000u, 0x40C04080u}; // (0, .5) (1, 1.5) (2, 3) (4, 6)
+                    uint32_t pm[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const __nv_bfloat162 t = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&mags[i]), sc);
+                        pm[i] = *reinterpret_cast<const uint32_t *>(&t);
+                    }
+                    const uint32_t tlo_a = __byte_perm(pm[0], pm[1], 0x6420u), thi_a = __byte_perm(pm[0], pm[1], 0x7531u);
+                    const uint32_t tlo_b = __byte_perm(pm[2], pm[3], 0x6420u), thi_b = __byte_perm(pm[2], pm[3], 0x7531u);
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
-                        // The eight magnitudes 0, .5, 1, 1.5, 2, 3, 4, 6 as bf16 are looked up a byte at a time by the byte
-                        // permute unit (low bytes 00 00 80 C0 00 40 80 C0, high bytes 00 3F 3F 3F 40 40 40 40); the sign bit
-                        // of each nibble is moved onto the multiplier, so the product carries it.
                         const uint32_t w = v[q];
-                        const uint32_t sel_l = w & 0x77777777u, sel_h = sel_l >> 16, sg = w & 0x88888888u;
-                        const uint32_t lo_a = __byte_perm(0xC0800000u, 0xC0804000u, sel_l), hi_a = __byte_perm(0x3F3F3F00u, 0x40404040u, sel_l);
-                        const uint32_t lo_b = __byte_perm(0xC0800000u, 0xC0804000u, sel_h), hi_b = __byte_perm(0x3F3F3F00u, 0x40404040u, sel_h);
+                        const uint32_t sel_l = w & 0x77777777u, sel_h = sel_l >> 16, wl = w << 4;
+                        const uint32_t lo_a = __byte_perm(tlo_a, tlo_b, sel_l), hi_a = __byte_perm(thi_a, thi_b, sel_l);
+                        const uint32_t lo_b = __byte_perm(tlo_a, tlo_b, sel_h), hi_b = __byte_perm(thi_a, thi_b, sel_h);
                         const uint32_t pr[4] = {__byte_perm(lo_a, hi_a, 0x5140u), __byte_perm(lo_a, hi_a, 0x7362u),
                                                 __byte_perm(lo_b, hi_b, 0x5140u), __byte_perm(lo_b, hi_b, 0x7362u)};
                         uint4 o;
                         uint32_t *ov = reinterpret_cast<uint32_t *>(&o);
 #pragma unroll
                         for (int b = 0; b < 4; b++) {
-                            const uint32_t sx = __byte_perm(sg, 0u, 0x4440u + b) * 0x01001000u; // sign bits 3, 7 of the byte -> 15, 31
-                            uint32_t mult;
-                            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(mult) : "r"(sx), "r"(0x80008000u), "r"(s2)); // (sx & mask) ^ s2
-                            const __nv_bfloat162 r2 = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&pr[b]),
-                                                              *reinterpret_cast<const __nv_bfloat162 *>(&mult));
-                            ov[b] = *reinterpret_cast<const uint32_t *>(&r2);
+                            // byte 1 <- sign of the low nibble of byte b (bit 7 of (w << 4)), byte 3 <- sign of the high nibble
+                            const uint32_t sm = __byte_perm(wl, w, 0xC080u + 0x1010u * b);
+                            asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(ov[b]) : "r"(sm), "r"(0x80008000u), "r"(pr[b])); // (sm & mask) ^ pr
                         }
                         mf_sts128(dst + ((((uint32_t)(half * 4 + q)) ^ sw) << 4), o);
                     }
