@@ -403,11 +403,9 @@ bool moe_fused_supported(int n, int k, const void *blocks, const void *scales, c
 {
     if (const char *env = tuning_env("OXQ_MOE_FUSED"))
         if (env[0] == '0') return false;
-    if (n <= 0 || k <= 0 || k % 32 != 0 || n % 2 != 0) return false;
-    const int nkb = k / 32;
-    (void)nkb;
-    return (k / 2) % 16 == 0 && aligned(blocks, 16) && aligned(scales, 16) && aligned(a, 16) &&
-           aligned(out, 2) && ldo > 0;
+    // k % 32 == 0: whole MXFP4 blocks, and the packed rows (k / 2 bytes) keep the 16-byte pitch a tensor map needs
+    if (n <= 0 || k <= 0 || k % 32 != 0 || n % 2 != 0 || scales == nullptr) return false;
+    return aligned(blocks, 16) && aligned(a, 16) && aligned(out, 2) && ldo > 0;
 }
 
 // out = epilogue(a . W_e^T + bias_e) for every token block of the table: a = expert-sorted activations [a_rows, k] bf16,
