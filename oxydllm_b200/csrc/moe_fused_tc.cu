@@ -8,11 +8,12 @@
 // running at the same time share their token block in L2. Per CTA:
 //   warp 0 (one lane)   TMA: boxes of packed nibbles (128 out features x 32 bytes = 64 input columns) into a
 //                       ring of six slots;
-//   warp 2 (one lane)   TMA: the stage's tile of the activations ([rows, 64] bf16 in boxes of 64 rows, 128-byte swizzle)
-//                       into one of four slots;
-//   warps 4..19         unpack, two teams of eight warps taking stages in turn: a thread turns
-//                       one 16-byte block (32 weights; its E8M0 scale byte read through L1/L2) into 32 bf16 weights, the bits the
-//                       dequantization kernel writes, as four 16-byte chunks of the K-major operand row (128-byte swizzle) in one of four slots;
+//   warp 2 (one lane)   TMA: the stage's tile of the activations ([rows, 64] bf16 in boxes of 64 rows, 128-byte
+//                       swizzle) into one of four slots;
+//   warps 4..19         unpack, two teams of eight warps taking stages in turn: a thread turns one 16-byte block
+//                       (32 weights; its E8M0 scale byte read through L1/L2) into 32 bf16 weights, the bits the
+//                       dequantization kernel writes, as four 16-byte chunks of the K-major operand row (128-byte
+//                       swizzle) in one of four slots;
 //   warp 1 (one lane)   tcgen05.mma kind::f16, A = weights [128, 64], B = activations, D[128, rows] f32 in one of
 //                       two tensor-memory buffers for the whole of k; one commit per stage frees the slot (weights and
 //                       activations share a full / empty barrier pair per slot, so the issuer polls once per stage);
