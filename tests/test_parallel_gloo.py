@@ -57,8 +57,8 @@ def test_column_parallel_awq_equals_unsharded():
     assert all(r[0] == 0.0 for r in res)  # same arithmetic per column: identical bits
 
 
-def _ep_case(rank, world):
-    e, hidden, inter, t_local, k = 6, 64, 32, 11, 3
+def _ep_case(rank, world, e=6):
+    hidden, inter, t_local, k = 64, 32, 11, 3
     d = synth.gptoss_moe(e, hidden, inter, t_local * world, seed=7)
     x_all, lg_all = d["x"], d["logits"]
     sl = slice(rank * t_local, (rank + 1) * t_local)
@@ -90,6 +90,15 @@ def test_expert_parallel_all_to_all_equals_unsharded():
     assert all(r < 1e-5 for r in res), res
 
 
+def _ep_case_uneven(rank, world):
+    return _ep_case(rank, world, e=5)  # shards (0, 3) and (3, 5): unequal split sizes in the counts exchange
+
+
+def test_expert_parallel_with_an_uneven_expert_split():
+    res = _run(_ep_case_uneven)
+    assert all(r < 1e-5 for r in res), res
+
+
 def test_shard_arithmetic():
     assert [parallel.column_shard(128256, 8, r) for r in (0, 7)] == [(0, 16032), (112224, 128256)]
     assert [parallel.expert_shard(32, 8, r) for r in (0, 3, 7)] == [(0, 4), (12, 16), (28, 32)]
@@ -101,3 +110,5 @@ def test_shard_arithmetic():
     top_idx = torch.tensor([[5, 0], [1, 4]])
     order, counts = parallel.plan_dispatch(top_idx, 6, 2)
     assert counts.tolist() == [2, 2] and order.tolist() == [1, 2, 0, 3]
+    order, per_expert = parallel.plan_dispatch_by_expert(top_idx, 6)  # sorted by expert id, pair order kept
+    assert per_expert.tolist() == [1, 1, 0, 0, 1, 1] and order.tolist() == [1, 2, 3, 0]
