@@ -471,6 +471,8 @@ static int moe_forward_impl(const void *x, int x_dtype, const float *router_logi
         return OXQ_OK;
     }
     moe_count_kernel<<<n_exp, 1024, 0, st>>>(top_idx, pairs, expert_lo, counts);
+    // the grouped kernel's table of token blocks goes where the m-tile table of the dense path would (same capacity bound);
+    // grp_beg[0] then holds the number of blocks
     if (fused) moe_plan_blocks_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, moe_fused_block_rows(), offsets, entries, grp_beg);
     else moe_plan_kernel<<<1, 32, 0, st>>>(counts, n_exp, expert_lo, L.group_experts, offsets, entries, grp_beg);
     moe_scatter_kernel<<<n_exp, 1024, 0, st>>>(top_idx, pairs, expert_lo, offsets, perm, inv);
